@@ -1,0 +1,80 @@
+"""ctypes binding of libb200ops.so (the C ABI declared in include/b200ops.h).
+
+There is no fallback: if the shared library is missing the import fails with
+instructions to build it, and every non-zero return code raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200ops.so")
+
+BF16, F32 = 0, 1
+FLAG_PDL = 1
+EPI_NONE, EPI_SWIGLU, EPI_GELU = 0, 1, 2
+
+ERRORS = {
+    -1: "B200_ERR_SHAPE (unsupported size / divisibility)",
+    -2: "B200_ERR_ALIGN (pointer or leading dimension not 16-byte aligned)",
+    -3: "B200_ERR_LAUNCH (CUDA launch error)",
+    -4: "B200_ERR_ARG (null pointer / bad enum)",
+    -5: "B200_ERR_TIMEOUT (bounded device-side wait expired)",
+    -6: "B200_ERR_DRIVER (driver entry point unavailable)",
+}
+
+_p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_int64
+
+# name -> (restype, argtypes); must list every symbol include/b200ops.h declares
+SIGNATURES = {
+    "b200_version": (_i, []),
+    "b200_sm_count": (_i, []),
+    "b200_gemv_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _p]),
+    "b200_add_rmsnorm": (_i, [_p, _p, _i, _p, _p, _i, _p, _i, _i, _f, _i, _p]),
+    "b200_add_layernorm": (_i, [_p, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _f, _i, _p]),
+    "b200_qk_rope_cache": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
+                                _f, _i, _p]),
+    "b200_flash_decode_workspace_bytes": (_l, [_i, _i, _i, _i]),
+    "b200_flash_decode": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _l, _l, _i, _f, _i, _p]),
+    "b200_gemm_bf16": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _i, _p]),
+    "b200_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),
+    "b200_flash_prefill": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_i, _f, _i, _p]),
+    "b200_embed_gather": (_i, [_p, _i, _p, _p, _i, _i, _i, _p]),
+    "b200_silu_mul": (_i, [_p, _p, _p, _l, _i, _p]),
+    "b200_argmax_workspace_bytes": (_l, [_i]),
+    "b200_argmax_f32": (_i, [_p, _p, _p, _i, _i, _p, _i, _p]),
+    "b200_greedy_select": (_i, [_p, _p, _i, _p, _p, _i, _i, _p]),
+}
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def load(path: str = LIB_PATH) -> C.CDLL:
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing: build it with `python -m hoid_optimized_models_b200.build` "
+            "(needs nvcc); there is no CPU or PyTorch fallback for these ops")
+    lib = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+_LIB = None
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = load()
+    return _LIB
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise B200Error(f"{what} failed: {ERRORS.get(code, code)}")

@@ -1,0 +1,465 @@
+// Dense / grouped bf16 GEMM  Y[M,N] = X[M,K] W[N,K]^T  on the sm_100a tensor cores.
+//
+// Persistent, warp-specialised, one CTA per SM:
+//   warp 0      TMA producer: cp.async.bulk.tensor 2D loads of a 128x64 X tile and a
+//               256x64 W tile (both K-major, 128-byte swizzle) into a 4-stage ring
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (cta_group::1,
+//               kind::f16, M128 N256 K16) with fp32 accumulators in tensor memory;
+//               tcgen05.commit releases ring stages and publishes accumulators
+//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time, fused bias / residual /
+//               SwiGLU / GELU, bf16 stores.  Two 256-column accumulators alternate so
+//               the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Grouped mode (MoE experts): rows of X are sorted by expert, `offsets[e]` is the
+// first row of expert e, W is [E, N, K]; M-tiles never straddle an expert for
+// stores (loads may read the neighbour's rows, the epilogue masks them).
+//
+// Every mbarrier wait is bounded: on expiry the CTA records B200_ERR_TIMEOUT in
+// the status word, all roles leave their loops, tensor memory is released and
+// the kernel returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kABytes = BM * BK * 2;   // 16 KiB
+constexpr uint32_t kBBytes = BN * BK * 2;   // 32 KiB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr int kMaxExperts = 256;
+constexpr long long kWaitBudget = 4000000000LL;  // clock64 ticks (~2 s)
+
+struct GemmArgs {
+  uint16_t* y; const uint16_t* bias; const uint16_t* resid; const int* offsets;
+  int* status;
+  int M, N, K, ldy, ldr, epilogue, n_groups;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the budget expires or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 1023) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitBudget) { *abort_flag = 1; return false; }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte-swizzled operand tile: rows 128 B apart, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);   // start address
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for SW128 K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                        // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+// bf16 x bf16 -> fp32, both operands K-major, M = BM, N = BN.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                            ((uint32_t)(BM >> 4) << 24);
+
+// ---------------------------------------------------------------- tile schedule
+struct Tile { int row0, row_end, n0, wrow0; bool valid; };
+
+struct Sched {
+  int mt, nt, total;
+  const int* cum;      // grouped: smem prefix of tiles per group [n_groups + 1]
+  const int* offs;     // grouped: smem row offsets [n_groups + 1]
+  int n_groups, M, N;
+  __device__ __forceinline__ Tile get(int t) const {
+    Tile r;
+    r.valid = t < total;
+    if (!r.valid) { r.row0 = r.row_end = r.n0 = r.wrow0 = 0; return r; }
+    if (n_groups == 0) {
+      const int tm = t % mt, tn = t / mt;
+      r.row0 = tm * BM; r.row_end = min(M, r.row0 + BM); r.n0 = tn * BN; r.wrow0 = r.n0;
+    } else {
+      int lo = 0, hi = n_groups - 1;           // last group with cum[g] <= t
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (cum[mid] <= t) lo = mid; else hi = mid - 1; }
+      const int local = t - cum[lo];
+      const int tn = local % nt, tm = local / nt;
+      r.row0 = offs[lo] + tm * BM; r.row_end = min(offs[lo + 1], r.row0 + BM);
+      r.n0 = tn * BN; r.wrow0 = lo * N + r.n0;
+    }
+    return r;
+  }
+};
+
+__device__ __forceinline__ float gelu_erf(float v) {
+  return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+            GemmArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // carve: [stages x (A|B)] 1024-aligned, then barriers and bookkeeping
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + kStages * kStageBytes);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_cum = reinterpret_cast<int*>(tmem_slot + 4);
+  int* s_off = s_cum + (kMaxExperts + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto full_bar = [&](int s) { return smem_u32(bars + s); };
+  auto empty_bar = [&](int s) { return smem_u32(bars + kStages + s); };
+  auto tfull_bar = [&](int s) { return smem_u32(bars + 2 * kStages + s); };
+  auto tempty_bar = [&](int s) { return smem_u32(bars + 2 * kStages + 2 + s); };
+
+  pdl_launch_dependents();
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(tfull_bar(s), 1); mbar_init(tempty_bar(s), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  pdl_wait();  // offsets / X / residual come from earlier kernels
+
+  Sched sch;
+  sch.M = a.M; sch.N = a.N; sch.n_groups = a.n_groups;
+  sch.nt = (a.N + BN - 1) / BN;
+  sch.cum = s_cum; sch.offs = s_off;
+  if (a.n_groups > 0) {
+    for (int g = tid; g <= a.n_groups; g += kGemmThreads) s_off[g] = a.offsets[g];
+    __syncthreads();
+    if (tid == 0) {
+      int c = 0;
+      for (int g = 0; g < a.n_groups; ++g) {
+        s_cum[g] = c;
+        c += ((s_off[g + 1] - s_off[g] + BM - 1) / BM) * sch.nt;
+      }
+      s_cum[a.n_groups] = c;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  sch.mt = (a.M + BM - 1) / BM;
+  sch.total = a.n_groups > 0 ? s_cum[a.n_groups] : sch.mt * sch.nt;
+  const int kblocks = (a.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < sch.total; t += gridDim.x) {
+        const Tile tl = sch.get(t);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t sa = base + stage * kStageBytes;
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(sa, &map_x, full_bar(stage), kb * BK, tl.row0);
+          tma_load_2d(sa + kABytes, &map_w, full_bar(stage), kb * BK, tl.wrow0);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // drain: give loads already in flight a bounded chance to land before exit
+        for (int s = 0; s < kStages; ++s) {
+          const long long t0 = clock64();
+          while (!mbar_try(full_bar(s), 0) && !mbar_try(full_bar(s), 1) &&
+                 clock64() - t0 < 2000000) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < sch.total; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * kStageBytes;
+          const uint64_t da = umma_desc(sa), db = umma_desc(sa + kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advance 16 elements (32 B) along K inside the 128-byte swizzle atom
+            tc_mma(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), kIdesc,
+                   (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int slab = warp & 3;  // TMEM lanes [32*slab, 32*slab+32) belong to this warp
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < sch.total; t += gridDim.x) {
+      const Tile tl = sch.get(t);
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tl.row0 + slab * 32 + lane;
+      const bool row_ok = row < tl.row_end;
+      const uint32_t taddr = tmem_base + ((uint32_t)(slab * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = tl.n0 + c * 32;
+        if (col0 >= a.N) break;  // warp-uniform
+        uint32_t r[32];
+        tc_ld32(taddr + c * 32, r);
+        tc_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (a.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < a.N) {
+              float b8[8];
+              unpack8(*reinterpret_cast<const uint4*>(a.bias + col0 + j), b8);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[j + e] += b8[e];
+            }
+          }
+        }
+        if (a.epilogue == B200_EPI_SWIGLU) {
+          if (row_ok) {
+            uint16_t* dst = a.y + (size_t)row * a.ldy + (col0 >> 1);
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              if (col0 + 2 * j < a.N) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float g = v[2 * (j + e)], u = v[2 * (j + e) + 1];
+                  o[e] = g / (1.f + __expf(-g)) * u;
+                }
+                uint4 w;
+                w.x = pack_bf16(o[0], o[1]); w.y = pack_bf16(o[2], o[3]);
+                w.z = pack_bf16(o[4], o[5]); w.w = pack_bf16(o[6], o[7]);
+                *reinterpret_cast<uint4*>(dst + j) = w;
+              }
+            }
+          }
+        } else {
+          if (a.epilogue == B200_EPI_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+          }
+          if (row_ok) {
+            uint16_t* dst = a.y + (size_t)row * a.ldy + col0;
+            const uint16_t* rs = a.resid ? a.resid + (size_t)row * a.ldr + col0 : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < a.N) {
+                if (rs != nullptr) {
+                  float r8[8];
+                  unpack8(*reinterpret_cast<const uint4*>(rs + j), r8);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[j + e] += r8[e];
+                }
+                uint4 w;
+                w.x = pack_bf16(v[j + 0], v[j + 1]); w.y = pack_bf16(v[j + 2], v[j + 3]);
+                w.z = pack_bf16(v[j + 4], v[j + 5]); w.w = pack_bf16(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(dst + j) = w;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag && a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+static PFN_cuTensorMapEncodeTiled g_encode = nullptr;
+
+static int get_encode() {
+  if (g_encode != nullptr) return B200_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qr;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess ||
+      qr != cudaDriverEntryPointSuccess || fn == nullptr)
+    return B200_ERR_DRIVER;
+  g_encode = (PFN_cuTensorMapEncodeTiled)fn;
+  return B200_OK;
+}
+
+// 2D bf16 map over a row-major [rows, cols] matrix with leading dimension ld (elements);
+// box = box_rows x 64 columns, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                    uint32_t box_rows) {
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstr,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_DRIVER;
+}
+
+constexpr size_t kGemmSmem = 1024 + (size_t)kStages * kStageBytes + 256 + 2 * (kMaxExperts + 1) * 4;
+
+static int gemm_launch(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldw,
+                       int ldy, const void* bias, const void* resid, int ldr, int epilogue,
+                       const int* offsets, int n_groups, int max_tiles_m, int* status, int flags,
+                       cudaStream_t stream) {
+  if (!x || !w || !y) return B200_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (N & 7)) return B200_ERR_SHAPE;
+  if ((ldx & 7) || (ldw & 7) || (ldy & 7) || (resid && (ldr & 7))) return B200_ERR_ALIGN;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)y & 15) ||
+      ((uintptr_t)bias & 15) || ((uintptr_t)resid & 15))
+    return B200_ERR_ALIGN;
+  if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_GELU) return B200_ERR_ARG;
+  if (epilogue == B200_EPI_SWIGLU && (resid != nullptr || (N & 15))) return B200_ERR_SHAPE;
+  if (n_groups < 0 || n_groups > kMaxExperts || (n_groups > 0 && !offsets)) return B200_ERR_ARG;
+  int rc = get_encode();
+  if (rc != B200_OK) return rc;
+
+  CUtensorMap mx, mw;
+  const uint64_t wrows = n_groups > 0 ? (uint64_t)n_groups * N : (uint64_t)N;
+  if ((rc = make_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, BM)) != B200_OK) return rc;
+  if ((rc = make_map(&mw, w, wrows, (uint64_t)K, (uint64_t)ldw, BN)) != B200_OK) return rc;
+
+  GemmArgs a;
+  a.y = (uint16_t*)y; a.bias = (const uint16_t*)bias; a.resid = (const uint16_t*)resid;
+  a.offsets = offsets; a.status = status;
+  a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.ldr = ldr; a.epilogue = epilogue; a.n_groups = n_groups;
+
+  const int nt = (N + BN - 1) / BN;
+  long tiles = (long)max_tiles_m * nt;
+  int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
+  if (grid < 1) grid = 1;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kGemmSmem) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  cudaError_t e = launch(gemm_kernel, dim3(grid), dim3(kGemmThreads), kGemmSmem, stream,
+                         (flags & B200_FLAG_PDL) != 0, mx, mw, a);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K,
+                              int ldx, int ldw, int ldy, const void* bias, const void* resid,
+                              int ldr, int epilogue, int* status, int flags,
+                              b200_stream_t stream) {
+  return gemm_launch(x, w, y, M, N, K, ldx, ldw, ldy, bias, resid, ldr, epilogue, nullptr, 0,
+                     (M + BM - 1) / BM, status, flags, (cudaStream_t)stream);
+}
+
+extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, void* y, const int* offsets,
+                                     int n_experts, int rows, int N, int K, int ldx, int ldy,
+                                     int epilogue, int* status, int flags, b200_stream_t stream) {
+  if (n_experts <= 0) return B200_ERR_ARG;
+  // upper bound on M-tiles: every expert may add one partial tile
+  const int max_tiles_m = (rows + BM - 1) / BM + n_experts;
+  return gemm_launch(x, w, y, rows, N, K, ldx, K, ldy, nullptr, nullptr, 0, epilogue, offsets,
+                     n_experts, max_tiles_m, status, flags, (cudaStream_t)stream);
+}

@@ -1,0 +1,220 @@
+// Decode GEMV  y[N] = W[N,K] x[K]  — HBM-bound weight streaming for sm_100a.
+//
+// Work split: each CTA owns a contiguous block of rows.  Inside the CTA the
+// block's weights are one flat run of 512-byte "segments" (32 lanes x 16 B =
+// 256 bf16 of one row); the run is cut into eight equal pieces, one per warp,
+// so every warp streams a contiguous address range with perfectly coalesced
+// 128-bit loads and the load imbalance is at most one segment.  A lane keeps a
+// private fp32 partial for the row it is in; when the warp crosses a row
+// boundary it shuffle-reduces and parks the value in shared memory.  Row sums
+// are finished in a fixed order (warp 0..7), so results are bit-reproducible.
+//
+// The first batch of weight loads is issued before the programmatic-dependent-
+// launch wait, so under B200_FLAG_PDL weight streaming overlaps the tail of
+// the previous kernel in the stream.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kGemvU = 8;  // 16-byte loads in flight per lane per batch
+
+struct GemvArgs {
+  const void* x;
+  const uint16_t* w;
+  void* y;
+  const uint16_t* norm_w;
+  const uint16_t* bias;
+  const void* resid;
+  int K, N, ldw, rpc;  // rpc = rows per CTA
+  int x_dtype, y_dtype, resid_dtype, epilogue;
+  float eps;
+};
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
+__device__ __forceinline__ float gelu_erf_f(float v) {
+  return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+}
+
+__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* xs = reinterpret_cast<float*>(smem_raw);          // K floats, segment-swizzled
+  float* part = xs + a.K;                                    // rpc * kGemvWarps
+  float* red = part + a.rpc * kGemvWarps;                    // 32
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = a.K, spr = K >> 8;
+  const int r0 = blockIdx.x * a.rpc;
+  const int nrows = min(a.N - r0, a.rpc);
+
+  pdl_launch_dependents();
+  if (nrows <= 0) return;
+
+  const long S = (long)nrows * spr;
+  const int s0 = (int)(S * warp / kGemvWarps);
+  const int s1 = (int)(S * (warp + 1) / kGemvWarps);
+
+  // load cursor and compute cursor over (row, segment-in-row)
+  int lrow = s0 / spr, lk = s0 - lrow * spr;
+  int crow = lrow, ck = lk;
+  const unsigned char* wb =
+      reinterpret_cast<const unsigned char*>(a.w) + (size_t)r0 * a.ldw * 2 + lane * 16;
+  const size_t row_bytes = (size_t)a.ldw * 2;
+
+  uint4 wc[kGemvU];
+#pragma unroll
+  for (int j = 0; j < kGemvU; ++j) {
+    if (s0 + j < s1) {
+      wc[j] = ldg_stream(wb + lrow * row_bytes + (size_t)lk * 512);
+      if (++lk == spr) { lk = 0; ++lrow; }
+    }
+  }
+
+  // ---- everything below may depend on the previous kernel ----
+  pdl_wait();
+
+  // stage x (fp32, segment-swizzled: [seg][half][lane] float4) and zero the row partials
+  float ss = 0.f;
+  float4* xs4 = reinterpret_cast<float4*>(xs);
+  for (int i = tid; i < (K >> 2); i += kGemvThreads) {
+    float4 v;
+    if (a.x_dtype == B200_F32) {
+      v = reinterpret_cast<const float4*>(a.x)[i];
+    } else {
+      uint2 u = reinterpret_cast<const uint2*>(a.x)[i];
+      v = make_float4(bf16lo(u.x), bf16hi(u.x), bf16lo(u.y), bf16hi(u.y));
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    const int k = i << 2, seg = k >> 8, within = k & 255;
+    xs4[seg * 64 + ((within >> 2) & 1) * 32 + (within >> 3)] = v;
+  }
+  for (int i = tid; i < a.rpc * kGemvWarps; i += kGemvThreads) part[i] = 0.f;
+  if (a.norm_w != nullptr) {
+    const float tot = block_sum(ss, red);
+    const float scale = rsqrtf(tot / (float)K + a.eps);
+    for (int i = tid; i < (K >> 2); i += kGemvThreads) {
+      const int k = i << 2, seg = k >> 8, within = k & 255;
+      const int si = seg * 64 + ((within >> 2) & 1) * 32 + (within >> 3);
+      uint2 u = reinterpret_cast<const uint2*>(a.norm_w)[i];
+      float4 v = xs4[si];
+      v.x = v.x * scale * bf16lo(u.x);
+      v.y = v.y * scale * bf16hi(u.x);
+      v.z = v.z * scale * bf16lo(u.y);
+      v.w = v.w * scale * bf16hi(u.y);
+      xs4[si] = v;
+    }
+  }
+  __syncthreads();
+
+  float acc = 0.f;
+  for (int s = s0; s < s1; s += kGemvU) {
+    uint4 wn[kGemvU];
+#pragma unroll
+    for (int j = 0; j < kGemvU; ++j) {
+      if (s + kGemvU + j < s1) {
+        wn[j] = ldg_stream(wb + lrow * row_bytes + (size_t)lk * 512);
+        if (++lk == spr) { lk = 0; ++lrow; }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kGemvU; ++j) {
+      if (s + j < s1) {
+        const float4 xa = xs4[ck * 64 + lane];
+        const float4 xb = xs4[ck * 64 + 32 + lane];
+        const uint4 w = wc[j];
+        acc = fmaf(bf16lo(w.x), xa.x, acc);
+        acc = fmaf(bf16hi(w.x), xa.y, acc);
+        acc = fmaf(bf16lo(w.y), xa.z, acc);
+        acc = fmaf(bf16hi(w.y), xa.w, acc);
+        acc = fmaf(bf16lo(w.z), xb.x, acc);
+        acc = fmaf(bf16hi(w.z), xb.y, acc);
+        acc = fmaf(bf16lo(w.w), xb.z, acc);
+        acc = fmaf(bf16hi(w.w), xb.w, acc);
+        if (++ck == spr) {
+          const float v = warp_sum(acc);
+          if (lane == 0) part[crow * kGemvWarps + warp] = v;
+          acc = 0.f; ck = 0; ++crow;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kGemvU; ++j) wc[j] = wn[j];
+  }
+  if (ck != 0 && s1 > s0) {
+    const float v = warp_sum(acc);
+    if (lane == 0) part[crow * kGemvWarps + warp] = v;
+  }
+  __syncthreads();
+
+  // ---- epilogue: fixed-order row sums ----
+  auto row_value = [&](int r) -> float {
+    float v = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGemvWarps; ++i) v += part[r * kGemvWarps + i];
+    if (a.bias != nullptr) v += __uint_as_float((uint32_t)a.bias[r0 + r] << 16);
+    return v;
+  };
+  if (a.epilogue == B200_EPI_SWIGLU) {
+    for (int t = tid; t < (nrows >> 1); t += kGemvThreads) {
+      const float g = row_value(2 * t), u = row_value(2 * t + 1);
+      const float o = silu_f(g) * u;
+      const int oi = (r0 >> 1) + t;
+      if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = o;
+      else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(o);
+    }
+  } else {
+    for (int t = tid; t < nrows; t += kGemvThreads) {
+      float v = row_value(t);
+      if (a.epilogue == B200_EPI_GELU) v = gelu_erf_f(v);
+      const int oi = r0 + t;
+      if (a.resid != nullptr) {
+        v += (a.resid_dtype == B200_F32)
+                 ? reinterpret_cast<const float*>(a.resid)[oi]
+                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.resid)[oi]);
+      }
+      if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = v;
+      else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(v);
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y, int y_dtype,
+                              int K, int N, int ldw, const void* norm_w, float eps,
+                              const void* bias, const void* resid, int resid_dtype,
+                              int epilogue, int flags, b200_stream_t stream) {
+  if (!x || !w || !y) return B200_ERR_ARG;
+  if (K <= 0 || N <= 0 || (K & 255) != 0 || ldw < K) return B200_ERR_SHAPE;
+  if ((ldw & 7) != 0 || ((uintptr_t)w & 15) != 0 || ((uintptr_t)x & 15) != 0) return B200_ERR_ALIGN;
+  if (epilogue == B200_EPI_SWIGLU && ((N & 1) != 0 || resid != nullptr)) return B200_ERR_SHAPE;
+  if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_GELU) return B200_ERR_ARG;
+  if (K > 32768) return B200_ERR_SHAPE;
+
+  // two CTAs per SM; grow the grid in whole waves until the per-CTA row block is small
+  int grid = 2 * kNumSMs;
+  int rpc = (N + grid - 1) / grid;
+  while (rpc > 1024) { grid += 2 * kNumSMs; rpc = (N + grid - 1) / grid; }
+  if (epilogue == B200_EPI_SWIGLU && (rpc & 1)) ++rpc;
+  grid = (N + rpc - 1) / rpc;
+
+  GemvArgs a;
+  a.x = x; a.w = (const uint16_t*)w; a.y = y;
+  a.norm_w = (const uint16_t*)norm_w; a.bias = (const uint16_t*)bias; a.resid = resid;
+  a.K = K; a.N = N; a.ldw = ldw; a.rpc = rpc;
+  a.x_dtype = x_dtype; a.y_dtype = y_dtype; a.resid_dtype = resid_dtype; a.epilogue = epilogue;
+  a.eps = eps;
+
+  const size_t smem = (size_t)K * 4 + (size_t)rpc * kGemvWarps * 4 + 128;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_set = true;
+  }
+  cudaError_t e = launch(gemv_kernel, dim3(grid), dim3(kGemvThreads), smem, (cudaStream_t)stream,
+                         (flags & B200_FLAG_PDL) != 0, a);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}

@@ -1,0 +1,307 @@
+"""Batch-1 dense decoder engine (Llama-3.1 / Qwen3 families) on the b200 ops.
+
+Mirrors the reference engines' interface — `capture()`, `step(tok, pos)`,
+`prefill(ids)`, `generate(ids, n_new)` with all buffers allocated up front
+(models/llama31-8b/llama31_optimized.py:317-520, models/qwen3-4b/qwen3_optimized.py:312-517)
+— but with a different dataflow:
+
+decode (6 launches per layer, fp32 activations, one CUDA graph for the whole step)
+    gemv[rmsnorm prologue, packed q|k|v] -> qk_rope_cache -> flash_decode (LSE combine fused)
+    -> gemv[o_proj, + residual] -> gemv[rmsnorm prologue, gate|up interleaved, SwiGLU epilogue]
+    -> gemv[down_proj, + residual];  lm_head gemv (fp32 logits) -> argmax -> greedy_select,
+    which feeds the next step's token and position on the device.
+
+prefill (bf16 activations)
+    add_rmsnorm -> gemm[q|k|v] -> qk_rope_cache -> flash_prefill (reads the cache) ->
+    gemm[o_proj + residual] -> add_rmsnorm -> gemm[gate|up, SwiGLU epilogue] ->
+    gemm[down + residual]; logits for the last position only.
+
+Tensor parallelism (head-sharded, one process per GPU): q/k/v/gate/up are column-sharded,
+o/down row-sharded with an all-reduce after each, lm_head vocabulary-sharded with an
+all-gather of per-rank (max logit, argmax) records.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from . import ops
+from .configs import DecoderConfig
+from .weights import rope_tables
+
+EPI_SWIGLU = ops.EPI_SWIGLU
+
+
+def _interleave_rows(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up -> [2I, K] with row 2j = gate_j and row 2j+1 = up_j."""
+    I, K = gate.shape
+    return torch.stack((gate, up), dim=1).reshape(2 * I, K).contiguous()
+
+
+class DenseDecoder:
+    def __init__(self, cfg: DecoderConfig, weights: Dict[str, torch.Tensor], max_seq: int,
+                 device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None,
+                 n_splits: Optional[int] = None, max_new_tokens: int = 1024,
+                 free_source_weights: bool = False):
+        if cfg.n_experts:
+            raise ValueError("use MoeDecoder for mixture-of-experts configurations")
+        if cfg.n_kv % tp_size or cfg.n_q % tp_size or cfg.inter % tp_size or cfg.vocab % tp_size:
+            raise ValueError("tensor-parallel size must divide heads, intermediate and vocab")
+        self.cfg, self.device, self.max_seq = cfg, torch.device(device), max_seq
+        self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
+        H, hd = cfg.hidden, cfg.head_dim
+        self.n_q, self.n_kv = cfg.n_q // tp_size, cfg.n_kv // tp_size
+        self.q_size, self.kv_size = self.n_q * hd, self.n_kv * hd
+        self.inter = cfg.inter // tp_size
+        self.vocab_local = cfg.vocab // tp_size
+        self.scale = hd ** -0.5
+        r = tp_rank
+        dev = self.device
+
+        def take(name):
+            t = weights.pop(name) if free_source_weights else weights[name]
+            return t
+
+        def rows(t, n_local):  # column-parallel: a contiguous block of output rows
+            return t[r * n_local:(r + 1) * n_local]
+
+        self.embed = take("model.embed_tokens.weight").to(dev)
+        head = self.embed if cfg.tied else take("lm_head.weight").to(dev)
+        self.lm_head = rows(head, self.vocab_local).contiguous() if tp_size > 1 else head
+        self.final_norm_w = take("model.norm.weight").to(dev)
+        self.ln1: List[torch.Tensor] = []
+        self.ln2: List[torch.Tensor] = []
+        self.wqkv: List[torch.Tensor] = []
+        self.wo: List[torch.Tensor] = []
+        self.wgu: List[torch.Tensor] = []
+        self.wd: List[torch.Tensor] = []
+        self.qn: List[Optional[torch.Tensor]] = []
+        self.kn: List[Optional[torch.Tensor]] = []
+        for i in range(cfg.layers):
+            p = f"model.layers.{i}."
+            self.ln1.append(take(p + "input_layernorm.weight").to(dev))
+            self.ln2.append(take(p + "post_attention_layernorm.weight").to(dev))
+            q = rows(take(p + "self_attn.q_proj.weight"), self.q_size)
+            k = rows(take(p + "self_attn.k_proj.weight"), self.kv_size)
+            v = rows(take(p + "self_attn.v_proj.weight"), self.kv_size)
+            self.wqkv.append(torch.cat((q, k, v), dim=0).to(dev).contiguous())
+            o = take(p + "self_attn.o_proj.weight")
+            self.wo.append(o[:, r * self.q_size:(r + 1) * self.q_size].to(dev).contiguous())
+            g = rows(take(p + "mlp.gate_proj.weight"), self.inter)
+            u = rows(take(p + "mlp.up_proj.weight"), self.inter)
+            self.wgu.append(_interleave_rows(g.to(dev), u.to(dev)))
+            d = take(p + "mlp.down_proj.weight")
+            self.wd.append(d[:, r * self.inter:(r + 1) * self.inter].to(dev).contiguous())
+            if cfg.qk_norm:
+                self.qn.append(take(p + "self_attn.q_norm.weight").to(dev))
+                self.kn.append(take(p + "self_attn.k_norm.weight").to(dev))
+            else:
+                self.qn.append(None)
+                self.kn.append(None)
+
+        self.cos, self.sin = rope_tables(cfg, max_seq, dev)
+        # KV cache [layer, k|v, n_kv, max_seq, hd]: the layout cache-write and both attention
+        # kernels share (row = (kv_head * max_seq + pos) * hd)
+        self.kv = torch.zeros(cfg.layers, 2, self.n_kv, max_seq, hd, dtype=torch.bfloat16, device=dev)
+
+        f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
+        # step state on the device: {position, kv_len, generated}; one graph serves every step
+        self.state = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.pos, self.kv_len = self.state[0:1], self.state[1:2]
+        self.tok = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.tok_log = torch.zeros(max_new_tokens, dtype=torch.int32, device=dev)
+        self.h, self.h2 = f32(H), f32(H)
+        self.qkv = f32(self.q_size + 2 * self.kv_size)
+        self.q = f32(self.q_size)
+        self.attn = f32(self.q_size)
+        self.act = f32(self.inter)
+        self.logits = f32(self.vocab_local)
+        self.cand = f32(2)
+        self.cand_all = f32(tp_size, 2)
+        if n_splits is None:
+            n_splits = max(1, min((4 * 148) // self.n_kv, (max_seq + 63) // 64))
+        self.n_splits = n_splits
+        self.fd_ws = ops.flash_decode_workspace(self.n_q, self.n_kv, hd, n_splits, dev)
+        self.am_ws = ops.argmax_workspace(dev)
+        self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 1 + 6 * cfg.layers + 3
+
+    # ------------------------------------------------------------------ collectives
+    def _all_reduce(self, t: torch.Tensor) -> None:
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+
+    # ------------------------------------------------------------------ decode
+    def step_static(self, collect: Optional[list] = None) -> None:
+        """One decode step for the token in self.tok at position self.pos (device state).
+        `collect` (eager only) receives a copy of the residual stream after every layer."""
+        cfg = self.cfg
+        tp = self.tp_size > 1
+        lead = self.tp_rank == 0
+        ops.embed_gather(self.h, self.embed, self.tok)
+        h, h2 = self.h, self.h2
+        for i in range(cfg.layers):
+            ops.gemv(self.qkv, h, self.wqkv[i], norm_w=self.ln1[i], eps=cfg.eps)
+            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
+                              self.pos, self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i],
+                              kn_w=self.kn[i])
+            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
+                             self.fd_ws, self.n_q, self.n_kv, self.n_splits, self.scale)
+            if tp:
+                ops.gemv(h2, self.attn, self.wo[i], resid=h if lead else None)
+                self._all_reduce(h2)
+                h, h2 = h2, h
+            else:
+                ops.gemv(h, self.attn, self.wo[i], resid=h)
+            ops.gemv(self.act, h, self.wgu[i], norm_w=self.ln2[i], eps=cfg.eps, epilogue=EPI_SWIGLU)
+            if tp:
+                ops.gemv(h2, self.act, self.wd[i], resid=h if lead else None)
+                self._all_reduce(h2)
+                h, h2 = h2, h
+            else:
+                ops.gemv(h, self.act, self.wd[i], resid=h)
+            if collect is not None:
+                collect.append(h.clone())
+        ops.gemv(self.logits, h, self.lm_head, norm_w=self.final_norm_w, eps=cfg.eps)
+        ops.argmax(self.cand, self.logits, self.am_ws, idx_base=self.tp_rank * self.vocab_local)
+        if tp:
+            torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2),
+                                                     group=self.group)
+            ops.greedy_select(self.tok, self.cand_all, self.state, self.tok_log)
+        else:
+            ops.greedy_select(self.tok, self.cand, self.state, self.tok_log)
+        # an even number of buffer swaps per layer keeps the residual stream in self.h
+
+    def capture(self, warmup: int = 3) -> None:
+        """Warm up on a side stream, then record step_static into one CUDA graph.  The step state
+        lives on the device, so the same graph replays at every position."""
+        saved = (self.state.clone(), self.tok.clone(), self.tok_log.clone(), self.kv[:, :, :, :warmup + 1].clone())
+        self.state.zero_()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(warmup):
+                self.step_static()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.state.zero_()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.step_static()
+        torch.cuda.synchronize()
+        self.state.copy_(saved[0]); self.tok.copy_(saved[1]); self.tok_log.copy_(saved[2])
+        self.kv[:, :, :, :warmup + 1].copy_(saved[3])
+
+    def set_step(self, tok: int, pos: int, generated: int = 0) -> None:
+        self.tok.fill_(tok)
+        self.state.copy_(torch.tensor([pos, pos + 1, generated, 0], dtype=torch.int32),
+                         non_blocking=False)
+
+    def step(self, tok: int, pos: int) -> torch.Tensor:
+        """Reference-style host-driven step: returns this rank's logits."""
+        self.set_step(tok, pos)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step_static()
+        return self.logits
+
+    # ------------------------------------------------------------------ prefill
+    def _prefill_buffers(self, P: int) -> Dict[str, torch.Tensor]:
+        if P not in self._pbuf:
+            bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=self.device)
+            H = self.cfg.hidden
+            self._pbuf[P] = {
+                "ids": torch.zeros(P, dtype=torch.int32, device=self.device),
+                "x": bf(P, H), "hn": bf(P, H), "part": bf(P, H),
+                "qkv": bf(P, self.q_size + 2 * self.kv_size), "q": bf(P, self.q_size),
+                "att": bf(P, self.q_size), "act": bf(P, self.inter),
+                "pos0": torch.zeros(1, dtype=torch.int32, device=self.device),
+                "last": torch.zeros(H, dtype=torch.float32, device=self.device),
+            }
+        return self._pbuf[P]
+
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor, collect: Optional[list] = None) -> int:
+        """Runs the prompt, fills the KV cache and returns the first generated token.
+        `collect` receives a copy of the residual stream after every layer."""
+        cfg = self.cfg
+        P = ids.numel()
+        if P + 1 > self.max_seq:
+            raise ValueError("prompt too long for this cache")
+        e = self._prefill_buffers(P)
+        e["ids"].copy_(ids.to(torch.int32))
+        tp = self.tp_size > 1
+        hd = cfg.head_dim
+        x, hn, part = e["x"], e["hn"], e["part"]
+        ops.embed_gather(x, self.embed, e["ids"])
+        ops.add_rmsnorm(hn, x, self.ln1[0], cfg.eps)
+        for i in range(cfg.layers):
+            kc, vc = self.kv[i, 0], self.kv[i, 1]
+            ops.gemm(e["qkv"], hn, self.wqkv[i])
+            ops.qk_rope_cache(e["q"], kc, vc, e["qkv"], self.cos, self.sin, e["pos0"],
+                              self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i], kn_w=self.kn[i])
+            ops.flash_prefill(e["att"].view(1, P, self.n_q, hd), e["q"].view(1, P, self.n_q, hd),
+                              kc.unsqueeze(0), vc.unsqueeze(0), P, True, self.scale)
+            if tp:
+                ops.gemm(part, e["att"], self.wo[i])
+                self._all_reduce(part)
+                ops.add_rmsnorm(hn, x, self.ln2[i], cfg.eps, b=part, resid_out=x)
+            else:
+                ops.gemm(x, e["att"], self.wo[i], resid=x)
+                ops.add_rmsnorm(hn, x, self.ln2[i], cfg.eps)
+            ops.gemm(e["act"], hn, self.wgu[i], epilogue=EPI_SWIGLU)
+            nw = self.ln1[i + 1] if i + 1 < cfg.layers else self.final_norm_w
+            if tp:
+                ops.gemm(part, e["act"], self.wd[i])
+                self._all_reduce(part)
+                ops.add_rmsnorm(hn, x, nw, cfg.eps, b=part, resid_out=x)
+            else:
+                ops.gemm(x, e["act"], self.wd[i], resid=x)
+                ops.add_rmsnorm(hn, x, nw, cfg.eps)
+            if collect is not None:
+                collect.append(x.clone())
+        # hn now holds the final-norm output; project the last position only
+        ops.gemv(self.logits, hn[P - 1], self.lm_head)
+        ops.argmax(self.cand, self.logits, self.am_ws, idx_base=self.tp_rank * self.vocab_local)
+        if tp:
+            torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2),
+                                                     group=self.group)
+            ops.greedy_select(self.tok, self.cand_all)
+        else:
+            ops.greedy_select(self.tok, self.cand)
+        self.last_prefill_hidden = x
+        return int(self.tok.item())
+
+    # ------------------------------------------------------------------ generation
+    @torch.no_grad()
+    def generate(self, ids: torch.Tensor, n_new: int, sync_every_step: bool = False) -> List[int]:
+        """Greedy generation.  The decode loop replays one graph per token; token selection and
+        position bookkeeping stay on the device, so the host reads the tokens once at the end
+        (or every step with sync_every_step, the reference's behaviour)."""
+        P = ids.numel()
+        if n_new > self.tok_log.numel() + 1:
+            raise ValueError("n_new exceeds max_new_tokens")
+        first = self.prefill(ids)
+        out = [first]
+        self.set_step(first, P, 0)
+        if self.graph is None:
+            self.capture()
+            self.set_step(first, P, 0)
+        for _ in range(n_new - 1):
+            self.graph.replay()
+            if sync_every_step:
+                out.append(int(self.tok.item()))
+        if not sync_every_step:
+            out.extend(self.tok_log[:n_new - 1].tolist())
+        return out
+
+
+class Llama31Optimized(DenseDecoder):
+    """Drop-in for the reference's Llama31Optimized (models/llama31-8b/llama31_optimized.py:317)."""
+
+
+class Qwen3Optimized(DenseDecoder):
+    """Drop-in for the reference's Qwen3Optimized (models/qwen3-4b/qwen3_optimized.py:312)."""

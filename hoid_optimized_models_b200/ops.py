@@ -1,0 +1,284 @@
+"""torch custom ops `b200::<op>` over the C ABI.
+
+Every op is out-parameter style (the caller owns all buffers, as in the
+reference engines: models/llama31-8b/llama31_optimized.py:347-376), launches on
+the current torch stream, allocates nothing and is safe inside
+`torch.cuda.graph` capture.  The ops keep the reference's module boundaries
+(norm, prepare_qkv, decode attention, GEMV, ...), see include/b200ops.h.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import BF16, F32, FLAG_PDL, EPI_NONE, EPI_SWIGLU, EPI_GELU, check
+
+Tensor = torch.Tensor
+
+_PDL = False
+
+
+def set_pdl(enabled: bool) -> None:
+    """Enable programmatic dependent launch on every op launched afterwards."""
+    global _PDL
+    _PDL = bool(enabled)
+
+
+def _flags() -> int:
+    return FLAG_PDL if _PDL else 0
+
+
+def _dt(t: Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return BF16
+    if t.dtype == torch.float32:
+        return F32
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _ptr(t: Optional[Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("b200 ops take CUDA tensors only (there is no CPU path)")
+    if not t.is_contiguous():
+        raise RuntimeError("b200 ops take contiguous tensors")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _bf16(t: Optional[Tensor], name: str) -> None:
+    if t is not None and t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16")
+
+
+# ----------------------------------------------------------------------------- GEMV
+@torch.library.custom_op("b200::gemv", mutates_args=("y",))
+def gemv(y: Tensor, x: Tensor, w: Tensor, norm_w: Optional[Tensor] = None, eps: float = 0.0,
+         bias: Optional[Tensor] = None, resid: Optional[Tensor] = None,
+         epilogue: int = EPI_NONE) -> None:
+    """y = W x with optional RMSNorm prologue, bias, residual and SwiGLU/GELU epilogue.
+    w is the HuggingFace [N, K] weight; x is [K] or [1, K]."""
+    _bf16(w, "w"); _bf16(norm_w, "norm_w"); _bf16(bias, "bias")
+    N, K = w.shape
+    if x.numel() != K:
+        raise RuntimeError(f"x has {x.numel()} elements, expected {K}")
+    n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    if y.numel() != n_out:
+        raise RuntimeError(f"y has {y.numel()} elements, expected {n_out}")
+    check(_lib.lib().b200_gemv_bf16(
+        _ptr(x), _dt(x), _ptr(w), _ptr(y), _dt(y), K, N, w.stride(0),
+        _ptr(norm_w), eps, _ptr(bias), _ptr(resid), _dt(resid) if resid is not None else 0,
+        epilogue, _flags(), _stream()), "b200_gemv_bf16")
+
+
+# ----------------------------------------------------------------------------- norms
+@torch.library.custom_op("b200::add_rmsnorm", mutates_args=("resid_out", "norm_out"))
+def add_rmsnorm(norm_out: Tensor, a: Tensor, w: Tensor, eps: float, b: Optional[Tensor] = None,
+                resid_out: Optional[Tensor] = None) -> None:
+    """norm_out = rmsnorm(a (+ b)) * w; resid_out (optional) receives a + b."""
+    _bf16(w, "w")
+    N = w.numel()
+    rows = a.numel() // N
+    if b is not None and b.dtype != a.dtype:
+        raise TypeError("a and b must share a dtype")
+    if resid_out is not None and resid_out.dtype != norm_out.dtype:
+        raise TypeError("resid_out and norm_out must share a dtype")
+    check(_lib.lib().b200_add_rmsnorm(
+        _ptr(resid_out), _ptr(norm_out), _dt(norm_out), _ptr(a), _ptr(b), _dt(a), _ptr(w),
+        rows, N, eps, _flags(), _stream()), "b200_add_rmsnorm")
+
+
+@torch.library.custom_op("b200::add_layernorm", mutates_args=("resid_out", "norm_out"))
+def add_layernorm(norm_out: Tensor, x: Tensor, gamma: Tensor, beta: Tensor, eps: float,
+                  bias: Optional[Tensor] = None, resid: Optional[Tensor] = None,
+                  resid_out: Optional[Tensor] = None) -> None:
+    """norm_out = LayerNorm(x (+ bias) (+ resid)); resid_out (optional) receives the sum."""
+    _bf16(gamma, "gamma"); _bf16(beta, "beta"); _bf16(bias, "bias")
+    N = gamma.numel()
+    rows = x.numel() // N
+    if resid is not None and resid.dtype != x.dtype:
+        raise TypeError("x and resid must share a dtype")
+    check(_lib.lib().b200_add_layernorm(
+        _ptr(resid_out), _ptr(norm_out), _dt(norm_out), _ptr(x), _ptr(bias), _ptr(resid), _dt(x),
+        _ptr(gamma), _ptr(beta), rows, N, eps, _flags(), _stream()), "b200_add_layernorm")
+
+
+# ----------------------------------------------------------------------------- rope + cache
+@torch.library.custom_op("b200::qk_rope_cache", mutates_args=("q_out", "kcache", "vcache"))
+def qk_rope_cache(q_out: Tensor, kcache: Tensor, vcache: Tensor, qkv: Tensor, cos: Tensor,
+                  sin: Tensor, pos: Tensor, n_q: int, n_kv: int, eps: float = 0.0,
+                  qn_w: Optional[Tensor] = None, kn_w: Optional[Tensor] = None) -> None:
+    """(QK-RMSNorm +) RoPE on the packed q|k|v rows; q -> q_out, k/v -> cache rows pos + t.
+    kcache / vcache are [n_kv, max_seq, hd] bf16; pos is a device int32 scalar tensor."""
+    _bf16(kcache, "kcache"); _bf16(vcache, "vcache"); _bf16(qn_w, "qn_w"); _bf16(kn_w, "kn_w")
+    hd = kcache.shape[-1]
+    max_seq = kcache.shape[-2]
+    s = qkv.numel() // ((n_q + 2 * n_kv) * hd)
+    if pos.dtype != torch.int32 or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+        raise TypeError("pos must be int32 and cos/sin float32")
+    if cos.shape[0] < max_seq or cos.shape[-1] != hd // 2:
+        raise RuntimeError("cos/sin tables must be [>= max_seq, hd/2]")
+    check(_lib.lib().b200_qk_rope_cache(
+        _ptr(q_out), _dt(q_out), _ptr(kcache), _ptr(vcache), _ptr(qkv), _dt(qkv),
+        _ptr(qn_w), _ptr(kn_w), _ptr(cos), _ptr(sin), _ptr(pos), s, n_q, n_kv, hd, max_seq,
+        eps, _flags(), _stream()), "b200_qk_rope_cache")
+
+
+# ----------------------------------------------------------------------------- flash decode
+def flash_decode_workspace(n_q: int, n_kv: int, hd: int, n_splits: int, device) -> Tensor:
+    """Zero-initialised scratch for `flash_decode` (arrival counters + split records)."""
+    nbytes = _lib.lib().b200_flash_decode_workspace_bytes(n_q, n_kv, hd, n_splits)
+    return torch.zeros((nbytes + 3) // 4, dtype=torch.float32, device=device)
+
+
+@torch.library.custom_op("b200::flash_decode", mutates_args=("out", "workspace"))
+def flash_decode(out: Tensor, q: Tensor, kcache: Tensor, vcache: Tensor, kv_len: Tensor,
+                 workspace: Tensor, n_q: int, n_kv: int, n_splits: int, scale: float,
+                 kv_head_stride: int = -1, kv_row_stride: int = -1) -> None:
+    """out[n_q, hd] = softmax(q K^T * scale) V over the first kv_len cache rows of each kv head.
+    Default strides describe a contiguous [n_kv, max_seq, hd] cache."""
+    _bf16(kcache, "kcache"); _bf16(vcache, "vcache")
+    hd = q.numel() // n_q
+    if kv_row_stride < 0:
+        kv_row_stride = kcache.stride(-2)
+    if kv_head_stride < 0:
+        kv_head_stride = kcache.stride(-3) if kcache.dim() >= 3 else hd
+    if kv_len.dtype != torch.int32:
+        raise TypeError("kv_len must be int32")
+    need = _lib.lib().b200_flash_decode_workspace_bytes(n_q, n_kv, hd, n_splits)
+    if workspace.numel() * workspace.element_size() < need:
+        raise RuntimeError("flash_decode workspace too small")
+    check(_lib.lib().b200_flash_decode(
+        _ptr(out), _dt(out), _ptr(q), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(kv_len),
+        _ptr(workspace), n_q, n_kv, hd, kv_head_stride, kv_row_stride, n_splits, scale,
+        _flags(), _stream()), "b200_flash_decode")
+
+
+# ----------------------------------------------------------------------------- GEMM
+_STATUS = {}
+
+
+def status_word(device) -> Tensor:
+    """Device int32 that tensor-core kernels set to B200_ERR_TIMEOUT if a bounded wait expires."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device) -> None:
+    """Synchronising check of the status word (tests and debugging only)."""
+    v = int(status_word(device).item())
+    if v != 0:
+        status_word(device).zero_()
+        check(v, "tensor-core kernel (device status)")
+
+
+@torch.library.custom_op("b200::gemm", mutates_args=("y",))
+def gemm(y: Tensor, x: Tensor, w: Tensor, bias: Optional[Tensor] = None,
+         resid: Optional[Tensor] = None, epilogue: int = EPI_NONE) -> None:
+    """y[M, N] = x[M, K] w[N, K]^T (+ bias) (+ resid) with optional SwiGLU / GELU epilogue."""
+    for t, n in ((y, "y"), (x, "x"), (w, "w"), (bias, "bias"), (resid, "resid")):
+        _bf16(t, n)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise RuntimeError("x / w inner dimensions differ")
+    n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    if y.shape[0] != M or y.shape[1] != n_out:
+        raise RuntimeError(f"y must be [{M}, {n_out}]")
+    if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
+        raise RuntimeError("innermost dimensions must be contiguous")
+    check(_lib.lib().b200_gemm_bf16(
+        x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0), w.stride(0), y.stride(0),
+        _ptr(bias), resid.data_ptr() if resid is not None else None,
+        resid.stride(0) if resid is not None else 0, epilogue,
+        status_word(x.device).data_ptr(), _flags(), _stream()), "b200_gemm_bf16")
+
+
+@torch.library.custom_op("b200::moe_grouped_gemm", mutates_args=("y",))
+def moe_grouped_gemm(y: Tensor, x: Tensor, w: Tensor, offsets: Tensor,
+                     epilogue: int = EPI_NONE) -> None:
+    """y[r] = x[r] w[e(r)]^T for rows sorted by expert; offsets is int32 [E + 1]; w is [E, N, K]."""
+    for t, n in ((y, "y"), (x, "x"), (w, "w")):
+        _bf16(t, n)
+    E, N, K = w.shape
+    rows = x.shape[0]
+    if offsets.dtype != torch.int32 or offsets.numel() != E + 1:
+        raise TypeError("offsets must be int32 [E + 1]")
+    check(_lib.lib().b200_moe_grouped_gemm(
+        _ptr(x), _ptr(w), _ptr(y), _ptr(offsets), E, rows, N, K, x.stride(0), y.stride(0),
+        epilogue, status_word(x.device).data_ptr(), _flags(), _stream()), "b200_moe_grouped_gemm")
+
+
+# ----------------------------------------------------------------------------- flash prefill
+@torch.library.custom_op("b200::flash_prefill", mutates_args=("out",))
+def flash_prefill(out: Tensor, q: Tensor, k: Tensor, v: Tensor, kv_len: int, causal: bool,
+                  scale: float, q_pos0: int = 0) -> None:
+    """Flash attention over strided views.
+
+    q / out: [B, S, n_q, hd] views; k / v: [B, n_kv, L, hd] views (any strides with a
+    contiguous last dimension), attending to the first kv_len of L keys.  A decode cache
+    [n_kv, max_seq, hd] is passed as cache.unsqueeze(0)."""
+    for t, n in ((out, "out"), (q, "q"), (k, "k"), (v, "v")):
+        _bf16(t, n)
+        if t.stride(-1) != 1:
+            raise RuntimeError("last dimension must be contiguous")
+    B, S, n_q, hd = q.shape
+    n_kv = k.shape[1]
+    check(_lib.lib().b200_flash_prefill(
+        out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, kv_len, q_pos0, n_q, n_kv,
+        hd, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(2), k.stride(1),
+        v.stride(0), v.stride(2), v.stride(1), out.stride(0), out.stride(1), out.stride(2),
+        1 if causal else 0, scale, _flags(), _stream()), "b200_flash_prefill")
+
+
+# ----------------------------------------------------------------------------- small ops
+@torch.library.custom_op("b200::embed_gather", mutates_args=("out",))
+def embed_gather(out: Tensor, table: Tensor, ids: Tensor) -> None:
+    _bf16(table, "table")
+    if ids.dtype != torch.int32:
+        raise TypeError("ids must be int32")
+    check(_lib.lib().b200_embed_gather(_ptr(out), _dt(out), _ptr(table), _ptr(ids), ids.numel(),
+                                       table.shape[1], _flags(), _stream()), "b200_embed_gather")
+
+
+@torch.library.custom_op("b200::silu_mul", mutates_args=("out",))
+def silu_mul(out: Tensor, gate: Tensor, up: Tensor) -> None:
+    _bf16(out, "out"); _bf16(gate, "gate"); _bf16(up, "up")
+    check(_lib.lib().b200_silu_mul(_ptr(out), _ptr(gate), _ptr(up), gate.numel(), _flags(),
+                                   _stream()), "b200_silu_mul")
+
+
+def argmax_workspace(device) -> Tensor:
+    nbytes = _lib.lib().b200_argmax_workspace_bytes(0)
+    return torch.zeros((nbytes + 3) // 4, dtype=torch.int32, device=device)
+
+
+@torch.library.custom_op("b200::argmax", mutates_args=("cand", "workspace"))
+def argmax(cand: Tensor, logits: Tensor, workspace: Tensor, idx_base: int = 0) -> None:
+    """cand (float32 [2]) = {max logit, bit pattern of int32 argmax + idx_base}; lowest index
+    wins ties.  `cand.view(torch.int32)[1]` is the token id."""
+    if logits.dtype != torch.float32 or cand.dtype != torch.float32 or cand.numel() != 2:
+        raise TypeError("argmax takes float32 logits and a float32 [2] candidate record")
+    base = _ptr(cand)
+    check(_lib.lib().b200_argmax_f32(base + 4, base, _ptr(logits), logits.numel(), idx_base,
+                                     _ptr(workspace), _flags(), _stream()), "b200_argmax_f32")
+
+
+@torch.library.custom_op("b200::greedy_select", mutates_args=("tok_out", "state", "log"))
+def greedy_select(tok_out: Tensor, cand: Tensor, state: Optional[Tensor] = None,
+                  log: Optional[Tensor] = None) -> None:
+    """tok_out[0] = index of the best of the candidate records in cand (float32 [n, 2]);
+    appends it to log and advances state = {position, kv_len, generated} (int32 [3+])."""
+    if tok_out.dtype != torch.int32 or cand.dtype != torch.float32:
+        raise TypeError("greedy_select takes an int32 token and float32 candidates")
+    check(_lib.lib().b200_greedy_select(_ptr(tok_out), _ptr(cand), cand.numel() // 2, _ptr(state),
+                                        _ptr(log), log.numel() if log is not None else 0,
+                                        _flags(), _stream()), "b200_greedy_select")

@@ -1,0 +1,224 @@
+/*
+ * b200ops — C ABI of the sm_100a inference kernel library.
+ *
+ * Every entry point:
+ *   - takes plain device pointers, explicit sizes and an explicit stream;
+ *   - writes only into caller-provided buffers (nothing is allocated, nothing
+ *     synchronises, so every call can sit inside a CUDA-graph capture);
+ *   - returns B200_OK or a negative B200_ERR_* code (bad shape / alignment /
+ *     launch failure) and never throws.
+ *
+ * "Reference" citations name the file of hoid-ai/hoid-optimized-models whose
+ * kernel or library call the entry point replaces (path within that project).
+ *
+ * Conventions: bf16 tensors are raw uint16 storage; `*_dtype` arguments use
+ * B200_BF16 / B200_F32; weight matrices are row-major [N, K] exactly as the
+ * HuggingFace checkpoints store them (y = x W^T).  Positions / lengths that
+ * change from step to step are read from DEVICE scalars so that one captured
+ * graph serves every step (the reference's dyn_dims[14] / dyn_dims[18]).
+ */
+#ifndef B200OPS_H_
+#define B200OPS_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* b200_stream_t;
+
+enum { B200_BF16 = 0, B200_F32 = 1 };
+
+enum {
+  B200_OK = 0,
+  B200_ERR_SHAPE = -1,     /* unsupported size / divisibility */
+  B200_ERR_ALIGN = -2,     /* pointer or leading dimension not 16-byte aligned */
+  B200_ERR_LAUNCH = -3,    /* CUDA reported a launch error */
+  B200_ERR_ARG = -4,       /* null pointer / bad enum */
+  B200_ERR_TIMEOUT = -5,   /* a bounded device-side wait expired (status word) */
+  B200_ERR_DRIVER = -6     /* driver entry point (tensor-map encode) unavailable */
+};
+
+/* launch flags */
+enum {
+  B200_FLAG_PDL = 1        /* launch with programmatic stream serialization */
+};
+
+/* GEMV / GEMM epilogues */
+enum {
+  B200_EPI_NONE = 0,
+  B200_EPI_SWIGLU = 1,     /* rows interleaved (gate_j, up_j): out[j] = silu(y[2j]) * y[2j+1] */
+  B200_EPI_GELU = 2        /* exact erf GELU on (y + bias) */
+};
+
+int b200_version(void);
+/* Number of SMs the library sizes its grids for (148 on B200). */
+int b200_sm_count(void);
+
+/* ---------------------------------------------------------------------------
+ * a1. Decode GEMV  y[N] = W[N,K] . x[K]   (bf16 weights, fp32 accumulate)
+ * Reference: torch.matmul(h, W.t(), out=) at models/llama31-8b/llama31_optimized.py:391-418,
+ * models/qwen3-4b/qwen3_optimized.py:391-419, models/qwen3-30b-a3b/qwen3_optimized.py:472-494,
+ * models/whisper-large-v3/whisper_decoder_optimized.py:416-447 and the fused q/k/v GEMV
+ * models/whisper-large-v3/kernels/whisper_qkv_prefetch10_raw_b128_k.cu:2-21.
+ *
+ * Optional fusions (pass NULL to disable):
+ *   norm_w  : RMSNorm prologue, x <- x * rsqrt(mean(x^2) + eps) * norm_w   (bf16 [K])
+ *             (replaces models/llama31-8b/kernels/rmsnorm_prefetch16_k.cu:4-22 at s = 1)
+ *   bias    : bf16 [N] added to y
+ *   resid   : y = resid + W x; may alias y (replaces kernels/add_bf16_vec8_k.cu:10-21)
+ *   epilogue: B200_EPI_SWIGLU over interleaved gate/up rows, output length N/2
+ *             (replaces kernels/silu_mul_vec8_fast_k.cu:12-23), or B200_EPI_GELU.
+ * K must be a multiple of 256; w rows 16-byte aligned (ldw % 8 == 0).
+ */
+int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y, int y_dtype,
+                   int K, int N, int ldw,
+                   const void* norm_w, float eps,
+                   const void* bias,
+                   const void* resid, int resid_dtype,
+                   int epilogue, int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * a6. (residual add +) RMSNorm over rows.
+ *   sum = a (+ b)                       [rows, N]
+ *   resid_out <- sum (optional, rounded to its dtype first, as the reference does)
+ *   norm_out  <- sum * rsqrt(mean(sum^2) + eps) * w
+ * Reference: models/qwen3-4b/kernels/fused_residual_rmsnorm_multi_k.cu:2-54,
+ * models/qwen3-30b-a3b/kernels/fullcta_add_rmsnorm_k.cu:2-45,
+ * models/llama31-8b/kernels/rmsnorm_prefetch16_k.cu:4-22 (b = NULL).
+ * N % 8 == 0, N <= 16384.
+ */
+int b200_add_rmsnorm(void* resid_out, void* norm_out, int out_dtype,
+                     const void* a, const void* b, int in_dtype,
+                     const void* w, int rows, int N, float eps,
+                     int flags, b200_stream_t stream);
+
+/* (bias +) (residual add +) LayerNorm over rows, two-pass fp32 statistics.
+ *   sum = x (+ bias) (+ resid); with in_dtype bf16 each addition is rounded to bf16 like the reference
+ *   resid_out <- sum (optional); norm_out <- (sum - mean) * rsqrt(var + eps) * gamma + beta
+ * Reference: models/bge-m3/kernels/bge_bias_residual_ln_warp_packed_k.cu:2-67,
+ * models/whisper-large-v3/kernels/whisper_ordered_residual_ln_replicated_k.cu:32-111,
+ * whisper_resid_ln_oneshot_vec2_k.cu:2-24, whisper_ln_volatile_warptail_k.cu:6-75.
+ */
+int b200_add_layernorm(void* resid_out, void* norm_out, int out_dtype,
+                       const void* x, const void* bias, const void* resid, int in_dtype,
+                       const void* gamma, const void* beta,
+                       int rows, int N, float eps, int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * a7. (QK-RMSNorm +) RoPE + KV-cache write for `s` new tokens.
+ *   qkv      : [s, (n_q + 2 n_kv) * hd] packed projections (q heads, k heads, v heads)
+ *   q_out    : [s, n_q * hd]
+ *   kcache / vcache : [n_kv, max_seq, hd] bf16; rows pos0 + t are written
+ *   qn_w/kn_w: optional bf16 [hd] per-head RMSNorm weights (Qwen3)
+ *   cos/sin  : fp32 [max_seq, hd/2]; rotate-half convention
+ *   pos_dev  : device int32, position of the first new token
+ * Reference: models/qwen3-4b/qwen3_native_gen.py:16-92 (prepare_qkv_k),
+ * models/qwen3-30b-a3b/kernels/prepare_qkv_k.cu:5-76,
+ * models/llama31-8b/llama31_native_gen.py:30-110 (apply_rope_q_k, apply_rope_kv_k, cache_write_k).
+ */
+int b200_qk_rope_cache(void* q_out, int q_dtype, void* kcache, void* vcache,
+                       const void* qkv, int qkv_dtype,
+                       const void* qn_w, const void* kn_w,
+                       const float* cos_t, const float* sin_t,
+                       const int* pos_dev, int s, int n_q, int n_kv, int hd,
+                       int max_seq, float eps, int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * a3 + a4. Split-KV GQA flash-decode with the log-sum-exp combine fused in.
+ *   q      : [n_q, hd]; head h uses kv head h / (n_q / n_kv)
+ *   kcache : element (kvh, j, d) at kcache[kvh * kv_head_stride + j * kv_row_stride + d]
+ *   kv_len_dev : device int32, number of keys to attend to (position + 1)
+ *   workspace  : fp32 scratch of b200_flash_decode_workspace_bytes() bytes; its first
+ *                n_kv int32 words are arrival counters that must be zero before the
+ *                first call (the kernel leaves them zero).
+ *   n_splits   : CTAs per kv head (fixed at capture time; idle splits exit early)
+ * Reference: models/llama31-8b/kernels/dense_cached_attention_residue_partial_k.cu:19-124 and
+ * dense_cached_attention_residue_combine_k.cu:7-36;
+ * models/qwen3-30b-a3b/kernels/attn_gqa8_subsplit64_partial_k.cu:2-68 with its three reduce
+ * kernels; models/whisper-large-v3/kernels/whisper_cross_bias_partial.triton.py:1-25.
+ * hd in {64, 128}; n_q / n_kv in {1, 2, 4, 8}.
+ */
+int64_t b200_flash_decode_workspace_bytes(int n_q, int n_kv, int hd, int n_splits);
+int b200_flash_decode(void* out, int out_dtype, const void* q, int q_dtype,
+                      const void* kcache, const void* vcache, const int* kv_len_dev,
+                      void* workspace, int n_q, int n_kv, int hd,
+                      int64_t kv_head_stride, int64_t kv_row_stride,
+                      int n_splits, float scale, int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * a2. Prefill / encoder GEMM  Y[M,N] = X[M,K] W[N,K]^T  (bf16 in, fp32 accumulate in
+ * tensor memory, bf16 out) on tcgen05 tensor cores fed by TMA.
+ *   bias  : optional bf16 [N];  resid : optional bf16 [M, ldr], Y = resid + X W^T (may alias y)
+ *   epilogue: B200_EPI_SWIGLU (W rows interleaved gate/up, Y is [M, N/2]) or B200_EPI_GELU
+ *   status: optional device int32; receives B200_ERR_TIMEOUT if a bounded wait expired
+ * Reference: torch.matmul at M = P, models/llama31-8b/llama31_optimized.py:479-499;
+ * torch.mm(out=) models/bge-m3/bge_optimized.py:340-349; the CuTe-DSL GEMMs
+ * models/whisper-large-v3/kernels/fc1_persistent_exact_gelu_entry.cutedsl.py:173-759,
+ * triple_qkv_entry.cutedsl.py:150-804, conv2_blackwell_efc_bias_entry.cutedsl.py:1-42.
+ * K % 8 == 0, N % 8 == 0 (N % 16 for SwiGLU), all leading dimensions % 8 == 0.
+ */
+int b200_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K,
+                   int ldx, int ldw, int ldy, const void* bias, const void* resid, int ldr,
+                   int epilogue, int* status, int flags, b200_stream_t stream);
+
+/* a11. Grouped expert GEMM: rows of x are sorted by expert, offsets[e] (device int32
+ * [n_experts + 1]) is the first row of expert e, w is [n_experts, N, K]:
+ *   y[r, :] = x[r, :] w[e(r)]^T   (+ SwiGLU over interleaved gate/up rows)
+ * Reference: torch._grouped_mm, models/qwen3-30b-a3b/qwen3_optimized.py:583-585.
+ */
+int b200_moe_grouped_gemm(const void* x, const void* w, void* y, const int* offsets,
+                          int n_experts, int rows, int N, int K, int ldx, int ldy,
+                          int epilogue, int* status, int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * a5. Prefill / encoder flash attention (never materialises the score matrix).
+ *   q, k, v, out are bf16 with explicit element strides (batch, row, head); query row i of
+ *   head h uses kv head h / (n_q / n_kv); causal: row i sees keys <= q_pos0 + i;
+ *   kv_len keys are valid.  The strides let K/V be read straight from the decode cache
+ *   ([n_kv, max_seq, hd]: row stride hd, head stride max_seq * hd) or from a packed
+ *   q|k|v projection (encoder).
+ * Reference: models/llama31-8b/kernels/fmha_prefill_elastic.triton.py:1-58 (causal GQA),
+ * models/bge-m3/kernels/bge_fa2_attention_nokb_postvb_late.ptx:1-2329 (bidirectional d64),
+ * flash-attn-4 call at models/whisper-large-v3/whisper_optimized.py:356-360.
+ * hd in {64, 128}; all strides multiples of 8 elements.
+ */
+int b200_flash_prefill(void* out, const void* q, const void* k, const void* v,
+                       int batch, int S, int kv_len, int q_pos0, int n_q, int n_kv, int hd,
+                       int64_t q_bs, int64_t q_rs, int64_t q_hs,
+                       int64_t k_bs, int64_t k_rs, int64_t k_hs,
+                       int64_t v_bs, int64_t v_rs, int64_t v_hs,
+                       int64_t o_bs, int64_t o_rs, int64_t o_hs,
+                       int causal, float scale, int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * a8 / a12 small ops.
+ */
+/* out[r, :] = table[ids[r], :]  (bf16 table; out bf16 or fp32).
+ * Reference: embedding_k, models/llama31-8b/llama31_native_gen.py:17-27. */
+int b200_embed_gather(void* out, int out_dtype, const void* table, const int* ids,
+                      int rows, int H, int flags, b200_stream_t stream);
+/* out = silu(gate) * up, elementwise over n values (bf16).
+ * Reference: models/llama31-8b/kernels/silu_mul_vec8_fast_k.cu:12-23. */
+int b200_silu_mul(void* out, const void* gate, const void* up, int64_t n,
+                  int flags, b200_stream_t stream);
+/* Greedy head: idx_out[0] = argmax(logits[0:n]) (lowest index on ties), fp32 logits.
+ * Reference: logits.argmax() on the host side, models/llama31-8b/llama31_optimized.py:517-518. */
+/* workspace: b200_argmax_workspace_bytes() bytes, first word zero before the first call
+ * (the kernel leaves it zero); max_out (nullable) receives the winning logit; idx_base is
+ * added to the index (vocabulary shard offset). */
+int b200_argmax_f32(int* idx_out, float* max_out, const float* logits, int n, int idx_base,
+                    void* workspace, int flags, b200_stream_t stream);
+/* On-device greedy step: cand is n records {float value; int32 index} (one per tensor-parallel
+ * rank); the best (highest value, lowest index on ties) becomes tok_out[0], is appended to
+ * log[state[2]] and state = {position, kv_len, generated} is advanced by one.  Removes the
+ * per-token host round trip of models/llama31-8b/llama31_optimized.py:438-442,517-518. */
+int b200_greedy_select(int* tok_out, const void* cand, int n, int* state, int* log, int log_cap,
+                       int flags, b200_stream_t stream);
+int64_t b200_argmax_workspace_bytes(int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200OPS_H_ */
