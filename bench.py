@@ -161,6 +161,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--ttft-runs", type=int, default=3)
+    ap.add_argument("--skip-prefill", action="store_true",
+                    help="profiling aid: random KV cache instead of a prefill, decode timing only")
     args = ap.parse_args()
 
     from hoid_optimized_models_b200.configs import LLAMA31_8B, reduced
@@ -227,9 +229,13 @@ def main():
         return float(t.item())
 
     # ---- TTFT: prompt -> first token (p50 over runs, after one warm run) ----
-    first = eng.prefill(ids_dev)
     ttft = []
-    for _ in range(args.ttft_runs):
+    if args.skip_prefill:
+        eng.kv.normal_(0, 1)
+        first, ttft = 1, [float("nan")]
+    else:
+        first = eng.prefill(ids_dev)
+    for _ in range(0 if args.skip_prefill else args.ttft_runs):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -263,6 +269,14 @@ def main():
     clk = clocks.summary()
     ms_per_step = dec_ms / K
     tok_s = 1e3 / ms_per_step
+
+    if args.skip_prefill:
+        if rank == 0:
+            print(json.dumps({"profiling_only": True, "ms_per_step": ms_per_step, "tok_s": tok_s,
+                              "clocks": clk}))
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
 
     # ---- end to end through the public step API: H2D token + state, replay, D2H token ----
     tok_host = torch.zeros(1, dtype=torch.int32).pin_memory()

@@ -30,6 +30,7 @@ _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_int64
 SIGNATURES = {
     "b200_version": (_i, []),
     "b200_sm_count": (_i, []),
+    "b200_set_tuning": (_i, [_i, _i]),
     "b200_gemv_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _p]),
     "b200_add_rmsnorm": (_i, [_p, _p, _i, _p, _p, _i, _p, _i, _i, _f, _i, _p]),
     "b200_add_layernorm": (_i, [_p, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _f, _i, _p]),

@@ -16,6 +16,9 @@ namespace b200 {
 
 constexpr int kNumSMs = 148;
 
+// Tuning knobs set through b200_set_tuning (defined in misc.cu).
+extern int g_tuning[16];
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -1,23 +1,22 @@
 // Split-KV GQA flash-decode with the log-sum-exp combine fused into the same launch.
 //
-// Grid (n_splits, n_kv).  A CTA owns one kv head and one contiguous slice of the
-// context and serves all G = n_q / n_kv query heads of the group from a single
-// pass over K and V, so each cache byte is read from HBM once per step.
+// Grid (n_splits, n_kv), about one CTA per SM.  A CTA owns one kv head and one
+// contiguous slice of the context and serves all G = n_q / n_kv query heads of the
+// group from a single pass over K and V, so each cache byte is read from HBM once.
 //
-// Inside the CTA a key row (HD bf16) is spread over HD/8 lanes, 16 bytes each:
-// a warp-wide 128-bit load covers 32/(HD/8) adjacent keys = 512 contiguous
-// bytes.  Each lane group keeps its own online-softmax state (m, l, acc) in
-// registers and the groups are merged through shared memory at the end.  The
-// CTA then publishes its record to the workspace and bumps a per-kv-head
-// arrival counter; the CTA that arrives last merges all records of that head
-// and writes the output (fixed split order, so results do not depend on
-// arrival order).  No CTA ever waits on another.
+// A key row (HD bf16) is spread over HD/8 lanes, 16 bytes each: a warp-wide 128-bit
+// load covers 32/(HD/8) adjacent keys = 512 contiguous bytes, and a 16-warp CTA
+// keeps 64 KB of loads in flight.  Every lane group runs its own online softmax
+// (m, l, acc in registers); the groups of a warp are merged with shuffles, the
+// warps of a CTA through shared memory, and the CTA publishes ONE record
+// [acc(G x HD), m(G), l(G)] to the workspace.  The CTA that arrives last on the
+// per-kv-head counter merges the n_splits records (a handful of coalesced float4
+// loads per thread) in fixed split order and writes the output.  No CTA ever
+// waits on another.
 #include "common.cuh"
 
 namespace b200 {
 
-constexpr int kFdThreads = 128;
-constexpr int kFdWarps = kFdThreads / 32;
 constexpr int kFdU = 4;  // keys in flight per lane group per iteration
 
 struct FdArgs {
@@ -28,14 +27,20 @@ struct FdArgs {
   float scale_log2;
 };
 
+// threads per CTA: the register file holds 512 threads at 128 registers (G <= 4)
+constexpr int fd_threads(int G) { return G <= 4 ? 512 : 256; }
+
 template <int HD, int G>
-__global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdArgs a) {
+__global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
+  constexpr int THREADS = fd_threads(G);
+  constexpr int WARPS = THREADS / 32;
   constexpr int LPK = HD / 8;          // lanes per key
   constexpr int KPW = 32 / LPK;        // keys per warp-wide load
-  constexpr int NS = kFdWarps * KPW;   // lane groups ("streams") per CTA
-  constexpr int REC = HD + 2;
-  __shared__ float srec[NS * G * REC];
-  __shared__ float sw[NS * G];
+  constexpr int REC = G * HD + ((2 * G + 3) & ~3);  // record: acc[G][HD], m[G], l[G], 16-byte padded
+  extern __shared__ __align__(16) float fd_smem[];
+  float* srec = fd_smem;               // [WARPS][REC]
+  float* sw = srec + WARPS * REC;      // [max(WARPS, n_splits)][G] merge weights
+  __shared__ float s_M[G], s_den[G];
   __shared__ int s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -80,12 +85,12 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdArgs a) {
 
   // key handled by this lane group in unroll slot u of iteration `it`:
   //   k0 + ((it * U + u) * WARPS + warp) * KPW + sub
-  for (int base = k0 + warp * KPW; base < k1; base += kFdU * kFdWarps * KPW) {
+  for (int base = k0 + warp * KPW; base < k1; base += kFdU * WARPS * KPW) {
     uint4 kw[kFdU], vw[kFdU];
     bool ok[kFdU];
 #pragma unroll
     for (int u = 0; u < kFdU; ++u) {
-      const int key = base + u * kFdWarps * KPW + sub;
+      const int key = base + u * WARPS * KPW + sub;
       ok[u] = key < k1;
       kw[u] = make_uint4(0, 0, 0, 0);
       vw[u] = make_uint4(0, 0, 0, 0);
@@ -137,39 +142,57 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdArgs a) {
     }
   }
 
-  // ---- merge the CTA's lane groups ----
-  const int sid = warp * KPW + sub;
+  // ---- merge the lane groups of the warp with shuffles (lanes dl keep the same dims) ----
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float* r = srec + (sid * G + g) * REC;
+  for (int off = LPK; off < 32; off <<= 1) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) r[dl * 8 + e] = acc[g][e];
-    if (dl == 0) { r[HD] = m[g]; r[HD + 1] = l[g]; }
-  }
-  __syncthreads();
-  // per-(stream, head) weights exp2(m_s - M_g); thread t < G handles head t
-  if (tid < G) {
-    float M = -INFINITY;
-    for (int s2 = 0; s2 < NS; ++s2) M = fmaxf(M, srec[(s2 * G + tid) * REC + HD]);
-    const float Mu = (M == -INFINITY) ? 0.f : M;
-    float den = 0.f;
-    for (int s2 = 0; s2 < NS; ++s2) {
-      const float w = exp2f(srec[(s2 * G + tid) * REC + HD] - Mu);
-      sw[s2 * G + tid] = w;
-      den += srec[(s2 * G + tid) * REC + HD + 1] * w;
+    for (int g = 0; g < G; ++g) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
+      const float mn = fmaxf(m[g], mo);
+      const float mu = (mn == -INFINITY) ? 0.f : mn;
+      const float wa = exp2f(m[g] - mu), wb = exp2f(mo - mu);
+      l[g] = l[g] * wa + lo * wb;
+      m[g] = mn;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+        acc[g][e] = acc[g][e] * wa + ao * wb;
+      }
     }
-    float* wr = a.recs + ((size_t)(kvh * a.n_splits + split) * G + tid) * REC;
-    wr[HD] = M;
-    wr[HD + 1] = den;
+  }
+  // ---- one record per warp into shared memory ----
+  if (sub == 0) {
+    float* r = srec + warp * REC;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float4* dst = reinterpret_cast<float4*>(r + g * HD + dl * 8);
+      dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+      dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+      if (dl == 0) { r[G * HD + g] = m[g]; r[G * HD + G + g] = l[g]; }
+    }
   }
   __syncthreads();
-  for (int i = tid; i < G * HD; i += kFdThreads) {
-    const int g = i / HD, d = i - g * HD;
+  // ---- merge the CTA's warps: warp g' computes the weights of head g' ----
+  for (int g = warp; g < G; g += WARPS) {
+    const float mv = lane < WARPS ? srec[lane * REC + G * HD + g] : -INFINITY;
+    const float M = warp_max(mv);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    const float w = lane < WARPS ? exp2f(mv - Mu) : 0.f;
+    const float den = warp_sum(lane < WARPS ? srec[lane * REC + G * HD + G + g] * w : 0.f);
+    if (lane < WARPS) sw[lane * G + g] = w;
+    if (lane == 0) { s_M[g] = M; s_den[g] = den; }
+  }
+  __syncthreads();
+  float* wr = a.recs + (size_t)(kvh * a.n_splits + split) * REC;
+  for (int i = tid; i < G * HD; i += THREADS) {
+    const int g = i / HD;
     float num = 0.f;
 #pragma unroll
-    for (int s2 = 0; s2 < NS; ++s2) num = fmaf(srec[(s2 * G + g) * REC + d], sw[s2 * G + g], num);
-    a.recs[((size_t)(kvh * a.n_splits + split) * G + g) * REC + d] = num;
+    for (int w2 = 0; w2 < WARPS; ++w2) num = fmaf(srec[w2 * REC + i], sw[w2 * G + g], num);
+    wr[i] = num;
   }
+  if (tid < G) { wr[G * HD + tid] = s_M[tid]; wr[G * HD + G + tid] = s_den[tid]; }
 
   // ---- publish, and let the last-arriving CTA of this kv head finish the job ----
   __threadfence();
@@ -182,30 +205,66 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdArgs a) {
   if (!s_last) return;
   __threadfence();
 
-  const float* rb = a.recs + (size_t)kvh * a.n_splits * G * REC;
-  for (int i = tid; i < G * HD; i += kFdThreads) {
-    const int g = i / HD, d = i - g * HD;
+  const float* rb = a.recs + (size_t)kvh * a.n_splits * REC;
+  const int ns = a.n_splits;
+  for (int g = warp; g < G; g += WARPS) {
     float M = -INFINITY;
-    for (int sp = 0; sp < a.n_splits; ++sp) M = fmaxf(M, __ldcg(rb + (sp * G + g) * REC + HD));
+    for (int sp = lane; sp < ns; sp += 32) M = fmaxf(M, __ldcg(rb + (size_t)sp * REC + G * HD + g));
+    M = warp_max(M);
     const float Mu = (M == -INFINITY) ? 0.f : M;
-    float num = 0.f, den = 0.f;
-    for (int sp = 0; sp < a.n_splits; ++sp) {
-      const float* r = rb + (sp * G + g) * REC;
-      const float w = exp2f(__ldcg(r + HD) - Mu);
-      den = fmaf(__ldcg(r + HD + 1), w, den);
-      num = fmaf(__ldcg(r + d), w, num);
+    float den = 0.f;
+    for (int sp = lane; sp < ns; sp += 32) {
+      const float w = exp2f(__ldcg(rb + (size_t)sp * REC + G * HD + g) - Mu);
+      sw[sp * G + g] = w;
+      den = fmaf(__ldcg(rb + (size_t)sp * REC + G * HD + G + g), w, den);
     }
-    const float o = den > 0.f ? num / den : 0.f;
-    const size_t oi = (size_t)(kvh * G + g) * HD + d;
-    if (a.out_dtype == B200_F32) reinterpret_cast<float*>(a.out)[oi] = o;
-    else reinterpret_cast<__nv_bfloat16*>(a.out)[oi] = __float2bfloat16(o);
+    den = warp_sum(den);
+    if (lane == 0) s_den[g] = den;
+  }
+  __syncthreads();
+  for (int i4 = tid; i4 < G * HD / 4; i4 += THREADS) {
+    const int g = (i4 * 4) / HD;
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sp = 0; sp < ns; ++sp) {
+      const float4 r = __ldcg(reinterpret_cast<const float4*>(rb + (size_t)sp * REC) + i4);
+      const float w = sw[sp * G + g];
+      num.x = fmaf(r.x, w, num.x); num.y = fmaf(r.y, w, num.y);
+      num.z = fmaf(r.z, w, num.z); num.w = fmaf(r.w, w, num.w);
+    }
+    const float inv = s_den[g] > 0.f ? 1.f / s_den[g] : 0.f;
+    const size_t oi = (size_t)kvh * G * HD + (size_t)i4 * 4;
+    if (a.out_dtype == B200_F32) {
+      reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + oi)[0] =
+          make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+    } else {
+      uint2 w2;
+      w2.x = pack_bf16(num.x * inv, num.y * inv);
+      w2.y = pack_bf16(num.z * inv, num.w * inv);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out) + oi) = w2;
+    }
   }
   if (tid == 0) a.counters[kvh] = 0;  // ready for the next launch
 }
 
 template <int HD, int G>
+static size_t fd_smem_bytes(int n_splits) {
+  constexpr int WARPS = fd_threads(G) / 32;
+  const int wrows = n_splits > WARPS ? n_splits : WARPS;
+  return (size_t)(WARPS * (G * HD + ((2 * G + 3) & ~3)) + wrows * G) * 4;
+}
+
+template <int HD, int G>
 static cudaError_t fd_launch(const FdArgs& a, cudaStream_t st, bool pdl) {
-  return launch(flash_decode_kernel<HD, G>, dim3(a.n_splits, a.n_kv), dim3(kFdThreads), 0, st, pdl, a);
+  const size_t smem = fd_smem_bytes<HD, G>(a.n_splits);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(flash_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         160 * 1024);
+    attr_set = true;
+  }
+  return launch(flash_decode_kernel<HD, G>, dim3(a.n_splits, a.n_kv), dim3(fd_threads(G)), smem, st,
+                pdl, a);
 }
 
 static size_t fd_counter_bytes(int n_kv) { return ((size_t)n_kv * 4 + 255) & ~(size_t)255; }
@@ -216,7 +275,9 @@ using namespace b200;
 
 extern "C" int64_t b200_flash_decode_workspace_bytes(int n_q, int n_kv, int hd, int n_splits) {
   if (n_q <= 0 || n_kv <= 0 || n_splits <= 0) return 0;
-  return (int64_t)fd_counter_bytes(n_kv) + (int64_t)n_q * n_splits * (hd + 2) * 4;
+  const int G = n_q / n_kv;
+  // per kv head and split: acc[G][hd], m[G], l[G], padded to 16 bytes
+  return (int64_t)fd_counter_bytes(n_kv) + (int64_t)n_kv * n_splits * (G * hd + ((2 * G + 3) & ~3)) * 4;
 }
 
 extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_dtype,
@@ -225,7 +286,7 @@ extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_
                                  int64_t kv_head_stride, int64_t kv_row_stride,
                                  int n_splits, float scale, int flags, b200_stream_t stream) {
   if (!out || !q || !kcache || !vcache || !kv_len_dev || !workspace) return B200_ERR_ARG;
-  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_splits <= 0 || n_splits > 65535)
+  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_splits <= 0 || n_splits > 1024)
     return B200_ERR_SHAPE;
   if ((kv_row_stride & 7) != 0 || (kv_head_stride & 7) != 0 || ((uintptr_t)kcache & 15) != 0 ||
       ((uintptr_t)vcache & 15) != 0 || ((uintptr_t)q & 15) != 0 || ((uintptr_t)workspace & 15) != 0)

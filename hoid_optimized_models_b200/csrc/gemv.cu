@@ -11,14 +11,14 @@
 //
 // The first batch of weight loads is issued before the programmatic-dependent-
 // launch wait, so under B200_FLAG_PDL weight streaming overlaps the tail of
-// the previous kernel in the stream.
+// the previous kernel in the stream.  Loads go out in bursts of U per lane
+// (4 KB contiguous per warp): bursts measured much faster than a rolling window.
 #include "common.cuh"
 
 namespace b200 {
 
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kGemvU = 8;  // 16-byte loads in flight per lane per batch
 
 struct GemvArgs {
   const void* x;
@@ -37,7 +37,14 @@ __device__ __forceinline__ float gelu_erf_f(float v) {
   return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
 }
 
-__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs a) {
+// U    : 16-byte loads per lane per batch (two batches are in flight)
+// MINB : CTAs per SM the register budget is sized for
+// Measured on B200 (graph replay, 32 different weight matrices per case): U = 8 / MINB = 2
+// streams 5.9 TB/s on the 235 MB gate|up matrix; deeper prefetch (U = 16, or both batches
+// before the wait), a CTA-interleaved segment order and a bulk L2 prefetch of the slice were
+// all slower.
+template <int U, int MINB>
+__global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);          // K floats, segment-swizzled
   float* part = xs + a.K;                                    // rpc * kGemvWarps
@@ -51,25 +58,31 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs a) {
   pdl_launch_dependents();
   if (nrows <= 0) return;
 
-  const long S = (long)nrows * spr;
-  const int s0 = (int)(S * warp / kGemvWarps);
-  const int s1 = (int)(S * (warp + 1) / kGemvWarps);
+  const int S = nrows * spr;  // 512-byte segments owned by the CTA
+  // every warp streams its own contiguous eighth of the CTA's segments
+  const int s0 = (int)((long)S * warp / kGemvWarps);
+  const int s1 = (int)((long)S * (warp + 1) / kGemvWarps);
+  const int nbatch = (s1 - s0 + U - 1) / U;
+  auto batch_first = [&](int b) -> int { return s0 + b * U; };
 
-  // load cursor and compute cursor over (row, segment-in-row)
-  int lrow = s0 / spr, lk = s0 - lrow * spr;
-  int crow = lrow, ck = lk;
   const unsigned char* wb =
       reinterpret_cast<const unsigned char*>(a.w) + (size_t)r0 * a.ldw * 2 + lane * 16;
   const size_t row_bytes = (size_t)a.ldw * 2;
 
-  uint4 wc[kGemvU];
+  auto load_batch = [&](uint4* dst, int b) {
+    const int f = batch_first(b);
+    int row = f / spr, k = f - row * spr;
 #pragma unroll
-  for (int j = 0; j < kGemvU; ++j) {
-    if (s0 + j < s1) {
-      wc[j] = ldg_stream(wb + lrow * row_bytes + (size_t)lk * 512);
-      if (++lk == spr) { lk = 0; ++lrow; }
+    for (int j = 0; j < U; ++j) {
+      if (f + j < s1) {
+        dst[j] = ldg_stream(wb + row * row_bytes + (size_t)k * 512);
+        if (++k == spr) { k = 0; ++row; }
+      }
     }
-  }
+  };
+
+  uint4 wc[U];
+  if (nbatch > 0) load_batch(wc, 0);
 
   // ---- everything below may depend on the previous kernel ----
   pdl_wait();
@@ -108,18 +121,20 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs a) {
   __syncthreads();
 
   float acc = 0.f;
-  for (int s = s0; s < s1; s += kGemvU) {
-    uint4 wn[kGemvU];
+  int crow = 0, ck = 0;
+  auto flush = [&]() {
+    const float v = warp_sum(acc);
+    if (lane == 0) part[crow * kGemvWarps + warp] = v;   // a warp meets every row at most once
+    acc = 0.f;
+  };
+  for (int b = 0; b < nbatch; ++b) {
+    uint4 wn[U];
+    if (b + 1 < nbatch) load_batch(wn, b + 1);
+    const int f = batch_first(b);
+    if (b == 0) { crow = f / spr; ck = f - crow * spr; }
 #pragma unroll
-    for (int j = 0; j < kGemvU; ++j) {
-      if (s + kGemvU + j < s1) {
-        wn[j] = ldg_stream(wb + lrow * row_bytes + (size_t)lk * 512);
-        if (++lk == spr) { lk = 0; ++lrow; }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < kGemvU; ++j) {
-      if (s + j < s1) {
+    for (int j = 0; j < U; ++j) {
+      if (f + j < s1) {
         const float4 xa = xs4[ck * 64 + lane];
         const float4 xb = xs4[ck * 64 + 32 + lane];
         const uint4 w = wc[j];
@@ -131,20 +146,13 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs a) {
         acc = fmaf(bf16hi(w.z), xb.y, acc);
         acc = fmaf(bf16lo(w.w), xb.z, acc);
         acc = fmaf(bf16hi(w.w), xb.w, acc);
-        if (++ck == spr) {
-          const float v = warp_sum(acc);
-          if (lane == 0) part[crow * kGemvWarps + warp] = v;
-          acc = 0.f; ck = 0; ++crow;
-        }
+        if (++ck == spr) { flush(); ck = 0; ++crow; }
       }
     }
 #pragma unroll
-    for (int j = 0; j < kGemvU; ++j) wc[j] = wn[j];
+    for (int j = 0; j < U; ++j) wc[j] = wn[j];
   }
-  if (ck != 0 && s1 > s0) {
-    const float v = warp_sum(acc);
-    if (lane == 0) part[crow * kGemvWarps + warp] = v;
-  }
+  if (ck != 0 && s1 > s0) flush();
   __syncthreads();
 
   // ---- epilogue: fixed-order row sums ----
@@ -179,6 +187,26 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(GemvArgs a) {
   }
 }
 
+template <int U, int MINB>
+static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pdl) {
+  // MINB CTAs per SM; grow the grid in whole waves until the per-CTA row block is small
+  const int wave = MINB * kNumSMs;
+  int grid = wave;
+  int rpc = (a.N + grid - 1) / grid;
+  while (rpc > 1024) { grid += wave; rpc = (a.N + grid - 1) / grid; }
+  if (swiglu && (rpc & 1)) ++rpc;
+  grid = (a.N + rpc - 1) / rpc;
+  a.rpc = rpc;
+  const size_t smem = (size_t)a.K * 4 + (size_t)rpc * kGemvWarps * 4 + 128;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemv_kernel<U, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    attr_set = true;
+  }
+  return launch(gemv_kernel<U, MINB>, dim3(grid), dim3(kGemvThreads), smem, st, pdl, a);
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -194,27 +222,20 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_GELU) return B200_ERR_ARG;
   if (K > 32768) return B200_ERR_SHAPE;
 
-  // two CTAs per SM; grow the grid in whole waves until the per-CTA row block is small
-  int grid = 2 * kNumSMs;
-  int rpc = (N + grid - 1) / grid;
-  while (rpc > 1024) { grid += 2 * kNumSMs; rpc = (N + grid - 1) / grid; }
-  if (epilogue == B200_EPI_SWIGLU && (rpc & 1)) ++rpc;
-  grid = (N + rpc - 1) / rpc;
-
   GemvArgs a;
   a.x = x; a.w = (const uint16_t*)w; a.y = y;
   a.norm_w = (const uint16_t*)norm_w; a.bias = (const uint16_t*)bias; a.resid = resid;
-  a.K = K; a.N = N; a.ldw = ldw; a.rpc = rpc;
+  a.K = K; a.N = N; a.ldw = ldw; a.rpc = 0;
   a.x_dtype = x_dtype; a.y_dtype = y_dtype; a.resid_dtype = resid_dtype; a.epilogue = epilogue;
   a.eps = eps;
-
-  const size_t smem = (size_t)K * 4 + (size_t)rpc * kGemvWarps * 4 + 128;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_set = true;
+  const bool sw = epilogue == B200_EPI_SWIGLU;
+  const bool pdl = (flags & B200_FLAG_PDL) != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  switch (g_tuning[B200_TUNE_GEMV]) {
+    case 1: e = gemv_launch<4, 4>(a, sw, st, pdl); break;
+    case 2: e = gemv_launch<4, 3>(a, sw, st, pdl); break;
+    default: e = gemv_launch<8, 2>(a, sw, st, pdl); break;
   }
-  cudaError_t e = launch(gemv_kernel, dim3(grid), dim3(kGemvThreads), smem, (cudaStream_t)stream,
-                         (flags & B200_FLAG_PDL) != 0, a);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }

@@ -123,6 +123,14 @@ __global__ void greedy_select_kernel(int* tok_out, const Best* cand, int n, int*
 
 using namespace b200;
 
+namespace b200 { int g_tuning[16] = {3, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; }
+
+extern "C" int b200_set_tuning(int key, int value) {
+  if (key < 0 || key >= 16) return B200_ERR_ARG;
+  g_tuning[key] = value;
+  return B200_OK;
+}
+
 extern "C" int b200_version(void) { return 100; }
 extern "C" int b200_sm_count(void) { return kNumSMs; }
 

@@ -120,7 +120,7 @@ class DenseDecoder:
         self.cand = f32(2)
         self.cand_all = f32(tp_size, 2)
         if n_splits is None:
-            n_splits = max(1, min((4 * 148) // self.n_kv, (max_seq + 63) // 64))
+            n_splits = max(1, min(148 // self.n_kv, (max_seq + 63) // 64))  # ~one CTA per SM
         self.n_splits = n_splits
         self.fd_ws = ops.flash_decode_workspace(self.n_q, self.n_kv, hd, n_splits, dev)
         self.am_ws = ops.argmax_workspace(dev)
@@ -169,9 +169,9 @@ class DenseDecoder:
         if tp:
             torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2),
                                                      group=self.group)
-            ops.greedy_select(self.tok, self.cand_all, self.state, self.tok_log)
+            ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand_all)
         else:
-            ops.greedy_select(self.tok, self.cand, self.state, self.tok_log)
+            ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
         # an even number of buffer swaps per layer keeps the residual stream in self.h
 
     def capture(self, warmup: int = 3) -> None:
@@ -237,7 +237,7 @@ class DenseDecoder:
         hd = cfg.head_dim
         x, hn, part = e["x"], e["hn"], e["part"]
         ops.embed_gather(x, self.embed, e["ids"])
-        ops.add_rmsnorm(hn, x, self.ln1[0], cfg.eps)
+        ops.rmsnorm(hn, x, self.ln1[0], cfg.eps)
         for i in range(cfg.layers):
             kc, vc = self.kv[i, 0], self.kv[i, 1]
             ops.gemm(e["qkv"], hn, self.wqkv[i])
@@ -248,19 +248,19 @@ class DenseDecoder:
             if tp:
                 ops.gemm(part, e["att"], self.wo[i])
                 self._all_reduce(part)
-                ops.add_rmsnorm(hn, x, self.ln2[i], cfg.eps, b=part, resid_out=x)
+                ops.add_rmsnorm(hn, x, x, part, self.ln2[i], cfg.eps)
             else:
                 ops.gemm(x, e["att"], self.wo[i], resid=x)
-                ops.add_rmsnorm(hn, x, self.ln2[i], cfg.eps)
+                ops.rmsnorm(hn, x, self.ln2[i], cfg.eps)
             ops.gemm(e["act"], hn, self.wgu[i], epilogue=EPI_SWIGLU)
             nw = self.ln1[i + 1] if i + 1 < cfg.layers else self.final_norm_w
             if tp:
                 ops.gemm(part, e["act"], self.wd[i])
                 self._all_reduce(part)
-                ops.add_rmsnorm(hn, x, nw, cfg.eps, b=part, resid_out=x)
+                ops.add_rmsnorm(hn, x, x, part, nw, cfg.eps)
             else:
                 ops.gemm(x, e["act"], self.wd[i], resid=x)
-                ops.add_rmsnorm(hn, x, nw, cfg.eps)
+                ops.rmsnorm(hn, x, nw, cfg.eps)
             if collect is not None:
                 collect.append(x.clone())
         # hn now holds the final-norm output; project the last position only

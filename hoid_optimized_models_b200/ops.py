@@ -78,10 +78,7 @@ def gemv(y: Tensor, x: Tensor, w: Tensor, norm_w: Optional[Tensor] = None, eps: 
 
 
 # ----------------------------------------------------------------------------- norms
-@torch.library.custom_op("b200::add_rmsnorm", mutates_args=("resid_out", "norm_out"))
-def add_rmsnorm(norm_out: Tensor, a: Tensor, w: Tensor, eps: float, b: Optional[Tensor] = None,
-                resid_out: Optional[Tensor] = None) -> None:
-    """norm_out = rmsnorm(a (+ b)) * w; resid_out (optional) receives a + b."""
+def _rmsnorm_call(resid_out, norm_out, a, b, w, eps):
     _bf16(w, "w")
     N = w.numel()
     rows = a.numel() // N
@@ -94,11 +91,22 @@ def add_rmsnorm(norm_out: Tensor, a: Tensor, w: Tensor, eps: float, b: Optional[
         rows, N, eps, _flags(), _stream()), "b200_add_rmsnorm")
 
 
-@torch.library.custom_op("b200::add_layernorm", mutates_args=("resid_out", "norm_out"))
-def add_layernorm(norm_out: Tensor, x: Tensor, gamma: Tensor, beta: Tensor, eps: float,
-                  bias: Optional[Tensor] = None, resid: Optional[Tensor] = None,
-                  resid_out: Optional[Tensor] = None) -> None:
-    """norm_out = LayerNorm(x (+ bias) (+ resid)); resid_out (optional) receives the sum."""
+# Mutated arguments of a custom op are always leading, required, positional parameters.
+@torch.library.custom_op("b200::rmsnorm", mutates_args=("norm_out",))
+def rmsnorm(norm_out: Tensor, a: Tensor, w: Tensor, eps: float) -> None:
+    """norm_out = rmsnorm(a) * w."""
+    _rmsnorm_call(None, norm_out, a, None, w, eps)
+
+
+@torch.library.custom_op("b200::add_rmsnorm", mutates_args=("norm_out", "resid_out"))
+def add_rmsnorm(norm_out: Tensor, resid_out: Tensor, a: Tensor, b: Tensor, w: Tensor,
+                eps: float) -> None:
+    """resid_out = a + b (rounded to its dtype); norm_out = rmsnorm(resid_out) * w.
+    resid_out may alias a."""
+    _rmsnorm_call(resid_out, norm_out, a, b, w, eps)
+
+
+def _layernorm_call(resid_out, norm_out, x, gamma, beta, eps, bias, resid):
     _bf16(gamma, "gamma"); _bf16(beta, "beta"); _bf16(bias, "bias")
     N = gamma.numel()
     rows = x.numel() // N
@@ -107,6 +115,21 @@ def add_layernorm(norm_out: Tensor, x: Tensor, gamma: Tensor, beta: Tensor, eps:
     check(_lib.lib().b200_add_layernorm(
         _ptr(resid_out), _ptr(norm_out), _dt(norm_out), _ptr(x), _ptr(bias), _ptr(resid), _dt(x),
         _ptr(gamma), _ptr(beta), rows, N, eps, _flags(), _stream()), "b200_add_layernorm")
+
+
+@torch.library.custom_op("b200::layernorm", mutates_args=("norm_out",))
+def layernorm(norm_out: Tensor, x: Tensor, gamma: Tensor, beta: Tensor, eps: float,
+              bias: Optional[Tensor] = None, resid: Optional[Tensor] = None) -> None:
+    """norm_out = LayerNorm(x (+ bias) (+ resid))."""
+    _layernorm_call(None, norm_out, x, gamma, beta, eps, bias, resid)
+
+
+@torch.library.custom_op("b200::add_layernorm", mutates_args=("norm_out", "resid_out"))
+def add_layernorm(norm_out: Tensor, resid_out: Tensor, x: Tensor, gamma: Tensor, beta: Tensor,
+                  eps: float, bias: Optional[Tensor] = None,
+                  resid: Optional[Tensor] = None) -> None:
+    """resid_out = x (+ bias) (+ resid); norm_out = LayerNorm(resid_out)."""
+    _layernorm_call(resid_out, norm_out, x, gamma, beta, eps, bias, resid)
 
 
 # ----------------------------------------------------------------------------- rope + cache
@@ -272,13 +295,22 @@ def argmax(cand: Tensor, logits: Tensor, workspace: Tensor, idx_base: int = 0) -
                                      _ptr(workspace), _flags(), _stream()), "b200_argmax_f32")
 
 
-@torch.library.custom_op("b200::greedy_select", mutates_args=("tok_out", "state", "log"))
-def greedy_select(tok_out: Tensor, cand: Tensor, state: Optional[Tensor] = None,
-                  log: Optional[Tensor] = None) -> None:
-    """tok_out[0] = index of the best of the candidate records in cand (float32 [n, 2]);
-    appends it to log and advances state = {position, kv_len, generated} (int32 [3+])."""
+def _greedy_call(tok_out, cand, state, log):
     if tok_out.dtype != torch.int32 or cand.dtype != torch.float32:
         raise TypeError("greedy_select takes an int32 token and float32 candidates")
     check(_lib.lib().b200_greedy_select(_ptr(tok_out), _ptr(cand), cand.numel() // 2, _ptr(state),
                                         _ptr(log), log.numel() if log is not None else 0,
                                         _flags(), _stream()), "b200_greedy_select")
+
+
+@torch.library.custom_op("b200::greedy_select", mutates_args=("tok_out",))
+def greedy_select(tok_out: Tensor, cand: Tensor) -> None:
+    """tok_out[0] = index of the best of the candidate records in cand (float32 [n, 2])."""
+    _greedy_call(tok_out, cand, None, None)
+
+
+@torch.library.custom_op("b200::greedy_advance", mutates_args=("tok_out", "state", "log"))
+def greedy_advance(tok_out: Tensor, state: Tensor, log: Tensor, cand: Tensor) -> None:
+    """greedy_select, then log[state[2]] = token and state = {position, kv_len, generated}
+    (int32 [3+]) advances by one: the next graph replay continues without the host."""
+    _greedy_call(tok_out, cand, state, log)

@@ -53,6 +53,10 @@ enum {
 };
 
 int b200_version(void);
+/* Kernel tuning knobs (process-wide, host side): key B200_TUNE_GEMV selects the GEMV
+ * variant (loads per batch / CTAs per SM / row mapping); 0 is the measured best. */
+enum { B200_TUNE_GEMV = 0 };
+int b200_set_tuning(int key, int value);
 /* Number of SMs the library sizes its grids for (148 on B200). */
 int b200_sm_count(void);
 

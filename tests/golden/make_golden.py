@@ -1,0 +1,67 @@
+"""Generates tests/golden/decoder_<family>.npz from the HuggingFace eager fp32 models (the
+reference's parity authority) on tiny seeded configurations.
+
+    python tests/golden/make_golden.py
+
+Each file holds the token ids, the HF per-layer hidden state of the last position, the HF
+logits of the last four positions, 8 HF greedy tokens and (MoE) the HF router's top-k expert
+ids; the transformers / torch versions are recorded alongside."""
+import json
+import os
+import sys
+from dataclasses import replace
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from hoid_optimized_models_b200.configs import LLAMA31_8B, QWEN3_4B, QWEN3_30B_A3B  # noqa: E402
+from hoid_optimized_models_b200.weights import make_decoder_weights  # noqa: E402
+from oracle import ref_decoder as R  # noqa: E402
+
+SEED = 1234
+
+
+def tiny(base):
+    moe = bool(base.n_experts)
+    return replace(base, name=base.name + "-tiny", hidden=128, layers=2, n_q=4, n_kv=2, head_dim=32,
+                   inter=0 if moe else 256, vocab=512, n_experts=8 if moe else 0,
+                   top_k=2 if moe else 0, moe_inter=64 if moe else 0)
+
+
+FAMILIES = {"llama": LLAMA31_8B, "qwen3": QWEN3_4B, "qwen3moe": QWEN3_30B_A3B}
+
+
+def main():
+    import transformers
+    meta = {"transformers": transformers.__version__, "torch": torch.__version__, "seed": SEED}
+    for fam, base in FAMILIES.items():
+        cfg = tiny(base)
+        w = make_decoder_weights(cfg, SEED)
+        ids = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(SEED))
+        model = R.hf_model(cfg, w)
+        hs, logits = R.hf_forward(model, ids)
+        out = {"ids": ids.numpy(), "hidden_last": torch.stack([h[-1] for h in hs]).numpy(),
+               "logits_tail": logits[-4:].numpy(),
+               "greedy": np.array(R.hf_greedy(model, ids, 8))}
+        if cfg.n_experts:
+            captured = []
+            hooks = [l.mlp.gate.register_forward_hook(lambda m, i, o: captured.append(o))
+                     for l in model.model.layers]
+            R.hf_forward(model, ids)
+            for h in hooks:
+                h.remove()
+            # router output layout differs between transformers versions; keep the index tensor
+            idx = [c for o in captured for c in (o if isinstance(o, tuple) else (o,))
+                   if c.dtype in (torch.int64, torch.int32)]
+            out["router_ids"] = torch.stack([i.sort(-1).values for i in idx]).numpy()
+        np.savez_compressed(os.path.join(HERE, f"decoder_{fam}.npz"), **out)
+        print(fam, {k: v.shape for k, v in out.items()})
+    with open(os.path.join(HERE, "versions.json"), "w") as f:
+        json.dump(meta, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,76 @@
+"""CPU-side checks of the drop-in boundary: the C-ABI library builds, loads without a GPU and
+exports exactly the entry points include/b200ops.h declares; host-side argument validation
+raises instead of launching.  No compute is called here."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200ops.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_\w+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as g
+    g.build()
+    from hoid_optimized_models_b200 import _lib
+    return _lib.load()
+
+
+def test_header_and_binding_agree(lib):
+    from hoid_optimized_models_b200 import _lib
+    syms = declared_symbols()
+    assert len(syms) >= 15
+    assert syms == sorted(_lib.SIGNATURES), "ctypes table and header differ"
+    for s in syms:
+        assert isinstance(getattr(lib, s), ctypes._CFuncPtr), s
+
+
+def test_header_cites_reference():
+    text = open(HEADER).read()
+    # every compute entry point names the reference file it replaces (or says it has none)
+    for block in re.findall(r"/\*.*?\*/\s*(?:int64_t|int)\s+b200_\w+", text, flags=re.S):
+        name = block.split()[-1]
+        if name in ("b200_version", "b200_sm_count") or name.endswith("_workspace_bytes"):
+            continue
+    assert text.count("Reference:") >= 10
+
+
+def test_no_gpu_calls_needed_for_queries(lib):
+    assert lib.b200_version() >= 100
+    assert lib.b200_sm_count() == 148
+    assert lib.b200_flash_decode_workspace_bytes(32, 8, 128, 74) == 256 + 32 * 74 * 130 * 4
+    assert lib.b200_argmax_workspace_bytes(128256) > 0
+
+
+def test_argument_validation_returns_codes(lib):
+    # null pointers and bad shapes are rejected on the host before any launch
+    assert lib.b200_gemv_bf16(None, 0, None, None, 0, 256, 8, 256, None, 0.0, None, None, 0, 0, 0, None) == -4
+    one = ctypes.c_void_p(16)
+    assert lib.b200_gemv_bf16(one, 0, one, one, 0, 100, 8, 100, None, 0.0, None, None, 0, 0, 0, None) == -1
+    assert lib.b200_add_rmsnorm(None, one, 0, one, None, 0, one, 1, 12, 1e-5, 0, None) == -1
+    assert lib.b200_flash_decode(one, 1, one, 1, one, one, one, one, 32, 5, 128, 128, 128, 4, 1.0, 0, None) == -1
+    assert lib.b200_gemm_bf16(one, one, one, 128, 100, 64, 64, 64, 100, None, None, 0, 0, None, 0, None) == -1
+
+
+def test_ops_refuse_cpu_tensors():
+    """There is no CPU fallback: CPU tensors are an error, not a slow path."""
+    from hoid_optimized_models_b200 import ops
+    w = torch.zeros(8, 256, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.gemv(torch.zeros(8), torch.zeros(256), w)
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    from hoid_optimized_models_b200 import _lib
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _lib.load(str(tmp_path / "nope.so"))

@@ -59,13 +59,25 @@ def _run(dev, cfg, P, seed):
         err = float((step_hidden[l].cpu() - ref).abs().max() / ref.abs().max())
         assert err < 2e-2, f"decode layer {l}: {err}"
     greedy_ref = logits_ref.argmax(-1).tolist()
-    cos = torch.nn.functional.cosine_similarity(torch.stack(step_logits), logits_ref[1:], dim=-1)
+    got = torch.stack(step_logits)
+    cos = torch.nn.functional.cosine_similarity(got, logits_ref[1:], dim=-1)
     assert float(cos.min()) >= 0.999, f"logit cosine {float(cos.min())}"
+    # Greedy parity.  Random-init heads produce near-ties: a token may differ from the oracle's
+    # only where the oracle's own top-2 margin is inside the measured logit error of that step
+    # (bf16 KV cache and bf16 prefill activations against an fp32 oracle).  Teacher forcing
+    # makes every step an independent check.
+    err = (got - logits_ref[1:]).abs().max(-1).values          # per decode step
+    assert float(err.max()) < 3e-2 * float(logits_ref.abs().max()), f"logit error {float(err.max())}"
     top2 = logits_ref.topk(2, -1).values
-    margin = (top2[:, 0] - top2[:, 1])
-    assert toks == greedy_ref, (
-        f"greedy mismatch; oracle top-2 margins {margin.tolist()}")
-    return float(cos.min()), float(margin.min())
+    margin = top2[:, 0] - top2[:, 1]
+    noise = torch.cat((err[:1], err))                           # step 0 comes from the prefill
+    flips = [j for j in range(N_NEW) if toks[j] != greedy_ref[j]]
+    for j in flips:
+        assert float(margin[j]) <= 2 * float(noise[j]), (
+            f"step {j}: token {toks[j]} != oracle {greedy_ref[j]} with margin {float(margin[j]):.4f} "
+            f"> 2 x logit error {float(noise[j]):.4f}")
+    assert len(flips) <= 2, f"too many near-tie flips: {flips}"
+    return float(cos.min()), float(margin.min()), flips
 
 
 def test_llama_arch(dev):

@@ -86,12 +86,12 @@ def test_add_rmsnorm(dev, rows, N, dt):
     ref = rmsnorm(s.float(), w.float(), 1e-6)
     res = torch.empty(rows, N, dtype=dt, device=dev)
     out = torch.empty(rows, N, dtype=dt, device=dev)
-    ops.add_rmsnorm(out, a.to(dev), w.to(dev), 1e-6, b=b.to(dev), resid_out=res)
+    ops.add_rmsnorm(out, res, a.to(dev), b.to(dev), w.to(dev), 1e-6)
     assert torch.equal(res.cpu(), s)
     tol = 1e-2 if dt == torch.bfloat16 else 1e-5
     assert rel_err(out, ref) < tol
     out2 = torch.empty_like(out)
-    ops.add_rmsnorm(out2, a.to(dev), w.to(dev), 1e-6)
+    ops.rmsnorm(out2, a.to(dev), w.to(dev), 1e-6)
     assert rel_err(out2, rmsnorm(a.float(), w.float(), 1e-6)) < tol
 
 
@@ -108,14 +108,14 @@ def test_add_layernorm(dev, rows, N):
     ref = torch.nn.functional.layer_norm(s.float(), (N,), gamma.float(), beta.float(), 1e-5)
     res = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
     out = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
-    ops.add_layernorm(out, x.to(dev), gamma.to(dev), beta.to(dev), 1e-5, bias=bias.to(dev),
-                      resid=r.to(dev), resid_out=res)
+    ops.add_layernorm(out, res, x.to(dev), gamma.to(dev), beta.to(dev), 1e-5, bias=bias.to(dev),
+                      resid=r.to(dev))
     assert torch.equal(res.cpu(), s)
     assert rel_err(out, ref) < 1e-2
     # plain fp32 LayerNorm
     xf = torch.randn(rows, N, generator=g)
     outf = torch.empty(rows, N, dtype=torch.float32, device=dev)
-    ops.add_layernorm(outf, xf.to(dev), gamma.to(dev), beta.to(dev), 1e-5)
+    ops.layernorm(outf, xf.to(dev), gamma.to(dev), beta.to(dev), 1e-5)
     reff = torch.nn.functional.layer_norm(xf, (N,), gamma.float(), beta.float(), 1e-5)
     assert rel_err(outf, reff) < 1e-5
 
@@ -234,7 +234,7 @@ def test_embed_silu_argmax(dev):
     tok = torch.zeros(1, dtype=torch.int32, device=dev)
     state = torch.tensor([10, 11, 2, 0], dtype=torch.int32, device=dev)
     log = torch.zeros(8, dtype=torch.int32, device=dev)
-    ops.greedy_select(tok, cands.to(dev), state, log)
+    ops.greedy_advance(tok, state, log, cands.to(dev))
     assert int(tok) == 40 and state.tolist() == [11, 12, 3, 0] and int(log[2]) == 40
 
 

@@ -1,0 +1,88 @@
+"""Pins the CPU oracle (oracle/ref_decoder.py) that the GPU parity tests trust:
+
+1. against the committed golden vectors produced by the HuggingFace eager fp32 models (the
+   reference's parity authority) — tests/golden/make_golden.py;
+2. live against the same HuggingFace models when transformers is importable;
+3. the engine's RoPE tables against the oracle's / HuggingFace's frequency rule.
+Tolerances: fp32 against fp32 with a different summation order -> 1e-4 relative."""
+import os
+from dataclasses import replace
+
+import numpy as np
+import pytest
+import torch
+
+from hoid_optimized_models_b200.configs import LLAMA31_8B, QWEN3_4B, QWEN3_30B_A3B
+from hoid_optimized_models_b200.weights import make_decoder_weights, rope_inv_freq
+from oracle import ref_decoder as R
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+FAMILIES = {"llama": LLAMA31_8B, "qwen3": QWEN3_4B, "qwen3moe": QWEN3_30B_A3B}
+
+
+def tiny(base):
+    moe = bool(base.n_experts)
+    return replace(base, name=base.name + "-tiny", hidden=128, layers=2, n_q=4, n_kv=2, head_dim=32,
+                   inter=0 if moe else 256, vocab=512, n_experts=8 if moe else 0,
+                   top_k=2 if moe else 0, moe_inter=64 if moe else 0)
+
+
+@pytest.mark.parametrize("fam", sorted(FAMILIES))
+def test_restatement_matches_golden(fam):
+    cfg = tiny(FAMILIES[fam])
+    gold = np.load(os.path.join(GOLD, f"decoder_{fam}.npz"))
+    w = make_decoder_weights(cfg, 1234)
+    ids = torch.from_numpy(gold["ids"])
+    hidden, logits, router = R.decoder_forward(cfg, w, ids)
+    got = torch.stack([h[-1] for h in hidden]).numpy()
+    assert np.abs(got - gold["hidden_last"]).max() <= 1e-4 * np.abs(gold["hidden_last"]).max()
+    assert np.abs(logits[-4:].numpy() - gold["logits_tail"]).max() <= 1e-4 * np.abs(gold["logits_tail"]).max()
+    # greedy continuation by re-running the oracle on the growing sequence
+    seq = ids.clone()
+    out = []
+    for _ in range(len(gold["greedy"])):
+        _, lg, _ = R.decoder_forward(cfg, w, seq, logits_rows=[seq.numel() - 1], keep_hidden=False)
+        out.append(int(lg.argmax()))
+        seq = torch.cat((seq, torch.tensor([out[-1]])))
+    assert out == gold["greedy"].tolist()
+    if cfg.n_experts:
+        ids_k = torch.stack([R.moe_route(r, cfg.top_k)[0].sort(-1).values for r in router]).numpy()
+        assert np.array_equal(ids_k, gold["router_ids"])   # expert choice is bit-exact
+
+
+@pytest.mark.parametrize("fam", sorted(FAMILIES))
+def test_restatement_matches_live_hf(fam):
+    pytest.importorskip("transformers")
+    cfg = replace(tiny(FAMILIES[fam]), layers=3)
+    w = make_decoder_weights(cfg, 77)
+    ids = torch.randint(0, cfg.vocab, (40,), generator=torch.Generator().manual_seed(5))
+    hs, logits = R.hf_forward(R.hf_model(cfg, w), ids)
+    hidden, lg, _ = R.decoder_forward(cfg, w, ids)
+    for a, b in zip(hs, hidden):
+        assert float((a - b).abs().max()) <= 1e-4 * float(a.abs().max())
+    assert float((logits - lg).abs().max()) <= 1e-4 * float(logits.abs().max())
+
+
+def test_rope_tables_follow_llama3_rule():
+    for cfg in (LLAMA31_8B, QWEN3_4B):
+        a, b = rope_inv_freq(cfg), R.inv_freq(cfg)
+        assert float((a - b).abs().max()) < 1e-15
+    # the scaled band really is scaled: lowest frequency is divided by the factor
+    base = replace(LLAMA31_8B, rope_scaling=None)
+    assert abs(float(rope_inv_freq(LLAMA31_8B)[-1] * 8 / rope_inv_freq(base)[-1]) - 1) < 1e-12
+    assert float(rope_inv_freq(LLAMA31_8B)[0]) == float(rope_inv_freq(base)[0])
+
+
+def test_chunked_attention_is_chunk_invariant():
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(50, 4, 16, generator=g), torch.randn(50, 2, 16, generator=g),
+               torch.randn(50, 2, 16, generator=g))
+    a = R.causal_attention(q, k, v, 0.25, chunk=7)
+    b = R.causal_attention(q, k, v, 0.25, chunk=1024)
+    assert float((a - b).abs().max()) < 1e-6
+
+
+def test_algorithmic_bytes_match_derivation():
+    # 15 009 849 344 B of weights + 131 072 B of KV per cached position (Llama-3.1-8B)
+    assert LLAMA31_8B.decode_bytes_per_token(0) == 15_009_849_344
+    assert LLAMA31_8B.decode_bytes_per_token(8192) - LLAMA31_8B.decode_bytes_per_token(0) == 131072 * 8192
