@@ -17,7 +17,7 @@
 
 namespace b200 {
 
-constexpr int kFdU = 4;  // keys in flight per lane group per iteration
+constexpr int kFdU = 2;  // keys per lane group per iteration (two iterations in flight)
 
 struct FdArgs {
   void* out; const void* q; const uint16_t* k; const uint16_t* v; const int* kv_len;
@@ -85,23 +85,30 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
 
   // key handled by this lane group in unroll slot u of iteration `it`:
   //   k0 + ((it * U + u) * WARPS + warp) * KPW + sub
-  for (int base = k0 + warp * KPW; base < k1; base += kFdU * WARPS * KPW) {
-    uint4 kw[kFdU], vw[kFdU];
-    bool ok[kFdU];
+  // The loads of iteration it + 1 are issued before the arithmetic of iteration it.
+  constexpr int STRIDE = kFdU * WARPS * KPW;
+  uint4 kw[kFdU], vw[kFdU];
+  auto issue = [&](uint4* kd, uint4* vd, int base) {
 #pragma unroll
     for (int u = 0; u < kFdU; ++u) {
       const int key = base + u * WARPS * KPW + sub;
-      ok[u] = key < k1;
-      kw[u] = make_uint4(0, 0, 0, 0);
-      vw[u] = make_uint4(0, 0, 0, 0);
-      if (ok[u]) {
-        kw[u] = ldg_stream(kb + (size_t)key * a.row_stride);
-        vw[u] = ldg_stream(vb + (size_t)key * a.row_stride);
+      kd[u] = make_uint4(0, 0, 0, 0);
+      vd[u] = make_uint4(0, 0, 0, 0);
+      if (key < k1) {
+        kd[u] = ldg_stream(kb + (size_t)key * a.row_stride);
+        vd[u] = ldg_stream(vb + (size_t)key * a.row_stride);
       }
     }
+  };
+  const int base0 = k0 + warp * KPW;
+  if (base0 < k1) issue(kw, vw, base0);
+  for (int base = base0; base < k1; base += STRIDE) {
+    uint4 kn[kFdU], vn[kFdU];
+    if (base + STRIDE < k1) issue(kn, vn, base + STRIDE);
     float s[kFdU][G];
 #pragma unroll
     for (int u = 0; u < kFdU; ++u) {
+      const bool ok = base + u * WARPS * KPW + sub < k1;
       float kf[8];
       unpack8(kw[u], kf);
 #pragma unroll
@@ -111,7 +118,7 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
         for (int e = 0; e < 8; ++e) d = fmaf(q[g][e], kf[e], d);
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        s[u][g] = ok[u] ? d : -INFINITY;
+        s[u][g] = ok ? d : -INFINITY;
       }
     }
     float p[kFdU][G];
@@ -140,6 +147,8 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(p[u][g], vf[e], acc[g][e]);
     }
+#pragma unroll
+    for (int u = 0; u < kFdU; ++u) { kw[u] = kn[u]; vw[u] = vn[u]; }
   }
 
   // ---- merge the lane groups of the warp with shuffles (lanes dl keep the same dims) ----

@@ -30,7 +30,14 @@ struct GemvArgs {
   int K, N, ldw, rpc;  // rpc = rows per CTA
   int x_dtype, y_dtype, resid_dtype, epilogue;
   float eps;
+  // mixture-of-experts modes (see MODE below)
+  const int* expert_ids;     // [n_slots] expert chosen for each routing slot
+  const float* slot_scale;   // [n_slots] routing weight folded into the SwiGLU output (MODE 1)
+  long expert_stride;        // elements between consecutive experts' matrices
+  int segs_per_expert;       // MODE 2: 256-element segments of one expert's K range
 };
+
+constexpr int kMaxExpertSegs = 256;
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 __device__ __forceinline__ float gelu_erf_f(float v) {
@@ -43,9 +50,17 @@ __device__ __forceinline__ float gelu_erf_f(float v) {
 // streams 5.9 TB/s on the 235 MB gate|up matrix; deeper prefetch (U = 16, or both batches
 // before the wait), a CTA-interleaved segment order and a bulk L2 prefetch of the slice were
 // all slower.
-template <int U, int MINB>
+// MODE : 0 = dense matrix.
+//        1 = expert rows: blockIdx.y is a routing slot, the matrix of expert
+//            expert_ids[slot] is used and the output goes to y + slot * (N or N/2).
+//        2 = expert columns: x is the concatenation of the slots' activations and row r
+//            of the virtual matrix is the concatenation of row r of every chosen
+//            expert's matrix, so the sum over the selected experts happens in the dot
+//            product itself (one pass, no partial buffers, fixed order).
+template <int U, int MINB, int MODE>
 __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ long seg_off[MODE == 2 ? kMaxExpertSegs : 1];
   float* xs = reinterpret_cast<float*>(smem_raw);          // K floats, segment-swizzled
   float* part = xs + a.K;                                    // rpc * kGemvWarps
   float* red = part + a.rpc * kGemvWarps;                    // 32
@@ -68,6 +83,19 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   const unsigned char* wb =
       reinterpret_cast<const unsigned char*>(a.w) + (size_t)r0 * a.ldw * 2 + lane * 16;
   const size_t row_bytes = (size_t)a.ldw * 2;
+  if (MODE != 0) {
+    // the expert choice is produced by the previous kernel
+    pdl_wait();
+    if (MODE == 1) {
+      wb += (size_t)a.expert_ids[blockIdx.y] * a.expert_stride * 2;
+    } else {
+      for (int k = tid; k < spr; k += kGemvThreads) {
+        const int slot = k / a.segs_per_expert, within = k - slot * a.segs_per_expert;
+        seg_off[k] = ((long)a.expert_ids[slot] * a.expert_stride + (long)within * 256) * 2;
+      }
+      __syncthreads();
+    }
+  }
 
   auto load_batch = [&](uint4* dst, int b) {
     const int f = batch_first(b);
@@ -75,7 +103,7 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
 #pragma unroll
     for (int j = 0; j < U; ++j) {
       if (f + j < s1) {
-        dst[j] = ldg_stream(wb + row * row_bytes + (size_t)k * 512);
+        dst[j] = ldg_stream(wb + row * row_bytes + (MODE == 2 ? (size_t)seg_off[k] : (size_t)k * 512));
         if (++k == spr) { k = 0; ++row; }
       }
     }
@@ -166,8 +194,9 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   if (a.epilogue == B200_EPI_SWIGLU) {
     for (int t = tid; t < (nrows >> 1); t += kGemvThreads) {
       const float g = row_value(2 * t), u = row_value(2 * t + 1);
-      const float o = silu_f(g) * u;
-      const int oi = (r0 >> 1) + t;
+      float o = silu_f(g) * u;
+      if (MODE == 1 && a.slot_scale != nullptr) o *= a.slot_scale[blockIdx.y];
+      const int oi = (r0 >> 1) + t + (MODE == 1 ? (int)blockIdx.y * (a.N >> 1) : 0);
       if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = o;
       else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(o);
     }
@@ -175,7 +204,7 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
     for (int t = tid; t < nrows; t += kGemvThreads) {
       float v = row_value(t);
       if (a.epilogue == B200_EPI_GELU) v = gelu_erf_f(v);
-      const int oi = r0 + t;
+      const int oi = r0 + t + (MODE == 1 ? (int)blockIdx.y * a.N : 0);
       if (a.resid != nullptr) {
         v += (a.resid_dtype == B200_F32)
                  ? reinterpret_cast<const float*>(a.resid)[oi]
@@ -187,10 +216,11 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   }
 }
 
-template <int U, int MINB>
-static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pdl) {
-  // MINB CTAs per SM; grow the grid in whole waves until the per-CTA row block is small
-  const int wave = MINB * kNumSMs;
+template <int U, int MINB, int MODE = 0>
+static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pdl, int n_slots = 1) {
+  // MINB CTAs per SM (shared between the routing slots in MODE 1); grow the grid in whole
+  // waves until the per-CTA row block is small
+  const int wave = (MINB * kNumSMs + n_slots - 1) / n_slots;
   int grid = wave;
   int rpc = (a.N + grid - 1) / grid;
   while (rpc > 1024) { grid += wave; rpc = (a.N + grid - 1) / grid; }
@@ -200,11 +230,11 @@ static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pd
   const size_t smem = (size_t)a.K * 4 + (size_t)rpc * kGemvWarps * 4 + 128;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemv_kernel<U, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(gemv_kernel<U, MINB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          200 * 1024);
     attr_set = true;
   }
-  return launch(gemv_kernel<U, MINB>, dim3(grid), dim3(kGemvThreads), smem, st, pdl, a);
+  return launch(gemv_kernel<U, MINB, MODE>, dim3(grid, n_slots), dim3(kGemvThreads), smem, st, pdl, a);
 }
 
 }  // namespace b200
@@ -228,6 +258,7 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   a.K = K; a.N = N; a.ldw = ldw; a.rpc = 0;
   a.x_dtype = x_dtype; a.y_dtype = y_dtype; a.resid_dtype = resid_dtype; a.epilogue = epilogue;
   a.eps = eps;
+  a.expert_ids = nullptr; a.slot_scale = nullptr; a.expert_stride = 0; a.segs_per_expert = 0;
   const bool sw = epilogue == B200_EPI_SWIGLU;
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;
@@ -237,5 +268,52 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
     case 2: e = gemv_launch<4, 3>(a, sw, st, pdl); break;
     default: e = gemv_launch<8, 2>(a, sw, st, pdl); break;
   }
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+/* Decode-time expert MLP, first half: for each of the top_k routing slots
+ *   act[slot, j] = wt[slot] * silu(g_j) * u_j,   (g, u) = rows (2j, 2j+1) of w_gu[ids[slot]] . xn
+ * with xn = x or rmsnorm(x) * norm_w. */
+extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, const void* norm_w,
+                                       float eps, const void* w_gu, const int* ids,
+                                       const float* wts, int top_k, int inter, int hidden,
+                                       int flags, b200_stream_t stream) {
+  if (!act || !x || !w_gu || !ids) return B200_ERR_ARG;
+  if (top_k <= 0 || inter <= 0 || hidden <= 0 || (hidden & 255) != 0 || hidden > 32768)
+    return B200_ERR_SHAPE;
+  if (((uintptr_t)w_gu & 15) != 0 || ((uintptr_t)x & 15) != 0) return B200_ERR_ALIGN;
+  GemvArgs a;
+  a.x = x; a.w = (const uint16_t*)w_gu; a.y = act; a.norm_w = (const uint16_t*)norm_w;
+  a.bias = nullptr; a.resid = nullptr;
+  a.K = hidden; a.N = 2 * inter; a.ldw = hidden; a.rpc = 0;
+  a.x_dtype = x_dtype; a.y_dtype = B200_F32; a.resid_dtype = 0; a.epilogue = B200_EPI_SWIGLU;
+  a.eps = eps;
+  a.expert_ids = ids; a.slot_scale = wts; a.expert_stride = (long)2 * inter * hidden;
+  a.segs_per_expert = 0;
+  cudaError_t e = gemv_launch<8, 2, 1>(a, true, (cudaStream_t)stream,
+                                       (flags & B200_FLAG_PDL) != 0, top_k);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+/* Decode-time expert MLP, second half: y[d] = (resid[d] +) sum_slot w_down[ids[slot]][d, :] . act[slot, :]. */
+extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const void* w_down,
+                                    const int* ids, int top_k, int inter, int hidden,
+                                    const void* resid, int resid_dtype, int flags,
+                                    b200_stream_t stream) {
+  if (!y || !act || !w_down || !ids) return B200_ERR_ARG;
+  if (top_k <= 0 || inter <= 0 || hidden <= 0 || (inter & 255) != 0) return B200_ERR_SHAPE;
+  const int segs = inter >> 8;
+  if (top_k * segs > kMaxExpertSegs || (long)top_k * inter > 32768) return B200_ERR_SHAPE;
+  if (((uintptr_t)w_down & 15) != 0 || ((uintptr_t)act & 15) != 0) return B200_ERR_ALIGN;
+  GemvArgs a;
+  a.x = act; a.w = (const uint16_t*)w_down; a.y = y; a.norm_w = nullptr; a.bias = nullptr;
+  a.resid = resid;
+  a.K = top_k * inter; a.N = hidden; a.ldw = inter; a.rpc = 0;
+  a.x_dtype = B200_F32; a.y_dtype = y_dtype; a.resid_dtype = resid_dtype; a.epilogue = B200_EPI_NONE;
+  a.eps = 0.f;
+  a.expert_ids = ids; a.slot_scale = nullptr; a.expert_stride = (long)hidden * inter;
+  a.segs_per_expert = segs;
+  cudaError_t e = gemv_launch<8, 2, 2>(a, false, (cudaStream_t)stream,
+                                       (flags & B200_FLAG_PDL) != 0);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
