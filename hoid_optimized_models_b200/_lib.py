@@ -38,9 +38,16 @@ SIGNATURES = {
                                 _f, _i, _p]),
     "b200_flash_decode_workspace_bytes": (_l, [_i, _i, _i, _i]),
     "b200_flash_decode": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _l, _l, _i, _f, _i, _p]),
-    "b200_gemm_bf16": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _i, _p]),
+    "b200_gemm_bf16": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _i, _p]),
     "b200_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),
     "b200_flash_prefill": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_i, _f, _i, _p]),
+    "b200_moe_router": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_moe_permute_workspace_bytes": (_l, [_i, _i]),
+    "b200_moe_permute": (_i, [_p, _p, _p, _p, _i, _i, _p, _i, _p]),
+    "b200_moe_gather_rows": (_i, [_p, _p, _p, _i, _i, _i, _i, _p]),
+    "b200_moe_combine": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_moe_decode_gate_up": (_i, [_p, _p, _i, _p, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_moe_decode_down": (_i, [_p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _p]),
     "b200_embed_gather": (_i, [_p, _i, _p, _p, _i, _i, _i, _p]),
     "b200_silu_mul": (_i, [_p, _p, _p, _l, _i, _p]),
     "b200_argmax_workspace_bytes": (_l, [_i]),

@@ -36,7 +36,7 @@ constexpr long long kWaitBudget = 4000000000LL;  // clock64 ticks (~2 s)
 struct GemmArgs {
   uint16_t* y; const uint16_t* bias; const uint16_t* resid; const int* offsets;
   int* status;
-  int M, N, K, ldy, ldr, epilogue, n_groups;
+  int M, N, K, ldy, ldr, epilogue, n_groups, y_dtype;
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -330,7 +330,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
           }
-          if (row_ok) {
+          if (row_ok && a.y_dtype == B200_F32) {
+            float* dst = reinterpret_cast<float*>(a.y) + (size_t)row * a.ldy + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col0 + j < a.N)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+          } else if (row_ok) {
             uint16_t* dst = a.y + (size_t)row * a.ldy + col0;
             const uint16_t* rs = a.resid ? a.resid + (size_t)row * a.ldr + col0 : nullptr;
 #pragma unroll
@@ -399,8 +406,8 @@ static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t col
 
 constexpr size_t kGemmSmem = 1024 + (size_t)kStages * kStageBytes + 256 + 2 * (kMaxExperts + 1) * 4;
 
-static int gemm_launch(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldw,
-                       int ldy, const void* bias, const void* resid, int ldr, int epilogue,
+static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
+                       int ldx, int ldw, int ldy, const void* bias, const void* resid, int ldr, int epilogue,
                        const int* offsets, int n_groups, int max_tiles_m, int* status, int flags,
                        cudaStream_t stream) {
   if (!x || !w || !y) return B200_ERR_ARG;
@@ -411,6 +418,7 @@ static int gemm_launch(const void* x, const void* w, void* y, int M, int N, int 
     return B200_ERR_ALIGN;
   if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_GELU) return B200_ERR_ARG;
   if (epilogue == B200_EPI_SWIGLU && (resid != nullptr || (N & 15))) return B200_ERR_SHAPE;
+  if (y_dtype == B200_F32 && (resid != nullptr || epilogue == B200_EPI_SWIGLU)) return B200_ERR_ARG;
   if (n_groups < 0 || n_groups > kMaxExperts || (n_groups > 0 && !offsets)) return B200_ERR_ARG;
   int rc = get_encode();
   if (rc != B200_OK) return rc;
@@ -424,6 +432,7 @@ static int gemm_launch(const void* x, const void* w, void* y, int M, int N, int 
   a.y = (uint16_t*)y; a.bias = (const uint16_t*)bias; a.resid = (const uint16_t*)resid;
   a.offsets = offsets; a.status = status;
   a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.ldr = ldr; a.epilogue = epilogue; a.n_groups = n_groups;
+  a.y_dtype = y_dtype;
 
   const int nt = (N + BN - 1) / BN;
   long tiles = (long)max_tiles_m * nt;
@@ -446,11 +455,11 @@ static int gemm_launch(const void* x, const void* w, void* y, int M, int N, int 
 
 using namespace b200;
 
-extern "C" int b200_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K,
+extern "C" int b200_gemm_bf16(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                               int ldx, int ldw, int ldy, const void* bias, const void* resid,
                               int ldr, int epilogue, int* status, int flags,
                               b200_stream_t stream) {
-  return gemm_launch(x, w, y, M, N, K, ldx, ldw, ldy, bias, resid, ldr, epilogue, nullptr, 0,
+  return gemm_launch(x, w, y, y_dtype, M, N, K, ldx, ldw, ldy, bias, resid, ldr, epilogue, nullptr, 0,
                      (M + BM - 1) / BM, status, flags, (cudaStream_t)stream);
 }
 
@@ -460,6 +469,6 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, void* y, cons
   if (n_experts <= 0) return B200_ERR_ARG;
   // upper bound on M-tiles: every expert may add one partial tile
   const int max_tiles_m = (rows + BM - 1) / BM + n_experts;
-  return gemm_launch(x, w, y, rows, N, K, ldx, K, ldy, nullptr, nullptr, 0, epilogue, offsets,
+  return gemm_launch(x, w, y, B200_BF16, rows, N, K, ldx, K, ldy, nullptr, nullptr, 0, epilogue, offsets,
                      n_experts, max_tiles_m, status, flags, (cudaStream_t)stream);
 }

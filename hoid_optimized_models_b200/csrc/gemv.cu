@@ -35,6 +35,7 @@ struct GemvArgs {
   const float* slot_scale;   // [n_slots] routing weight folded into the SwiGLU output (MODE 1)
   long expert_stride;        // elements between consecutive experts' matrices
   int segs_per_expert;       // MODE 2: 256-element segments of one expert's K range
+  int expert_lo, n_local;    // experts [expert_lo, expert_lo + n_local) live in w (expert parallel)
 };
 
 constexpr int kMaxExpertSegs = 256;
@@ -87,11 +88,20 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
     // the expert choice is produced by the previous kernel
     pdl_wait();
     if (MODE == 1) {
-      wb += (size_t)a.expert_ids[blockIdx.y] * a.expert_stride * 2;
+      const int e = a.expert_ids[blockIdx.y] - a.expert_lo;
+      if (e < 0 || e >= a.n_local) {
+        // the slot's expert lives on another rank: its activations are zero here
+        float* o = reinterpret_cast<float*>(a.y) + (size_t)blockIdx.y * (a.N >> 1) + (r0 >> 1);
+        for (int t = tid; t < (nrows >> 1); t += kGemvThreads) o[t] = 0.f;
+        return;
+      }
+      wb += (size_t)e * a.expert_stride * 2;
     } else {
       for (int k = tid; k < spr; k += kGemvThreads) {
         const int slot = k / a.segs_per_expert, within = k - slot * a.segs_per_expert;
-        seg_off[k] = ((long)a.expert_ids[slot] * a.expert_stride + (long)within * 256) * 2;
+        const int e = a.expert_ids[slot] - a.expert_lo;
+        seg_off[k] = (e < 0 || e >= a.n_local)
+                         ? -1 : ((long)e * a.expert_stride + (long)within * 256) * 2;
       }
       __syncthreads();
     }
@@ -103,7 +113,12 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
 #pragma unroll
     for (int j = 0; j < U; ++j) {
       if (f + j < s1) {
-        dst[j] = ldg_stream(wb + row * row_bytes + (MODE == 2 ? (size_t)seg_off[k] : (size_t)k * 512));
+        if (MODE == 2) {
+          const long off = seg_off[k];
+          dst[j] = off < 0 ? make_uint4(0, 0, 0, 0) : ldg_stream(wb + row * row_bytes + off);
+        } else {
+          dst[j] = ldg_stream(wb + row * row_bytes + (size_t)k * 512);
+        }
         if (++k == spr) { k = 0; ++row; }
       }
     }
@@ -259,6 +274,7 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   a.x_dtype = x_dtype; a.y_dtype = y_dtype; a.resid_dtype = resid_dtype; a.epilogue = epilogue;
   a.eps = eps;
   a.expert_ids = nullptr; a.slot_scale = nullptr; a.expert_stride = 0; a.segs_per_expert = 0;
+  a.expert_lo = 0; a.n_local = 0;
   const bool sw = epilogue == B200_EPI_SWIGLU;
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;
@@ -277,7 +293,8 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
 extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, const void* norm_w,
                                        float eps, const void* w_gu, const int* ids,
                                        const float* wts, int top_k, int inter, int hidden,
-                                       int flags, b200_stream_t stream) {
+                                       int expert_lo, int n_local, int flags,
+                                       b200_stream_t stream) {
   if (!act || !x || !w_gu || !ids) return B200_ERR_ARG;
   if (top_k <= 0 || inter <= 0 || hidden <= 0 || (hidden & 255) != 0 || hidden > 32768)
     return B200_ERR_SHAPE;
@@ -289,7 +306,7 @@ extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, co
   a.x_dtype = x_dtype; a.y_dtype = B200_F32; a.resid_dtype = 0; a.epilogue = B200_EPI_SWIGLU;
   a.eps = eps;
   a.expert_ids = ids; a.slot_scale = wts; a.expert_stride = (long)2 * inter * hidden;
-  a.segs_per_expert = 0;
+  a.segs_per_expert = 0; a.expert_lo = expert_lo; a.n_local = n_local;
   cudaError_t e = gemv_launch<8, 2, 1>(a, true, (cudaStream_t)stream,
                                        (flags & B200_FLAG_PDL) != 0, top_k);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
@@ -298,6 +315,7 @@ extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, co
 /* Decode-time expert MLP, second half: y[d] = (resid[d] +) sum_slot w_down[ids[slot]][d, :] . act[slot, :]. */
 extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const void* w_down,
                                     const int* ids, int top_k, int inter, int hidden,
+                                    int expert_lo, int n_local,
                                     const void* resid, int resid_dtype, int flags,
                                     b200_stream_t stream) {
   if (!y || !act || !w_down || !ids) return B200_ERR_ARG;
@@ -312,7 +330,7 @@ extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const
   a.x_dtype = B200_F32; a.y_dtype = y_dtype; a.resid_dtype = resid_dtype; a.epilogue = B200_EPI_NONE;
   a.eps = 0.f;
   a.expert_ids = ids; a.slot_scale = nullptr; a.expert_stride = (long)hidden * inter;
-  a.segs_per_expert = segs;
+  a.segs_per_expert = segs; a.expert_lo = expert_lo; a.n_local = n_local;
   cudaError_t e = gemv_launch<8, 2, 2>(a, false, (cudaStream_t)stream,
                                        (flags & B200_FLAG_PDL) != 0);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;

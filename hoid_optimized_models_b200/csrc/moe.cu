@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(uint4* xg, const uint4*
 // out[t, :] = (resid[t, :] +) sum_slot w[t, slot] * y[inv[t * top_k + slot], :]   (fp32 sum, slot order)
 __global__ void __launch_bounds__(256) moe_combine_kernel(uint4* out, const uint4* y, const int* inv,
                                                           const float* w, const uint4* resid,
+                                                          const int* ids, int expert_lo, int n_local,
                                                           int tokens, int top_k, int cpr) {
   pdl_launch_dependents();
   pdl_wait();
@@ -174,6 +175,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(uint4* out, const uint
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
     if (resid != nullptr) unpack8(resid[i], acc);
     for (int k = 0; k < top_k; ++k) {
+      if (ids != nullptr) {   // expert parallel: rows of experts held elsewhere were not computed
+        const int e = ids[(size_t)t * top_k + k] - expert_lo;
+        if (e < 0 || e >= n_local) continue;
+      }
       const float wk = w[(size_t)t * top_k + k];
       float f[8];
       unpack8(y[(size_t)inv[(size_t)t * top_k + k] * cpr + c], f);
@@ -242,8 +247,8 @@ extern "C" int b200_moe_gather_rows(void* xg, const void* x, const int* order, i
 }
 
 extern "C" int b200_moe_combine(void* out, const void* y, const int* inv, const float* wts,
-                                const void* resid, int tokens, int top_k, int H, int flags,
-                                b200_stream_t stream) {
+                                const void* resid, const int* ids, int expert_lo, int n_local,
+                                int tokens, int top_k, int H, int flags, b200_stream_t stream) {
   if (!out || !y || !inv || !wts) return B200_ERR_ARG;
   if (tokens <= 0 || top_k <= 0 || H <= 0 || (H & 7) != 0) return B200_ERR_SHAPE;
   const long total = (long)tokens * (H >> 3);
@@ -251,6 +256,6 @@ extern "C" int b200_moe_combine(void* out, const void* y, const int* inv, const 
   if (grid > kNumSMs * 16) grid = kNumSMs * 16;
   cudaError_t e = launch(moe_combine_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream,
                          (flags & B200_FLAG_PDL) != 0, (uint4*)out, (const uint4*)y, inv, wts,
-                         (const uint4*)resid, tokens, top_k, H >> 3);
+                         (const uint4*)resid, ids, expert_lo, n_local, tokens, top_k, H >> 3);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }

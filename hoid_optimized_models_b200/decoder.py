@@ -44,19 +44,26 @@ class DenseDecoder:
                  device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None,
                  n_splits: Optional[int] = None, max_new_tokens: int = 1024,
                  free_source_weights: bool = False):
-        if cfg.n_experts:
-            raise ValueError("use MoeDecoder for mixture-of-experts configurations")
-        if cfg.n_kv % tp_size or cfg.n_q % tp_size or cfg.inter % tp_size or cfg.vocab % tp_size:
+        self.moe = cfg.n_experts > 0
+        if self.moe:
+            # expert parallelism: attention is replicated, experts are sharded
+            if cfg.n_experts % tp_size:
+                raise ValueError("expert-parallel size must divide the number of experts")
+        elif cfg.n_kv % tp_size or cfg.n_q % tp_size or cfg.inter % tp_size or cfg.vocab % tp_size:
             raise ValueError("tensor-parallel size must divide heads, intermediate and vocab")
         self.cfg, self.device, self.max_seq = cfg, torch.device(device), max_seq
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
         H, hd = cfg.hidden, cfg.head_dim
-        self.n_q, self.n_kv = cfg.n_q // tp_size, cfg.n_kv // tp_size
+        att_tp = 1 if self.moe else tp_size          # heads are sharded only for dense models
+        self.att_tp = att_tp
+        self.n_q, self.n_kv = cfg.n_q // att_tp, cfg.n_kv // att_tp
         self.q_size, self.kv_size = self.n_q * hd, self.n_kv * hd
-        self.inter = cfg.inter // tp_size
-        self.vocab_local = cfg.vocab // tp_size
+        self.inter = cfg.inter // att_tp
+        self.vocab_local = cfg.vocab // att_tp
         self.scale = hd ** -0.5
-        r = tp_rank
+        r = tp_rank if att_tp > 1 else 0
+        self.n_local_experts = cfg.n_experts // tp_size if self.moe else 0
+        self.expert_lo = tp_rank * self.n_local_experts
         dev = self.device
 
         def take(name):
@@ -68,7 +75,7 @@ class DenseDecoder:
 
         self.embed = take("model.embed_tokens.weight").to(dev)
         head = self.embed if cfg.tied else take("lm_head.weight").to(dev)
-        self.lm_head = rows(head, self.vocab_local).contiguous() if tp_size > 1 else head
+        self.lm_head = rows(head, self.vocab_local).contiguous() if att_tp > 1 else head
         self.final_norm_w = take("model.norm.weight").to(dev)
         self.ln1: List[torch.Tensor] = []
         self.ln2: List[torch.Tensor] = []
@@ -76,6 +83,7 @@ class DenseDecoder:
         self.wo: List[torch.Tensor] = []
         self.wgu: List[torch.Tensor] = []
         self.wd: List[torch.Tensor] = []
+        self.w_router: List[torch.Tensor] = []
         self.qn: List[Optional[torch.Tensor]] = []
         self.kn: List[Optional[torch.Tensor]] = []
         for i in range(cfg.layers):
@@ -88,11 +96,22 @@ class DenseDecoder:
             self.wqkv.append(torch.cat((q, k, v), dim=0).to(dev).contiguous())
             o = take(p + "self_attn.o_proj.weight")
             self.wo.append(o[:, r * self.q_size:(r + 1) * self.q_size].to(dev).contiguous())
-            g = rows(take(p + "mlp.gate_proj.weight"), self.inter)
-            u = rows(take(p + "mlp.up_proj.weight"), self.inter)
-            self.wgu.append(_interleave_rows(g.to(dev), u.to(dev)))
-            d = take(p + "mlp.down_proj.weight")
-            self.wd.append(d[:, r * self.inter:(r + 1) * self.inter].to(dev).contiguous())
+            if self.moe:
+                lo, hi = self.expert_lo, self.expert_lo + self.n_local_experts
+                self.w_router.append(take(p + "mlp.gate.weight").to(dev))
+                gu = take(p + "mlp.experts.gate_up_proj")[lo:hi].to(dev)   # [E, 2I, H], gate rows first
+                I = cfg.moe_inter
+                # load-time repack: interleave gate/up rows so that both the decode GEMV and
+                # the grouped GEMM can apply SwiGLU to adjacent outputs
+                self.wgu.append(torch.stack((gu[:, :I], gu[:, I:]), dim=2)
+                                .reshape(self.n_local_experts, 2 * I, H).contiguous())
+                self.wd.append(take(p + "mlp.experts.down_proj")[lo:hi].to(dev).contiguous())
+            else:
+                g = rows(take(p + "mlp.gate_proj.weight"), self.inter)
+                u = rows(take(p + "mlp.up_proj.weight"), self.inter)
+                self.wgu.append(_interleave_rows(g.to(dev), u.to(dev)))
+                d = take(p + "mlp.down_proj.weight")
+                self.wd.append(d[:, r * self.inter:(r + 1) * self.inter].to(dev).contiguous())
             if cfg.qk_norm:
                 self.qn.append(take(p + "self_attn.q_norm.weight").to(dev))
                 self.kn.append(take(p + "self_attn.k_norm.weight").to(dev))
@@ -115,7 +134,11 @@ class DenseDecoder:
         self.qkv = f32(self.q_size + 2 * self.kv_size)
         self.q = f32(self.q_size)
         self.attn = f32(self.q_size)
-        self.act = f32(self.inter)
+        self.act = f32(cfg.top_k * cfg.moe_inter if self.moe else self.inter)
+        if self.moe:
+            self.router_logits = f32(cfg.n_experts)
+            self.topk_ids = torch.zeros(cfg.top_k, dtype=torch.int32, device=dev)
+            self.topk_w = f32(cfg.top_k)
         self.logits = f32(self.vocab_local)
         self.cand = f32(2)
         self.cand_all = f32(tp_size, 2)
@@ -126,7 +149,7 @@ class DenseDecoder:
         self.am_ws = ops.argmax_workspace(dev)
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.launches_per_step = 1 + 6 * cfg.layers + 3
+        self.launches_per_step = 1 + (8 if self.moe else 6) * cfg.layers + 3
 
     # ------------------------------------------------------------------ collectives
     def _all_reduce(self, t: torch.Tensor) -> None:
@@ -138,7 +161,8 @@ class DenseDecoder:
         """One decode step for the token in self.tok at position self.pos (device state).
         `collect` (eager only) receives a copy of the residual stream after every layer."""
         cfg = self.cfg
-        tp = self.tp_size > 1
+        tp = self.att_tp > 1
+        ep = self.moe and self.tp_size > 1
         lead = self.tp_rank == 0
         ops.embed_gather(self.h, self.embed, self.tok)
         h, h2 = self.h, self.h2
@@ -155,24 +179,42 @@ class DenseDecoder:
                 h, h2 = h2, h
             else:
                 ops.gemv(h, self.attn, self.wo[i], resid=h)
-            ops.gemv(self.act, h, self.wgu[i], norm_w=self.ln2[i], eps=cfg.eps, epilogue=EPI_SWIGLU)
-            if tp:
-                ops.gemv(h2, self.act, self.wd[i], resid=h if lead else None)
-                self._all_reduce(h2)
-                h, h2 = h2, h
+            if self.moe:
+                ops.gemv(self.router_logits, h, self.w_router[i], norm_w=self.ln2[i], eps=cfg.eps)
+                ops.moe_router(self.topk_ids, self.topk_w, self.router_logits.view(1, -1))
+                ops.moe_decode_gate_up(self.act, h, self.wgu[i], self.topk_ids, self.topk_w,
+                                       norm_w=self.ln2[i], eps=cfg.eps,
+                                       expert_lo=self.expert_lo)
+                if ep:
+                    ops.moe_decode_down(h2, self.act, self.wd[i], self.topk_ids,
+                                        resid=h if lead else None, expert_lo=self.expert_lo)
+                    self._all_reduce(h2)
+                    h, h2 = h2, h
+                else:
+                    ops.moe_decode_down(h, self.act, self.wd[i], self.topk_ids, resid=h)
             else:
-                ops.gemv(h, self.act, self.wd[i], resid=h)
+                ops.gemv(self.act, h, self.wgu[i], norm_w=self.ln2[i], eps=cfg.eps,
+                         epilogue=EPI_SWIGLU)
+                if tp:
+                    ops.gemv(h2, self.act, self.wd[i], resid=h if lead else None)
+                    self._all_reduce(h2)
+                    h, h2 = h2, h
+                else:
+                    ops.gemv(h, self.act, self.wd[i], resid=h)
             if collect is not None:
                 collect.append(h.clone())
+        if h is not self.h:                      # odd number of buffer swaps (expert parallel)
+            self.h.copy_(h)
+            h = self.h
         ops.gemv(self.logits, h, self.lm_head, norm_w=self.final_norm_w, eps=cfg.eps)
-        ops.argmax(self.cand, self.logits, self.am_ws, idx_base=self.tp_rank * self.vocab_local)
+        ops.argmax(self.cand, self.logits, self.am_ws,
+                   idx_base=(self.tp_rank * self.vocab_local) if tp else 0)
         if tp:
             torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2),
                                                      group=self.group)
             ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand_all)
         else:
             ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
-        # an even number of buffer swaps per layer keeps the residual stream in self.h
 
     def capture(self, warmup: int = 3) -> None:
         """Warm up on a side stream, then record step_static into one CUDA graph.  The step state
@@ -217,23 +259,60 @@ class DenseDecoder:
                 "ids": torch.zeros(P, dtype=torch.int32, device=self.device),
                 "x": bf(P, H), "hn": bf(P, H), "part": bf(P, H),
                 "qkv": bf(P, self.q_size + 2 * self.kv_size), "q": bf(P, self.q_size),
-                "att": bf(P, self.q_size), "act": bf(P, self.inter),
+                "att": bf(P, self.q_size), "act": bf(P, max(self.inter, 8)),
                 "pos0": torch.zeros(1, dtype=torch.int32, device=self.device),
+                **self._moe_prefill_buffers(P),
                 "last": torch.zeros(H, dtype=torch.float32, device=self.device),
             }
         return self._pbuf[P]
 
+    def _moe_prefill_buffers(self, P: int) -> Dict[str, torch.Tensor]:
+        if not self.moe:
+            return {}
+        cfg, dev = self.cfg, self.device
+        pairs = P * cfg.top_k
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
+        return {
+            "rlogits": torch.empty(P, cfg.n_experts, dtype=torch.float32, device=dev),
+            "eids": i32(P, cfg.top_k), "ew": torch.empty(P, cfg.top_k, dtype=torch.float32, device=dev),
+            "order": i32(pairs), "inv": i32(pairs), "offs": i32(cfg.n_experts + 1),
+            "pws": ops.moe_permute_workspace(pairs, cfg.n_experts, dev),
+            "xg": bf(pairs, cfg.hidden), "eact": bf(pairs, cfg.moe_inter), "ey": bf(pairs, cfg.hidden),
+        }
+
+    def _moe_prefill(self, e: Dict[str, torch.Tensor], x: torch.Tensor, hn: torch.Tensor, i: int) -> None:
+        """x += sum over the routed experts (this rank's share under expert parallelism)."""
+        cfg = self.cfg
+        ops.gemm(e["rlogits"], hn, self.w_router[i])
+        ops.moe_router(e["eids"], e["ew"], e["rlogits"])
+        ops.moe_permute(e["order"], e["inv"], e["offs"], e["pws"], e["eids"])
+        ops.moe_gather_rows(e["xg"], hn, e["order"], cfg.top_k)
+        lo, n = self.expert_lo, self.n_local_experts
+        offs = e["offs"][lo:lo + n + 1]
+        ops.moe_grouped_gemm(e["eact"], e["xg"], self.wgu[i], offs, epilogue=EPI_SWIGLU)
+        ops.moe_grouped_gemm(e["ey"], e["eact"], self.wd[i], offs)
+        if self.tp_size > 1:
+            part = e["part"]
+            ops.moe_combine(part, e["ey"], e["inv"], e["ew"], None, e["eids"], lo, n)
+            self._all_reduce(part)
+        else:
+            ops.moe_combine(x, e["ey"], e["inv"], e["ew"], x)
+
     @torch.no_grad()
-    def prefill(self, ids: torch.Tensor, collect: Optional[list] = None) -> int:
+    def prefill(self, ids: torch.Tensor, collect: Optional[list] = None,
+                collect_router: Optional[list] = None) -> int:
         """Runs the prompt, fills the KV cache and returns the first generated token.
-        `collect` receives a copy of the residual stream after every layer."""
+        `collect` receives a copy of the residual stream after every layer, `collect_router`
+        the expert ids [P, top_k] every MoE layer chose."""
         cfg = self.cfg
         P = ids.numel()
         if P + 1 > self.max_seq:
             raise ValueError("prompt too long for this cache")
         e = self._prefill_buffers(P)
         e["ids"].copy_(ids.to(torch.int32))
-        tp = self.tp_size > 1
+        tp = self.att_tp > 1
+        ep = self.moe and self.tp_size > 1
         hd = cfg.head_dim
         x, hn, part = e["x"], e["hn"], e["part"]
         ops.embed_gather(x, self.embed, e["ids"])
@@ -252,20 +331,30 @@ class DenseDecoder:
             else:
                 ops.gemm(x, e["att"], self.wo[i], resid=x)
                 ops.rmsnorm(hn, x, self.ln2[i], cfg.eps)
-            ops.gemm(e["act"], hn, self.wgu[i], epilogue=EPI_SWIGLU)
             nw = self.ln1[i + 1] if i + 1 < cfg.layers else self.final_norm_w
-            if tp:
-                ops.gemm(part, e["act"], self.wd[i])
-                self._all_reduce(part)
-                ops.add_rmsnorm(hn, x, x, part, nw, cfg.eps)
+            if self.moe:
+                self._moe_prefill(e, x, hn, i)
+                if ep:
+                    ops.add_rmsnorm(hn, x, x, part, nw, cfg.eps)
+                else:
+                    ops.rmsnorm(hn, x, nw, cfg.eps)
             else:
-                ops.gemm(x, e["act"], self.wd[i], resid=x)
-                ops.rmsnorm(hn, x, nw, cfg.eps)
+                ops.gemm(e["act"], hn, self.wgu[i], epilogue=EPI_SWIGLU)
+                if tp:
+                    ops.gemm(part, e["act"], self.wd[i])
+                    self._all_reduce(part)
+                    ops.add_rmsnorm(hn, x, x, part, nw, cfg.eps)
+                else:
+                    ops.gemm(x, e["act"], self.wd[i], resid=x)
+                    ops.rmsnorm(hn, x, nw, cfg.eps)
             if collect is not None:
                 collect.append(x.clone())
+            if collect_router is not None and self.moe:
+                collect_router.append(e["eids"].clone())
         # hn now holds the final-norm output; project the last position only
         ops.gemv(self.logits, hn[P - 1], self.lm_head)
-        ops.argmax(self.cand, self.logits, self.am_ws, idx_base=self.tp_rank * self.vocab_local)
+        ops.argmax(self.cand, self.logits, self.am_ws,
+                   idx_base=(self.tp_rank * self.vocab_local) if tp else 0)
         if tp:
             torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2),
                                                      group=self.group)

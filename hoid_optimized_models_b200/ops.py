@@ -207,7 +207,7 @@ def check_status(device) -> None:
 def gemm(y: Tensor, x: Tensor, w: Tensor, bias: Optional[Tensor] = None,
          resid: Optional[Tensor] = None, epilogue: int = EPI_NONE) -> None:
     """y[M, N] = x[M, K] w[N, K]^T (+ bias) (+ resid) with optional SwiGLU / GELU epilogue."""
-    for t, n in ((y, "y"), (x, "x"), (w, "w"), (bias, "bias"), (resid, "resid")):
+    for t, n in ((x, "x"), (w, "w"), (bias, "bias"), (resid, "resid")):
         _bf16(t, n)
     M, K = x.shape
     N = w.shape[0]
@@ -219,7 +219,7 @@ def gemm(y: Tensor, x: Tensor, w: Tensor, bias: Optional[Tensor] = None,
     if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
         raise RuntimeError("innermost dimensions must be contiguous")
     check(_lib.lib().b200_gemm_bf16(
-        x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0), w.stride(0), y.stride(0),
+        x.data_ptr(), w.data_ptr(), y.data_ptr(), _dt(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
         _ptr(bias), resid.data_ptr() if resid is not None else None,
         resid.stride(0) if resid is not None else 0, epilogue,
         status_word(x.device).data_ptr(), _flags(), _stream()), "b200_gemm_bf16")
@@ -238,6 +238,80 @@ def moe_grouped_gemm(y: Tensor, x: Tensor, w: Tensor, offsets: Tensor,
     check(_lib.lib().b200_moe_grouped_gemm(
         _ptr(x), _ptr(w), _ptr(y), _ptr(offsets), E, rows, N, K, x.stride(0), y.stride(0),
         epilogue, status_word(x.device).data_ptr(), _flags(), _stream()), "b200_moe_grouped_gemm")
+
+
+# ----------------------------------------------------------------------------- MoE
+@torch.library.custom_op("b200::moe_router", mutates_args=("ids", "wts"))
+def moe_router(ids: Tensor, wts: Tensor, logits: Tensor, round_bf16: bool = False) -> None:
+    """ids int32 [s, k], wts fp32 [s, k] = top-k of softmax(logits [s, E]), renormalised."""
+    if ids.dtype != torch.int32 or wts.dtype != torch.float32:
+        raise TypeError("ids must be int32 and wts float32")
+    s, E = logits.shape[-2] if logits.dim() > 1 else 1, logits.shape[-1]
+    k = ids.numel() // s
+    check(_lib.lib().b200_moe_router(_ptr(ids), _ptr(wts), _ptr(logits), _dt(logits), s, E, k,
+                                     1 if round_bf16 else 0, _flags(), _stream()), "b200_moe_router")
+
+
+def moe_permute_workspace(pairs: int, E: int, device) -> Tensor:
+    n = _lib.lib().b200_moe_permute_workspace_bytes(pairs, E)
+    return torch.zeros((n + 3) // 4, dtype=torch.int32, device=device)
+
+
+@torch.library.custom_op("b200::moe_permute", mutates_args=("order", "inv", "offsets", "workspace"))
+def moe_permute(order: Tensor, inv: Tensor, offsets: Tensor, workspace: Tensor, ids: Tensor) -> None:
+    """Stable expert-major sort of the flattened (token, slot) pairs; offsets is int32 [E + 1]."""
+    for t in (order, inv, offsets, ids):
+        if t.dtype != torch.int32:
+            raise TypeError("moe_permute works on int32 tensors")
+    check(_lib.lib().b200_moe_permute(_ptr(order), _ptr(inv), _ptr(offsets), _ptr(ids), ids.numel(),
+                                      offsets.numel() - 1, _ptr(workspace), _flags(), _stream()),
+          "b200_moe_permute")
+
+
+@torch.library.custom_op("b200::moe_gather_rows", mutates_args=("xg",))
+def moe_gather_rows(xg: Tensor, x: Tensor, order: Tensor, top_k: int) -> None:
+    _bf16(xg, "xg"); _bf16(x, "x")
+    check(_lib.lib().b200_moe_gather_rows(_ptr(xg), _ptr(x), _ptr(order), order.numel(), top_k,
+                                          x.shape[-1], _flags(), _stream()), "b200_moe_gather_rows")
+
+
+@torch.library.custom_op("b200::moe_combine", mutates_args=("out",))
+def moe_combine(out: Tensor, y: Tensor, inv: Tensor, wts: Tensor,
+                resid: Optional[Tensor] = None, ids: Optional[Tensor] = None,
+                expert_lo: int = 0, n_local: int = 0) -> None:
+    """out[t] = (resid[t] +) sum_slot wts[t, slot] * y[inv[t, slot]]; out may alias resid.
+    With ids, only pairs routed to experts [expert_lo, expert_lo + n_local) are summed."""
+    _bf16(out, "out"); _bf16(y, "y"); _bf16(resid, "resid")
+    tokens, top_k = wts.shape
+    check(_lib.lib().b200_moe_combine(_ptr(out), _ptr(y), _ptr(inv), _ptr(wts), _ptr(resid),
+                                      _ptr(ids), expert_lo, n_local, tokens, top_k, y.shape[-1], _flags(), _stream()), "b200_moe_combine")
+
+
+@torch.library.custom_op("b200::moe_decode_gate_up", mutates_args=("act",))
+def moe_decode_gate_up(act: Tensor, x: Tensor, w_gu: Tensor, ids: Tensor, wts: Tensor,
+                       norm_w: Optional[Tensor] = None, eps: float = 0.0,
+                       expert_lo: int = 0) -> None:
+    """act[slot, j] = wts[slot] * silu(gate_j) * up_j for the experts ids[slot]; w_gu is
+    [E, 2I, H] with interleaved gate/up rows."""
+    _bf16(w_gu, "w_gu"); _bf16(norm_w, "norm_w")
+    E, two_i, H = w_gu.shape
+    if act.dtype != torch.float32:
+        raise TypeError("act must be float32")
+    check(_lib.lib().b200_moe_decode_gate_up(
+        _ptr(act), _ptr(x), _dt(x), _ptr(norm_w), eps, _ptr(w_gu), _ptr(ids), _ptr(wts),
+        ids.numel(), two_i // 2, H, expert_lo, E, _flags(), _stream()), "b200_moe_decode_gate_up")
+
+
+@torch.library.custom_op("b200::moe_decode_down", mutates_args=("y",))
+def moe_decode_down(y: Tensor, act: Tensor, w_down: Tensor, ids: Tensor,
+                    resid: Optional[Tensor] = None, expert_lo: int = 0) -> None:
+    """y[d] = (resid[d] +) sum_slot w_down[ids[slot]][d] . act[slot]; w_down is [E, H, I]."""
+    _bf16(w_down, "w_down")
+    E, H, I = w_down.shape
+    check(_lib.lib().b200_moe_decode_down(
+        _ptr(y), _dt(y), _ptr(act), _ptr(w_down), _ptr(ids), ids.numel(), I, H, expert_lo, E,
+        _ptr(resid),
+        _dt(resid) if resid is not None else 0, _flags(), _stream()), "b200_moe_decode_down")
 
 
 # ----------------------------------------------------------------------------- flash prefill

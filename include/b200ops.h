@@ -153,7 +153,8 @@ int b200_flash_decode(void* out, int out_dtype, const void* q, int q_dtype,
 
 /* ---------------------------------------------------------------------------
  * a2. Prefill / encoder GEMM  Y[M,N] = X[M,K] W[N,K]^T  (bf16 in, fp32 accumulate in
- * tensor memory, bf16 out) on tcgen05 tensor cores fed by TMA.
+ * tensor memory, bf16 out; fp32 out for plain / bias / GELU epilogues, e.g. router logits) on
+ * tcgen05 tensor cores fed by TMA.
  *   bias  : optional bf16 [N];  resid : optional bf16 [M, ldr], Y = resid + X W^T (may alias y)
  *   epilogue: B200_EPI_SWIGLU (W rows interleaved gate/up, Y is [M, N/2]) or B200_EPI_GELU
  *   status: optional device int32; receives B200_ERR_TIMEOUT if a bounded wait expired
@@ -163,7 +164,7 @@ int b200_flash_decode(void* out, int out_dtype, const void* q, int q_dtype,
  * triple_qkv_entry.cutedsl.py:150-804, conv2_blackwell_efc_bias_entry.cutedsl.py:1-42.
  * K % 8 == 0, N % 8 == 0 (N % 16 for SwiGLU), all leading dimensions % 8 == 0.
  */
-int b200_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K,
+int b200_gemm_bf16(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                    int ldx, int ldw, int ldy, const void* bias, const void* resid, int ldr,
                    int epilogue, int* status, int flags, b200_stream_t stream);
 
@@ -195,6 +196,61 @@ int b200_flash_prefill(void* out, const void* q, const void* k, const void* v,
                        int64_t v_bs, int64_t v_rs, int64_t v_hs,
                        int64_t o_bs, int64_t o_rs, int64_t o_hs,
                        int causal, float scale, int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * a9. MoE router: fp32 softmax over E logits -> top-k (ties: lowest expert index) ->
+ * weights renormalised over the selected experts; ids in descending-probability order.
+ *   logits: [s, E] fp32 or bf16; ids int32 [s, top_k]; wts fp32 [s, top_k]
+ *   round_bf16: round the weights through bf16 like the reference kernel does
+ * Reference: models/qwen3-30b-a3b/kernels/moe_router_parallel_topk_k.cu:2-111 (decode) and
+ * the torch softmax/topk/renorm at models/qwen3-30b-a3b/qwen3_optimized.py:569-572 (prefill).
+ * E % 32 == 0, E <= 256, top_k <= 32.
+ */
+int b200_moe_router(int* ids, float* wts, const void* logits, int logits_dtype, int s, int E,
+                    int top_k, int round_bf16, int flags, b200_stream_t stream);
+
+/* a11. Expert-major permutation of the s * top_k (token, slot) pairs: a stable counting sort
+ * by expert id, identical to torch.argsort(ids.flatten(), stable=True).
+ *   order[r]  : flat pair index (token * top_k + slot) at sorted row r
+ *   inv[p]    : sorted row of pair p (nullable)
+ *   offsets   : int32 [E + 1], first sorted row of every expert (offsets[E] = pairs)
+ *   workspace : b200_moe_permute_workspace_bytes(pairs, E) bytes
+ * Reference: models/qwen3-30b-a3b/qwen3_optimized.py:573-581 (argsort + scatter_add + cumsum).
+ */
+int64_t b200_moe_permute_workspace_bytes(int pairs, int E);
+int b200_moe_permute(int* order, int* inv, int* offsets, const int* ids, int pairs, int E,
+                     void* workspace, int flags, b200_stream_t stream);
+/* xg[r, :] = x[order[r] / top_k, :]  (bf16 rows of H elements).
+ * Reference: index_select at models/qwen3-30b-a3b/qwen3_optimized.py:582. */
+int b200_moe_gather_rows(void* xg, const void* x, const int* order, int rows, int top_k, int H,
+                         int flags, b200_stream_t stream);
+/* out[t, :] = (resid[t, :] +) sum_slot wts[t, slot] * y[inv[t * top_k + slot], :]
+ * (fp32 accumulation in slot order, one bf16 rounding).  With ids != NULL only the pairs whose
+ * expert lies in [expert_lo, expert_lo + n_local) are summed (expert parallelism).
+ * Reference: mul_ / index_copy_ / sum at models/qwen3-30b-a3b/qwen3_optimized.py:586-590. */
+int b200_moe_combine(void* out, const void* y, const int* inv, const float* wts,
+                     const void* resid, const int* ids, int expert_lo, int n_local,
+                     int tokens, int top_k, int H, int flags, b200_stream_t stream);
+
+/* a10. Decode-time expert MLP on the top_k selected experts (weight streaming, HBM bound).
+ *   w_gu  : [E, 2 * inter, hidden] bf16 with gate/up rows INTERLEAVED (row 2j = gate_j,
+ *           row 2j + 1 = up_j; a load-time repack of HuggingFace's gate-rows-then-up-rows)
+ *   w_down: [E, hidden, inter] bf16
+ *   gate_up: act[slot, j] = wts[slot] * silu(g_j) * u_j with optional RMSNorm prologue on x
+ *   down  : y[d] = (resid[d] +) sum_slot w_down[ids[slot]][d, :] . act[slot, :]
+ * Reference: models/qwen3-30b-a3b/kernels/moe_gate_up_silu_k.cu:2-32 and
+ * moe_down_accum_k.cu:2-33.  hidden % 256 == 0, inter % 256 == 0.
+ * Expert parallelism: w_gu / w_down hold experts [expert_lo, expert_lo + n_local) only; slots
+ * routed elsewhere contribute zero, and the ranks' outputs are summed by the caller.
+ */
+int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, const void* norm_w, float eps,
+                            const void* w_gu, const int* ids, const float* wts, int top_k,
+                            int inter, int hidden, int expert_lo, int n_local, int flags,
+                            b200_stream_t stream);
+int b200_moe_decode_down(void* y, int y_dtype, const void* act, const void* w_down,
+                         const int* ids, int top_k, int inter, int hidden,
+                         int expert_lo, int n_local,
+                         const void* resid, int resid_dtype, int flags, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * a8 / a12 small ops.

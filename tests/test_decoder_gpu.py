@@ -21,8 +21,8 @@ def _run(dev, cfg, P, seed):
     ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(seed))
     eng = DenseDecoder(cfg, w, max_seq=P + N_NEW + 2, device=dev)
     # --- prefill: per-layer hidden states ---
-    hid = []
-    first = eng.prefill(ids.to(dev), collect=hid)
+    hid, routed = [], []
+    first = eng.prefill(ids.to(dev), collect=hid, collect_router=routed)
     toks = [first]
     # --- decode: host-driven steps so that every step's logits can be inspected ---
     eng.capture()
@@ -47,12 +47,31 @@ def _run(dev, cfg, P, seed):
     # --- oracle: teacher-forced forward over prompt + generated tokens ---
     full = torch.cat((ids, torch.tensor(toks[:-1])))
     rows = list(range(P - 1, P + N_NEW - 1))
-    hidden, logits_ref, _ = decoder_forward(cfg, w, full, logits_rows=rows)
+    hidden, logits_ref, router_ref = decoder_forward(cfg, w, full, logits_rows=rows)
+    # MoE: a token whose k-th and (k+1)-th expert probabilities are closer than the bf16 noise
+    # of the router input may legitimately be routed differently from the fp32 oracle; such
+    # tokens (few, each with a tiny oracle margin) are left out of the hidden-state comparison
+    # from that layer on.  Given identical router logits the choice is bit-exact
+    # (tests/test_moe_gpu.py).
+    keep = torch.ones(P, dtype=torch.bool)
     for l in range(cfg.layers):
+        if cfg.n_experts:
+            from oracle.ref_decoder import moe_route
+            probs = torch.softmax(router_ref[l][:P].float(), -1)
+            ids_ref, _ = moe_route(router_ref[l][:P], cfg.top_k)
+            same = (routed[l].cpu().long().sort(-1).values == ids_ref.sort(-1).values).all(-1)
+            top = probs.topk(cfg.top_k + 1, -1).values
+            margin_k = (top[:, cfg.top_k - 1] - top[:, cfg.top_k]) / top[:, cfg.top_k - 1]
+            bad = margin_k[~same & keep]
+            assert bad.numel() == 0 or float(bad.max()) < 3e-2, f"routing differs at margin {float(bad.max())}"
+            keep &= same
+            print(f"layer {l}: {int((~same).sum())} tokens re-routed, max relative margin "
+                  f"{float(bad.max()) if bad.numel() else 0.0:.2e}")
+            assert int((~keep).sum()) <= max(2, P // 8), f"too many re-routed tokens: {int((~keep).sum())}"
         ref = hidden[l + 1][:P] if l + 1 < cfg.layers else None
         if ref is not None:
-            err = float((hid[l].float().cpu() - ref).abs().max() / ref.abs().max())
-            assert err < 2e-2, f"prefill layer {l}: {err}"
+            err = float((hid[l].float().cpu() - ref)[keep].abs().max() / ref.abs().max())
+            assert err < 2e-2, f"prefill layer {l}: {err} ({int((~keep).sum())} tokens re-routed)"
     # decode step 0 hidden states (position P)
     for l in range(cfg.layers - 1):
         ref = hidden[l + 1][P]
