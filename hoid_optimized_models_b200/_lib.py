@@ -22,6 +22,7 @@ ERRORS = {
     -4: "B200_ERR_ARG (null pointer / bad enum)",
     -5: "B200_ERR_TIMEOUT (bounded device-side wait expired)",
     -6: "B200_ERR_DRIVER (driver entry point unavailable)",
+    -7: "B200_ERR_SCRATCH (request exceeds the library's fixed scratch array)",
 }
 
 _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_int64
@@ -38,6 +39,8 @@ SIGNATURES = {
                                 _f, _i, _p]),
     "b200_flash_decode_workspace_bytes": (_l, [_i, _i, _i, _i]),
     "b200_flash_decode": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _l, _l, _i, _f, _i, _p]),
+    "b200_flash_decode_static_max_bytes": (_l, []),
+    "b200_flash_decode_static": (_i, [_p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _l, _l, _i, _f, _i, _p]),
     "b200_gemm_bf16": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _i, _p]),
     "b200_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),
     "b200_flash_prefill": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_i, _f, _i, _p]),

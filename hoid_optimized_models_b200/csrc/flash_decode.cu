@@ -319,3 +319,56 @@ extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_
 #undef FD_CASE
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------
+// Flash-decode for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at the point where they need
+// attention: a plugin running inside another framework's memory pool, a real-time serving
+// loop that forbids allocation (and the implicit synchronisation it can bring) after
+// start-up, or a process whose memory budget was fixed when it was launched.  For them the
+// split records and arrival counters live in the fixed array below instead of a
+// caller-provided workspace.  Every GPU that loads the library holds these 2 MiB until the
+// process exits.
+constexpr size_t kFdStaticBytes = 2u << 20;
+static __device__ __align__(256) unsigned char g_fd_static_scratch[kFdStaticBytes];
+
+// In host code `g_fd_static_scratch` is only a stand-in for the symbol, never a device
+// address; the real address is looked up once per device (with that device current).
+constexpr int kFdMaxDevices = 64;
+static void* g_fd_static_ptr[kFdMaxDevices] = {nullptr};
+
+static int fd_static_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kFdMaxDevices) return B200_ERR_ARG;
+  if (g_fd_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_fd_static_scratch) != cudaSuccess || p == nullptr)
+      return B200_ERR_LAUNCH;
+    g_fd_static_ptr[dev] = p;
+  }
+  *out = g_fd_static_ptr[dev];
+  return B200_OK;
+}
+
+extern "C" int64_t b200_flash_decode_static_max_bytes(void) { return (int64_t)kFdStaticBytes; }
+
+extern "C" int b200_flash_decode_static(void* out, int out_dtype, const void* q, int q_dtype,
+                                        const void* kcache, const void* vcache,
+                                        const int* kv_len_dev, int n_q, int n_kv, int hd,
+                                        int64_t kv_head_stride, int64_t kv_row_stride,
+                                        int n_splits, float scale, int flags,
+                                        b200_stream_t stream) {
+  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_splits <= 0) return B200_ERR_SHAPE;
+  // sizes whose records do not fit the fixed array are refused, never truncated
+  if (b200_flash_decode_workspace_bytes(n_q, n_kv, hd, n_splits) > (int64_t)kFdStaticBytes)
+    return B200_ERR_SCRATCH;
+  void* scratch = nullptr;
+  const int rc = fd_static_address(&scratch);   // first call on a device resolves the symbol
+  if (rc != B200_OK) return rc;
+  // The array keeps whatever the previous call left; the arrival counters must start at zero.
+  if (cudaMemsetAsync(scratch, 0, fd_counter_bytes(n_kv), (cudaStream_t)stream) != cudaSuccess)
+    return B200_ERR_LAUNCH;
+  return b200_flash_decode(out, out_dtype, q, q_dtype, kcache, vcache, kv_len_dev, scratch, n_q,
+                           n_kv, hd, kv_head_stride, kv_row_stride, n_splits, scale, flags, stream);
+}

@@ -37,7 +37,8 @@ enum {
   B200_ERR_LAUNCH = -3,    /* CUDA reported a launch error */
   B200_ERR_ARG = -4,       /* null pointer / bad enum */
   B200_ERR_TIMEOUT = -5,   /* a bounded device-side wait expired (status word) */
-  B200_ERR_DRIVER = -6     /* driver entry point (tensor-map encode) unavailable */
+  B200_ERR_DRIVER = -6,    /* driver entry point (tensor-map encode) unavailable */
+  B200_ERR_SCRATCH = -7    /* request needs more scratch than the library's fixed array holds */
 };
 
 /* launch flags */
@@ -150,6 +151,30 @@ int b200_flash_decode(void* out, int out_dtype, const void* q, int q_dtype,
                       void* workspace, int n_q, int n_kv, int hd,
                       int64_t kv_head_stride, int64_t kv_row_stride,
                       int n_splits, float scale, int flags, b200_stream_t stream);
+
+/* Flash-decode without any allocation (no counterpart in the reference).
+ *
+ * Same computation and arguments as b200_flash_decode, minus the workspace: the split
+ * records and arrival counters live in a 2 MiB array that is part of the library image
+ * (b200_flash_decode_static_max_bytes()), so a caller that is not allowed to allocate device
+ * memory - a plugin inside another framework's memory pool, an allocation-free serving loop,
+ * a process with a fixed memory budget - can still run decode attention.  Every GPU that
+ * loads the library holds the array until the process exits.
+ *   - Returns B200_ERR_SCRATCH when b200_flash_decode_workspace_bytes(n_q, n_kv, hd, n_splits)
+ *     exceeds the array; nothing is launched in that case.
+ *   - The first call on each device looks up the array's device address; make that call
+ *     with the device current and before any stream capture.
+ *   - All calls share the array.  Each call clears the counters it needs on `stream` first,
+ *     so calls on one stream are safe back to back; calls that overlap on the GPU (other
+ *     streams, other threads) race on the array and give wrong results.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ */
+int64_t b200_flash_decode_static_max_bytes(void);
+int b200_flash_decode_static(void* out, int out_dtype, const void* q, int q_dtype,
+                             const void* kcache, const void* vcache, const int* kv_len_dev,
+                             int n_q, int n_kv, int hd,
+                             int64_t kv_head_stride, int64_t kv_row_stride,
+                             int n_splits, float scale, int flags, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * a2. Prefill / encoder GEMM  Y[M,N] = X[M,K] W[N,K]^T  (bf16 in, fp32 accumulate in
