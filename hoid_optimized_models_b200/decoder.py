@@ -27,16 +27,11 @@ from typing import Dict, List, Optional
 import torch
 
 from . import ops
+from . import tp as tpart
 from .configs import DecoderConfig
 from .weights import rope_tables
 
 EPI_SWIGLU = ops.EPI_SWIGLU
-
-
-def _interleave_rows(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-    """[I, K] gate and up -> [2I, K] with row 2j = gate_j and row 2j+1 = up_j."""
-    I, K = gate.shape
-    return torch.stack((gate, up), dim=1).reshape(2 * I, K).contiguous()
 
 
 class DenseDecoder:
@@ -44,13 +39,8 @@ class DenseDecoder:
                  device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None,
                  n_splits: Optional[int] = None, max_new_tokens: int = 1024,
                  free_source_weights: bool = False):
-        self.moe = cfg.n_experts > 0
-        if self.moe:
-            # expert parallelism: attention is replicated, experts are sharded
-            if cfg.n_experts % tp_size:
-                raise ValueError("expert-parallel size must divide the number of experts")
-        elif cfg.n_kv % tp_size or cfg.n_q % tp_size or cfg.inter % tp_size or cfg.vocab % tp_size:
-            raise ValueError("tensor-parallel size must divide heads, intermediate and vocab")
+        self.moe = cfg.n_experts > 0   # expert parallelism: attention replicated, experts sharded
+        tpart.check_divisible(cfg, tp_size)
         self.cfg, self.device, self.max_seq = cfg, torch.device(device), max_seq
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
         H, hd = cfg.hidden, cfg.head_dim
@@ -67,8 +57,7 @@ class DenseDecoder:
         dev = self.device
 
         def take(name):
-            t = weights.pop(name) if free_source_weights else weights[name]
-            return t
+            return weights[name]
 
         def rows(t, n_local):  # column-parallel: a contiguous block of output rows
             return t[r * n_local:(r + 1) * n_local]
@@ -90,28 +79,21 @@ class DenseDecoder:
             p = f"model.layers.{i}."
             self.ln1.append(take(p + "input_layernorm.weight").to(dev))
             self.ln2.append(take(p + "post_attention_layernorm.weight").to(dev))
-            q = rows(take(p + "self_attn.q_proj.weight"), self.q_size)
-            k = rows(take(p + "self_attn.k_proj.weight"), self.kv_size)
-            v = rows(take(p + "self_attn.v_proj.weight"), self.kv_size)
-            self.wqkv.append(torch.cat((q, k, v), dim=0).to(dev).contiguous())
-            o = take(p + "self_attn.o_proj.weight")
-            self.wo.append(o[:, r * self.q_size:(r + 1) * self.q_size].to(dev).contiguous())
+            wqkv, wo = tpart.shard_attention(cfg, weights, i, r, att_tp)
+            self.wqkv.append(wqkv.to(dev))
+            self.wo.append(wo.to(dev))
             if self.moe:
-                lo, hi = self.expert_lo, self.expert_lo + self.n_local_experts
-                self.w_router.append(take(p + "mlp.gate.weight").to(dev))
-                gu = take(p + "mlp.experts.gate_up_proj")[lo:hi].to(dev)   # [E, 2I, H], gate rows first
-                I = cfg.moe_inter
-                # load-time repack: interleave gate/up rows so that both the decode GEMV and
-                # the grouped GEMM can apply SwiGLU to adjacent outputs
-                self.wgu.append(torch.stack((gu[:, :I], gu[:, I:]), dim=2)
-                                .reshape(self.n_local_experts, 2 * I, H).contiguous())
-                self.wd.append(take(p + "mlp.experts.down_proj")[lo:hi].to(dev).contiguous())
+                self.w_router.append(weights[p + "mlp.gate.weight"].to(dev))
+                gu, dn, _ = tpart.shard_experts(cfg, weights, i, tp_rank, tp_size)
+                self.wgu.append(gu.to(dev))
+                self.wd.append(dn.to(dev))
             else:
-                g = rows(take(p + "mlp.gate_proj.weight"), self.inter)
-                u = rows(take(p + "mlp.up_proj.weight"), self.inter)
-                self.wgu.append(_interleave_rows(g.to(dev), u.to(dev)))
-                d = take(p + "mlp.down_proj.weight")
-                self.wd.append(d[:, r * self.inter:(r + 1) * self.inter].to(dev).contiguous())
+                gu, dn = tpart.shard_mlp(cfg, weights, i, r, att_tp)
+                self.wgu.append(gu.to(dev))
+                self.wd.append(dn.to(dev))
+            if free_source_weights:
+                for k in [k for k in weights if k.startswith(p) and "norm" not in k]:
+                    del weights[k]
             if cfg.qk_norm:
                 self.qn.append(take(p + "self_attn.q_norm.weight").to(dev))
                 self.kn.append(take(p + "self_attn.k_norm.weight").to(dev))
