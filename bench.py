@@ -341,7 +341,10 @@ def main():
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel (gate|up + SwiGLU, N=28672/tp K=4096)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "peak_kind": f"of {peak_kind}",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the ncu
+                     # capture summarised in profiles/gemv_kernel_gate_up_llama8b.md
+                     "traffic": (234_945_000 + 3_219_712) if world == 1 else None,
                      "bytes_per_launch": gemv_bytes, "ms_per_launch": gemv_ms},
         "step_roofline": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_gbs,
                           "frac_of_peak": step_gbs / peak, "frac_of_8tbs": step_gbs / 8000.0},

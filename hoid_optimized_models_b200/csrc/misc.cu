@@ -101,6 +101,23 @@ __global__ void __launch_bounds__(256) argmax_kernel(int* idx_out, float* max_ou
   }
 }
 
+// out[b, :] = x[b * row_stride : +H] / max(||x||_2, eps): first-token pooling + L2 normalisation.
+__global__ void __launch_bounds__(256) cls_pool_l2_kernel(float* out, const uint16_t* x,
+                                                          long row_stride, int H, float eps) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint16_t* row = x + (size_t)blockIdx.x * row_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = __uint_as_float((uint32_t)row[i] << 16);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = 1.f / fmaxf(sqrtf(block_sum(ss, red)), eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[(size_t)blockIdx.x * H + i] = __uint_as_float((uint32_t)row[i] << 16) * inv;
+}
+
 // Pick the best of n (value, index) candidates (one per tensor-parallel rank; n = 1 on a
 // single GPU), publish it as the next input token, append it to the token log and advance
 // the step state {position, kv_len, tokens generated}.
@@ -157,6 +174,16 @@ extern "C" int b200_silu_mul(void* out, const void* gate, const void* up, int64_
   cudaError_t e = launch(silu_mul_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream,
                          (flags & B200_FLAG_PDL) != 0, (uint4*)out, (const uint4*)gate,
                          (const uint4*)up, nchunk);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+extern "C" int b200_cls_pool_l2(float* out, const void* x, int batch, int64_t row_stride, int H,
+                                float eps, int flags, b200_stream_t stream) {
+  if (!out || !x) return B200_ERR_ARG;
+  if (batch <= 0 || H <= 0) return B200_ERR_SHAPE;
+  cudaError_t e = launch(cls_pool_l2_kernel, dim3(batch), dim3(256), 0, (cudaStream_t)stream,
+                         (flags & B200_FLAG_PDL) != 0, out, (const uint16_t*)x, (long)row_stride, H,
+                         eps);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 

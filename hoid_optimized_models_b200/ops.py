@@ -346,6 +346,17 @@ def embed_gather(out: Tensor, table: Tensor, ids: Tensor) -> None:
                                        table.shape[1], _flags(), _stream()), "b200_embed_gather")
 
 
+@torch.library.custom_op("b200::cls_pool_l2", mutates_args=("out",))
+def cls_pool_l2(out: Tensor, x: Tensor, seq_len: int, eps: float = 1e-12) -> None:
+    """out[b] = L2-normalised first token of sequence b; x is bf16 [batch * seq_len, H]."""
+    _bf16(x, "x")
+    H = x.shape[-1]
+    if out.dtype != torch.float32:
+        raise TypeError("out must be float32")
+    check(_lib.lib().b200_cls_pool_l2(_ptr(out), _ptr(x), out.shape[0], seq_len * H, H, eps,
+                                      _flags(), _stream()), "b200_cls_pool_l2")
+
+
 @torch.library.custom_op("b200::silu_mul", mutates_args=("out",))
 def silu_mul(out: Tensor, gate: Tensor, up: Tensor) -> None:
     _bf16(out, "out"); _bf16(gate, "gate"); _bf16(up, "up")

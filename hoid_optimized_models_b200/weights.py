@@ -87,3 +87,30 @@ def rope_tables(cfg: DecoderConfig, max_seq: int, device):
     """fp32 [max_seq, head_dim/2] cos / sin from f64 angles."""
     ang = torch.arange(max_seq, dtype=torch.float64)[:, None] * rope_inv_freq(cfg)[None, :]
     return ang.cos().float().to(device), ang.sin().float().to(device)
+
+
+def make_encoder_weights(cfg, seed: int = 1234, device="cpu") -> Dict[str, torch.Tensor]:
+    """XLM-RoBERTa-architecture encoder weights under HuggingFace `XLMRobertaModel` names
+    (models/bge-m3/bge_optimized.py:294-313 reads exactly these).  Matrices N(0, 0.02^2), biases
+    N(0, 0.02^2), LayerNorm gamma 1 + N(0, 0.02^2) and beta N(0, 0.02^2), all bf16-rounded."""
+    w: Dict[str, torch.Tensor] = {}
+    H = cfg.hidden
+    w["embeddings.word_embeddings.weight"] = _normal((cfg.vocab, H), seed, 999, 0, device)
+    w["embeddings.position_embeddings.weight"] = _normal((cfg.max_pos, H), seed, 999, 1, device)
+    w["embeddings.token_type_embeddings.weight"] = _normal((1, H), seed, 999, 2, device)
+    w["embeddings.LayerNorm.weight"] = _normal((H,), seed, 999, 3, device, mean=1.0)
+    w["embeddings.LayerNorm.bias"] = _normal((H,), seed, 999, 4, device)
+    for i in range(cfg.layers):
+        p = f"encoder.layer.{i}."
+        slot = 0
+        for name, shape in (("attention.self.query", (H, H)), ("attention.self.key", (H, H)),
+                            ("attention.self.value", (H, H)), ("attention.output.dense", (H, H)),
+                            ("intermediate.dense", (cfg.inter, H)), ("output.dense", (H, cfg.inter))):
+            w[p + name + ".weight"] = _normal(shape, seed, i, slot, device)
+            w[p + name + ".bias"] = _normal((shape[0],), seed, i, slot + 1, device)
+            slot += 2
+        for name in ("attention.output.LayerNorm", "output.LayerNorm"):
+            w[p + name + ".weight"] = _normal((H,), seed, i, slot, device, mean=1.0)
+            w[p + name + ".bias"] = _normal((H,), seed, i, slot + 1, device)
+            slot += 2
+    return w

@@ -284,6 +284,11 @@ int b200_moe_decode_down(void* y, int y_dtype, const void* act, const void* w_do
  * Reference: embedding_k, models/llama31-8b/llama31_native_gen.py:17-27. */
 int b200_embed_gather(void* out, int out_dtype, const void* table, const int* ids,
                       int rows, int H, int flags, b200_stream_t stream);
+/* out[b, :] = x_b / max(||x_b||_2, eps) with x_b the bf16 row at x + b * row_stride (the first
+ * token of sequence b): CLS pooling + L2 normalisation to fp32 [batch, H].
+ * Reference: models/bge-m3/kernels/bge_pool_k.cu:1. */
+int b200_cls_pool_l2(float* out, const void* x, int batch, int64_t row_stride, int H, float eps,
+                     int flags, b200_stream_t stream);
 /* out = silu(gate) * up, elementwise over n values (bf16).
  * Reference: models/llama31-8b/kernels/silu_mul_vec8_fast_k.cu:12-23. */
 int b200_silu_mul(void* out, const void* gate, const void* up, int64_t n,

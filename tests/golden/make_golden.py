@@ -59,6 +59,18 @@ def main():
             out["router_ids"] = torch.stack([i.sort(-1).values for i in idx]).numpy()
         np.savez_compressed(os.path.join(HERE, f"decoder_{fam}.npz"), **out)
         print(fam, {k: v.shape for k, v in out.items()})
+    # encoder (XLM-RoBERTa architecture)
+    from hoid_optimized_models_b200.configs import XLMR_LARGE
+    from hoid_optimized_models_b200.weights import make_encoder_weights
+    from oracle import ref_encoder as E
+    ecfg = replace(XLMR_LARGE, name="xlmr-tiny", hidden=128, layers=2, heads=4, inter=256, vocab=600,
+                   max_pos=64)
+    ew = make_encoder_weights(ecfg, SEED)
+    eids = torch.randint(3, ecfg.vocab, (3, 20), generator=torch.Generator().manual_seed(SEED))
+    hs, pooled = E.hf_forward(E.hf_model(ecfg, ew), eids)
+    np.savez_compressed(os.path.join(HERE, "encoder_xlmr.npz"), ids=eids.numpy(),
+                        hidden_cls=torch.stack([h[:, 0] for h in hs]).numpy(), pooled=pooled.numpy())
+    print("xlmr", pooled.shape)
     with open(os.path.join(HERE, "versions.json"), "w") as f:
         json.dump(meta, f, indent=1)
 

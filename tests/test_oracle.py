@@ -86,3 +86,21 @@ def test_algorithmic_bytes_match_derivation():
     # 15 009 849 344 B of weights + 131 072 B of KV per cached position (Llama-3.1-8B)
     assert LLAMA31_8B.decode_bytes_per_token(0) == 15_009_849_344
     assert LLAMA31_8B.decode_bytes_per_token(8192) - LLAMA31_8B.decode_bytes_per_token(0) == 131072 * 8192
+
+
+def test_encoder_restatement_matches_golden_and_hf():
+    from hoid_optimized_models_b200.configs import XLMR_LARGE
+    from hoid_optimized_models_b200.weights import make_encoder_weights
+    from oracle import ref_encoder as E
+    cfg = replace(XLMR_LARGE, name="xlmr-tiny", hidden=128, layers=2, heads=4, inter=256, vocab=600,
+                  max_pos=64)
+    gold = np.load(os.path.join(GOLD, "encoder_xlmr.npz"))
+    w = make_encoder_weights(cfg, 1234)
+    ids = torch.from_numpy(gold["ids"])
+    hidden, pooled = E.encoder_forward(cfg, w, ids)
+    got = torch.stack([h[:, 0] for h in hidden]).numpy()
+    assert np.abs(got - gold["hidden_cls"]).max() <= 1e-4 * np.abs(gold["hidden_cls"]).max()
+    assert np.abs(pooled.numpy() - gold["pooled"]).max() <= 1e-5
+    pytest.importorskip("transformers")
+    hs, p2 = E.hf_forward(E.hf_model(cfg, w), ids)
+    assert float((p2 - pooled).abs().max()) <= 1e-5
