@@ -199,6 +199,8 @@ def main():
     group = None
     if world > 1:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
 
@@ -275,7 +277,11 @@ def main():
             print(json.dumps({"profiling_only": True, "ms_per_step": ms_per_step, "tok_s": tok_s,
                               "clocks": clk}))
         if world > 1:
-            torch.distributed.destroy_process_group()
+            eng.graph = None
+            torch.cuda.synchronize()
+            torch.distributed.barrier()
+            sys.stdout.flush()
+            os._exit(0)
         return
 
     # ---- end to end through the public step API: H2D token + state, replay, D2H token ----
@@ -320,9 +326,21 @@ def main():
     step_bytes = cfg.decode_bytes_per_token(ctx_mid) / world
     step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
 
-    if rank != 0:
+    def leave():
+        """Multi-rank exit: the captured graph holds NCCL kernels, so drop it, meet the other
+        ranks, flush and leave without the communicator teardown (which can block while graphs
+        that reference the communicator are alive)."""
         if world > 1:
-            torch.distributed.destroy_process_group()
+            eng.graph = None
+            torch.cuda.synchronize()
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        leave()
         return
 
     line = {
@@ -359,8 +377,7 @@ def main():
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": os.cpu_count(),
                                     "kind": "reference", "sample": f"failed: {e!r}"}
     print(json.dumps(line))
-    if world > 1:
-        torch.distributed.destroy_process_group()
+    leave()
 
 
 if __name__ == "__main__":
