@@ -51,6 +51,7 @@ SIGNATURES = {
     "b200_moe_combine": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "b200_moe_decode_gate_up": (_i, [_p, _p, _i, _p, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "b200_moe_decode_down": (_i, [_p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _p]),
+    "b200_flash_prefill_tc": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_i, _f, _p, _i, _p]),
     "b200_embed_gather": (_i, [_p, _i, _p, _p, _i, _i, _i, _p]),
     "b200_cls_pool_l2": (_i, [_p, _p, _i, _l, _i, _f, _i, _p]),
     "b200_silu_mul": (_i, [_p, _p, _p, _l, _i, _p]),

@@ -1,0 +1,425 @@
+// Prefill / encoder flash attention on the sm_100a tensor cores (tcgen05 + TMEM + TMA).
+//
+// One CTA owns 128 query rows of one head and walks the keys in tiles of 128:
+//   warp 0     TMA producer: Q once, then K and V tiles into a 2-stage ring
+//   warp 1     MMA issuer (one lane): S_j = Q K_j^T (M128 N128, K = head dim) into one of two
+//              S accumulators in tensor memory, and O_j = P_j V_j (V consumed in its natural
+//              [key][dim] layout as an MN-major operand) into one of two O-tile accumulators
+//   warps 2-9  softmax: two threads per query row (= TMEM lane), one per half of the key
+//              columns / output dims.  Two passes over S_j with tcgen05.ld (row max, exchanged
+//              between the two halves through shared memory, then exp2 / row sum), P_j written
+//              as bf16 into a 128-byte-swizzled shared tile that the second MMA reads; O_{j-1}
+//              is pulled from tensor memory one tile later and folded into fp32 registers with
+//              the online softmax correction, so the MMA of tile j+1 overlaps the softmax of
+//              tile j.
+// The score matrix never leaves the SM.  Causal tiles above the diagonal are never visited.
+// Every mbarrier wait is bounded (status word + clean TMEM release on expiry).
+#include "sm100.cuh"
+
+namespace b200 {
+
+constexpr int FA_BM = 128, FA_BN = 128;
+constexpr int kFaThreads = 320;   // TMA warp, MMA warp, 8 softmax warps
+constexpr uint32_t kAtomBytes = 128 * 128;   // a 128-row x 64-column bf16 box: 16 KiB
+
+struct FaArgs {
+  uint16_t* o; long o_bs, o_rs, o_hs;
+  int* status;
+  int S, kv_len, q_pos0, group, causal, n_q;
+  // row / column bookkeeping of the 2D views the tensor maps cover
+  int q_batch_rows, q_head_rows, q_head_cols;
+  int k_batch_rows, k_head_rows, k_head_cols;
+  int v_batch_rows, v_head_rows, v_head_cols;
+  float scale_log2;
+};
+
+// UMMA descriptor for an MN-major, 128-byte-swizzled operand: 64 contiguous MN elements per
+// 128-byte row, rows = K index; 8-row groups SBO bytes apart, 64-element MN blocks LBO apart.
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+__device__ __forceinline__ uint64_t umma_desc_k(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// bf16 x bf16 -> fp32, M = 128; b_major: 0 = K-major, 1 = MN-major
+constexpr uint32_t fa_idesc(int n, int b_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_major << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kFaThreads, 1)
+flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                        const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, FaArgs a) {
+  constexpr int ATOMS = HD / 64;                        // 64-column boxes per operand tile
+  constexpr uint32_t kQBytes = ATOMS * kAtomBytes;      // Q / K / V tile bytes
+  constexpr uint32_t kPBytes = 2 * kAtomBytes;          // P tile: 128 rows x 128 keys
+  constexpr uint32_t kStage = 2 * kQBytes;              // K + V
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // Operand tiles need 1024-byte alignment.  The whole 227 KB of shared memory is in use at
+  // head dim 128, so there is no room for alignment slack: the dynamic window starts 1 KB into
+  // the CTA's shared memory (after the system-reserved kilobyte) and is therefore aligned; if a
+  // future toolchain breaks that assumption the kernel reports it instead of corrupting tiles.
+  const uint32_t base = smem_u32(smem_raw);
+  if ((base & 1023u) != 0) {
+    if (threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, B200_ERR_ALIGN);
+    return;
+  }
+  unsigned char* gen = smem_raw;
+  const uint32_t sQ = base;
+  const uint32_t sKV = sQ + kQBytes;                    // 2 stages x (K | V)
+  const uint32_t sP = sKV + 2 * kStage;                 // 2 buffers
+  unsigned char* gP = gen + kQBytes + 2 * kStage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kQBytes + 2 * kStage + 2 * kPBytes);
+  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7,8 p_full | 9,10 o_full
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xch = reinterpret_cast<float*>(tmem_slot + 4);   // [2 parities][2 halves][128 rows]
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mtile = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int m0 = mtile * FA_BM;
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / a.group;
+
+  pdl_launch_dependents();
+  if (tid == 0) {
+    mbar_init(bar(0), 1);
+    for (int i = 1; i <= 6; ++i) mbar_init(bar(i), 1);
+    mbar_init(bar(7), 256); mbar_init(bar(8), 256);
+    mbar_init(bar(9), 1); mbar_init(bar(10), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid < 128) reinterpret_cast<int*>(xch + 512)[tid] = 0;   // 256 16-bit exchange sequence numbers
+  pdl_wait();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;            // S buffers at columns 0 and 128
+  const uint32_t tO = tmem_base + 256;      // O-tile buffers at columns 256 and 256 + HD
+
+  // keys this query tile can see
+  int kv_end = a.kv_len;
+  if (a.causal) kv_end = min(kv_end, a.q_pos0 + m0 + FA_BM);
+  const int ntiles = (kv_end + FA_BN - 1) / FA_BN;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && ntiles > 0) {
+      const int q_row = b * a.q_batch_rows + head * a.q_head_rows + m0;
+      const int q_col = head * a.q_head_cols;
+      mbar_expect_tx(bar(0), kQBytes);
+#pragma unroll
+      for (int t = 0; t < ATOMS; ++t) tma_load_2d(sQ + t * kAtomBytes, &map_q, bar(0), q_col + 64 * t, q_row);
+      const int k_row0 = b * a.k_batch_rows + kvh * a.k_head_rows, k_col = kvh * a.k_head_cols;
+      const int v_row0 = b * a.v_batch_rows + kvh * a.v_head_rows, v_col = kvh * a.v_head_cols;
+      bool ok = true;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(bar(3 + st), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const uint32_t sk = sKV + st * kStage, sv = sk + kQBytes;
+        mbar_expect_tx(bar(1 + st), kStage);
+#pragma unroll
+        for (int t = 0; t < ATOMS; ++t) {
+          tma_load_2d(sk + t * kAtomBytes, &map_k, bar(1 + st), k_col + 64 * t, k_row0 + j * FA_BN);
+          tma_load_2d(sv + t * kAtomBytes, &map_v, bar(1 + st), v_col + 64 * t, v_row0 + j * FA_BN);
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i <= 2; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try(bar(i), 0) && !mbar_try(bar(i), 1) && clock64() - t0 < 2000000) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && ntiles > 0) {
+      constexpr uint32_t idesc_s = fa_idesc(FA_BN, 0);
+      constexpr uint32_t idesc_o = fa_idesc(HD, 1);
+      bool ok = mbar_wait(bar(0), 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(bar(1 + st), (j >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sk = sKV + st * kStage;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          tc_mma(tS + st * FA_BN, umma_desc_k(sQ + off), umma_desc_k(sk + off), idesc_s, k != 0 ? 1u : 0u);
+        }
+        tc_commit(bar(5 + st));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < ntiles) { if (!issue_s(j + 1)) { ok = false; break; } }
+        if (!mbar_wait(bar(7 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sv = sKV + st * kStage + kQBytes;
+        const uint32_t sp = sP + st * kPBytes;
+#pragma unroll
+        for (int k = 0; k < FA_BN / 16; ++k) {
+          // A = P (K-major over keys): 16 keys = 32 bytes inside a 64-key atom
+          const uint64_t da = umma_desc_k(sp + (k >> 2) * kAtomBytes + (k & 3) * 32);
+          // B = V (MN-major over dims): 16 keys = two 8-row groups = 2048 bytes
+          const uint64_t db = umma_desc_mn(sv + k * 2048, kAtomBytes, 1024);
+          tc_mma(tO + st * HD, da, db, idesc_o, k != 0 ? 1u : 0u);
+        }
+        tc_commit(bar(9 + st));    // O tile ready
+        tc_commit(bar(3 + st));    // K/V stage free
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps
+    const int slab = warp & 3;                        // TMEM lanes [32 slab, 32 slab + 32)
+    const int half = (warp - 2) >> 2;                 // which half of the columns / dims
+    const int row = slab * 32 + lane;                 // query row inside the tile = TMEM lane
+    const int qpos = a.q_pos0 + m0 + row;             // absolute position for the causal rule
+    const uint32_t lane_addr = (uint32_t)(slab * 32) << 16;
+    constexpr int OD = HD / 2;                        // output dims owned by this thread
+    float o_acc[OD];
+#pragma unroll
+    for (int d = 0; d < OD; ++d) o_acc[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    bool ok = true;
+    // Exchange one float per tile with the thread that owns the other half of this row:
+    // value slots are double-buffered by tile parity, a per-thread sequence number publishes
+    // them, and the reader's wait is bounded like every other wait in this kernel.
+    volatile float* xval = xch;                                        // [2][2][128]
+    volatile unsigned short* xseq = reinterpret_cast<volatile unsigned short*>(xch + 512);   // [2][128]
+    auto exchange = [&](int seq, float mine, float* other) -> bool {
+      xval[(seq & 1) * 256 + half * 128 + row] = mine;
+      __threadfence_block();
+      xseq[half * 128 + row] = (unsigned short)seq;
+      const long long t0 = clock64();
+      int spins = 0;
+      // the partner is never more than one tile ahead, so equality modulo 2^16 is enough
+      while (xseq[(half ^ 1) * 128 + row] != (unsigned short)seq &&
+             xseq[(half ^ 1) * 128 + row] != (unsigned short)(seq + 1)) {
+        if ((++spins & 255) == 0) {
+          if (*abort_flag) return false;
+          if (clock64() - t0 > kWaitBudget) { *abort_flag = 1; return false; }
+        }
+      }
+      __threadfence_block();
+      *other = xval[(seq & 1) * 256 + (half ^ 1) * 128 + row];
+      return true;
+    };
+    auto ex2 = [](float x) -> float {
+      float y;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+      return y;
+    };
+
+    auto fold_o = [&](int j, float corr) -> bool {
+      // o_acc = o_acc * corr + O_j  (O_j was produced with the row maximum after tile j)
+      const int st = j & 1;
+      if (!mbar_wait(bar(9 + st), (j >> 1) & 1, abort_flag)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < OD / 32; ++c) {
+        uint32_t r[32];
+        tc_ld32(tO + st * HD + half * OD + lane_addr + c * 32, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], corr, __uint_as_float(r[i]));
+      }
+      return true;
+    };
+
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int st = j & 1;
+      if (!mbar_wait(bar(5 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = j * FA_BN + half * 64;          // first key of this thread's columns
+      // columns at or beyond `valid` are masked (end of the keys, or above the diagonal)
+      int valid = a.kv_len - key0;
+      if (a.causal) valid = min(valid, qpos - key0 + 1);
+      const uint32_t s_addr = tS + st * FA_BN + half * 64 + lane_addr;
+      // pass 1: row maximum over this half, then exchange with the other half
+      float mt = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tc_ld32(s_addr + c * 32, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          mt = fmaxf(mt, (c * 32 + i < valid) ? __uint_as_float(r[i]) : -INFINITY);
+      }
+      float mt_other;
+      if (!exchange(j + 1, mt, &mt_other)) { ok = false; break; }
+      mt = fmaxf(mt, mt_other);
+      const float m_new = fmaxf(m_run, mt * a.scale_log2);
+      const float mu = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = ex2(m_run - mu);
+      // pass 2: p = exp2(s * scale - m), row sum, P tile (bf16, 128-byte swizzle, K-major);
+      // this half's 64 keys are exactly one 64-key atom of the P tile
+      float ps = 0.f;
+      unsigned char* prow = gP + st * kPBytes + half * kAtomBytes + row * 128;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tc_ld32(s_addr + c * 32, r);
+        tc_wait_ld();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = ex2(fmaf(__uint_as_float(r[i]), a.scale_log2, -mu));
+          p[i] = (c * 32 + i < valid) ? e : 0.f;
+          ps += p[i];
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16(p[q4 * 8 + 0], p[q4 * 8 + 1]); w.y = pack_bf16(p[q4 * 8 + 2], p[q4 * 8 + 3]);
+          w.z = pack_bf16(p[q4 * 8 + 4], p[q4 * 8 + 5]); w.w = pack_bf16(p[q4 * 8 + 6], p[q4 * 8 + 7]);
+          const int chunk = c * 4 + q4;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+        }
+      }
+      l_run = l_run * corr + ps;
+      m_run = m_new;
+      // make the P tile visible to the tensor core (async proxy) and hand it over
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(bar(7 + st));
+      // fold the previous tile's output while the tensor core works on this one
+      if (j > 0) { if (!fold_o(j - 1, corr_prev)) { ok = false; break; } }
+      corr_prev = corr;
+    }
+    if (ok && ntiles > 0) ok = fold_o(ntiles - 1, corr_prev);
+    // the row sum is split between the two halves
+    float l_other = 0.f;
+    if (ok) ok = exchange(ntiles + 1, l_run, &l_other);
+    l_run += l_other;
+    if (ok && m0 + row < a.S) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint16_t* dst = a.o + (long)b * a.o_bs + (long)(m0 + row) * a.o_rs + (long)head * a.o_hs + half * OD;
+#pragma unroll
+      for (int d = 0; d < OD; d += 8) {
+        uint4 w;
+        w.x = pack_bf16(o_acc[d] * inv, o_acc[d + 1] * inv);
+        w.y = pack_bf16(o_acc[d + 2] * inv, o_acc[d + 3] * inv);
+        w.z = pack_bf16(o_acc[d + 4] * inv, o_acc[d + 5] * inv);
+        w.w = pack_bf16(o_acc[d + 6] * inv, o_acc[d + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + d) = w;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag && a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+                 : "memory");
+  }
+}
+
+// Splits element strides (batch, row, head) of a [B, rows, heads, hd]-like view into the 2D
+// (row, column) bookkeeping the tensor maps use.  Returns false if the view is not expressible.
+static bool split_strides(int64_t bs, int64_t rs, int64_t hs, int* batch_rows, int* head_rows,
+                          int* head_cols) {
+  if (rs <= 0) return false;
+  if (bs % rs != 0) return false;
+  *batch_rows = (int)(bs / rs);
+  if (hs % rs == 0 && hs >= rs) { *head_rows = (int)(hs / rs); *head_cols = 0; }
+  else if (hs < rs) { *head_rows = 0; *head_cols = (int)hs; }
+  else return false;
+  return true;
+}
+
+template <int HD>
+static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                     const FaArgs& a, dim3 grid, cudaStream_t st, bool pdl) {
+  // tiles (Q, 2 x K, 2 x V, 2 x P) + 11 barriers + TMEM slot / flags + exchange area
+  constexpr size_t smem = (size_t)(HD / 64) * kAtomBytes * 5 + 2 * 2 * kAtomBytes + 88 + 16 + 2048 + 512;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(flash_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  cudaError_t e = launch(flash_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, st, pdl, mq, mk, mv, a);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_flash_prefill_tc(void* out, const void* q, const void* k, const void* v,
+                                     int batch, int S, int kv_len, int q_pos0, int n_q, int n_kv,
+                                     int hd,
+                                     int64_t q_bs, int64_t q_rs, int64_t q_hs,
+                                     int64_t k_bs, int64_t k_rs, int64_t k_hs,
+                                     int64_t v_bs, int64_t v_rs, int64_t v_hs,
+                                     int64_t o_bs, int64_t o_rs, int64_t o_hs,
+                                     int causal, float scale, int* status, int flags,
+                                     b200_stream_t stream) {
+  if (!out || !q || !k || !v) return B200_ERR_ARG;
+  if (batch <= 0 || S <= 0 || kv_len <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 ||
+      (hd != 64 && hd != 128) || batch > 65535 || n_q > 65535)
+    return B200_ERR_SHAPE;
+  const int64_t strides[12] = {q_bs, q_rs, q_hs, k_bs, k_rs, k_hs, v_bs, v_rs, v_hs, o_bs, o_rs, o_hs};
+  for (int i = 0; i < 12; ++i) if (strides[i] & 7) return B200_ERR_ALIGN;
+  if (((uintptr_t)out & 15) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15))
+    return B200_ERR_ALIGN;
+  FaArgs a;
+  a.o = (uint16_t*)out; a.o_bs = o_bs; a.o_rs = o_rs; a.o_hs = o_hs; a.status = status;
+  a.S = S; a.kv_len = kv_len; a.q_pos0 = q_pos0; a.group = n_q / n_kv; a.causal = causal ? 1 : 0;
+  a.n_q = n_q;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  if (!split_strides(q_bs, q_rs, q_hs, &a.q_batch_rows, &a.q_head_rows, &a.q_head_cols) ||
+      !split_strides(k_bs, k_rs, k_hs, &a.k_batch_rows, &a.k_head_rows, &a.k_head_cols) ||
+      !split_strides(v_bs, v_rs, v_hs, &a.v_batch_rows, &a.v_head_rows, &a.v_head_cols))
+    return B200_ERR_SHAPE;
+  int rc = get_encode();
+  if (rc != B200_OK) return rc;
+  // 2D views [rows, row_stride]; rows stop at the last valid row so that tiles reaching past
+  // it are zero-filled by the TMA unit instead of touching memory the caller does not own
+  const uint64_t q_rows = (uint64_t)(batch - 1) * a.q_batch_rows + (uint64_t)(n_q - 1) * a.q_head_rows + S;
+  const uint64_t k_rows = (uint64_t)(batch - 1) * a.k_batch_rows + (uint64_t)(n_kv - 1) * a.k_head_rows + kv_len;
+  const uint64_t v_rows = (uint64_t)(batch - 1) * a.v_batch_rows + (uint64_t)(n_kv - 1) * a.v_head_rows + kv_len;
+  const uint64_t q_cols = a.q_head_cols ? (uint64_t)a.q_head_cols * n_q : (uint64_t)hd;
+  const uint64_t k_cols = a.k_head_cols ? (uint64_t)a.k_head_cols * n_kv : (uint64_t)hd;
+  const uint64_t v_cols = a.v_head_cols ? (uint64_t)a.v_head_cols * n_kv : (uint64_t)hd;
+  CUtensorMap mq, mk, mv;
+  if ((rc = make_map(&mq, q, q_rows, q_cols, (uint64_t)q_rs, 128, 64)) != B200_OK) return rc;
+  if ((rc = make_map(&mk, k, k_rows, k_cols, (uint64_t)k_rs, 128, 64)) != B200_OK) return rc;
+  if ((rc = make_map(&mv, v, v_rows, v_cols, (uint64_t)v_rs, 128, 64)) != B200_OK) return rc;
+  dim3 grid((S + FA_BM - 1) / FA_BM, n_q, batch);
+  const bool pdl = (flags & B200_FLAG_PDL) != 0;
+  return hd == 128 ? fa_launch<128>(mq, mk, mv, a, grid, (cudaStream_t)stream, pdl)
+                   : fa_launch<64>(mq, mk, mv, a, grid, (cudaStream_t)stream, pdl);
+}

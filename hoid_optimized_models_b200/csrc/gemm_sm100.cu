@@ -17,10 +17,7 @@
 // Every mbarrier wait is bounded: on expiry the CTA records B200_ERR_TIMEOUT in
 // the status word, all roles leave their loops, tensor memory is released and
 // the kernel returns.
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
-#include "common.cuh"
+#include "sm100.cuh"
 
 namespace b200 {
 
@@ -31,86 +28,12 @@ constexpr uint32_t kABytes = BM * BK * 2;   // 16 KiB
 constexpr uint32_t kBBytes = BN * BK * 2;   // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr int kMaxExperts = 256;
-constexpr long long kWaitBudget = 4000000000LL;  // clock64 ticks (~2 s)
 
 struct GemmArgs {
   uint16_t* y; const uint16_t* bias; const uint16_t* resid; const int* offsets;
   int* status;
   int M, N, K, ldy, ldr, epilogue, n_groups, y_dtype;
 };
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the budget expires or another role aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  int spins = 0;
-  while (!mbar_try(bar, parity)) {
-    if ((++spins & 1023) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudget) { *abort_flag = 1; return false; }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-               ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                       uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // K-major, 128-byte-swizzled operand tile: rows 128 B apart, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -377,33 +300,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 }
 
 // ---------------------------------------------------------------- host side
-static PFN_cuTensorMapEncodeTiled g_encode = nullptr;
-
-static int get_encode() {
-  if (g_encode != nullptr) return B200_OK;
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult qr;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess ||
-      qr != cudaDriverEntryPointSuccess || fn == nullptr)
-    return B200_ERR_DRIVER;
-  g_encode = (PFN_cuTensorMapEncodeTiled)fn;
-  return B200_OK;
-}
-
-// 2D bf16 map over a row-major [rows, cols] matrix with leading dimension ld (elements);
-// box = box_rows x 64 columns, 128-byte swizzle, zero fill outside.
-static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
-                    uint32_t box_rows) {
-  cuuint64_t gdim[2] = {cols, rows};
-  cuuint64_t gstr[1] = {ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstr,
-                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_DRIVER;
-}
-
 constexpr size_t kGemmSmem = 1024 + (size_t)kStages * kStageBytes + 256 + 2 * (kMaxExperts + 1) * 4;
 
 static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
@@ -425,8 +321,8 @@ static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M
 
   CUtensorMap mx, mw;
   const uint64_t wrows = n_groups > 0 ? (uint64_t)n_groups * N : (uint64_t)N;
-  if ((rc = make_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, BM)) != B200_OK) return rc;
-  if ((rc = make_map(&mw, w, wrows, (uint64_t)K, (uint64_t)ldw, BN)) != B200_OK) return rc;
+  if ((rc = make_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, BM, BK)) != B200_OK) return rc;
+  if ((rc = make_map(&mw, w, wrows, (uint64_t)K, (uint64_t)ldw, BN, BK)) != B200_OK) return rc;
 
   GemmArgs a;
   a.y = (uint16_t*)y; a.bias = (const uint16_t*)bias; a.resid = (const uint16_t*)resid;

@@ -317,7 +317,7 @@ def moe_decode_down(y: Tensor, act: Tensor, w_down: Tensor, ids: Tensor,
 # ----------------------------------------------------------------------------- flash prefill
 @torch.library.custom_op("b200::flash_prefill", mutates_args=("out",))
 def flash_prefill(out: Tensor, q: Tensor, k: Tensor, v: Tensor, kv_len: int, causal: bool,
-                  scale: float, q_pos0: int = 0) -> None:
+                  scale: float, q_pos0: int = 0, impl: str = "tc") -> None:
     """Flash attention over strided views.
 
     q / out: [B, S, n_q, hd] views; k / v: [B, n_kv, L, hd] views (any strides with a
@@ -329,6 +329,14 @@ def flash_prefill(out: Tensor, q: Tensor, k: Tensor, v: Tensor, kv_len: int, cau
             raise RuntimeError("last dimension must be contiguous")
     B, S, n_q, hd = q.shape
     n_kv = k.shape[1]
+    if impl == "tc":   # tcgen05 / TMEM kernel (the product path); "mma" keeps the mma.sync tiles
+        check(_lib.lib().b200_flash_prefill_tc(
+            out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, kv_len, q_pos0, n_q,
+            n_kv, hd, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(2), k.stride(1),
+            v.stride(0), v.stride(2), v.stride(1), out.stride(0), out.stride(1), out.stride(2),
+            1 if causal else 0, scale, status_word(q.device).data_ptr(), _flags(), _stream()),
+            "b200_flash_prefill_tc")
+        return
     check(_lib.lib().b200_flash_prefill(
         out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, kv_len, q_pos0, n_q, n_kv,
         hd, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(2), k.stride(1),

@@ -221,6 +221,18 @@ int b200_flash_prefill(void* out, const void* q, const void* k, const void* v,
                        int64_t v_bs, int64_t v_rs, int64_t v_hs,
                        int64_t o_bs, int64_t o_rs, int64_t o_hs,
                        int causal, float scale, int flags, b200_stream_t stream);
+/* Same contract on the tcgen05 tensor cores (TMA-fed, S and O accumulators in tensor memory,
+ * 128 x 128 tiles).  Each of q / k / v must be expressible as a 2D row-major view: the batch
+ * stride a multiple of the row stride, and the head stride either a multiple of the row stride
+ * (heads are row blocks, as in the KV cache) or smaller than it (heads are column blocks, as in
+ * packed projections).  status (nullable) receives B200_ERR_TIMEOUT if a bounded wait expired. */
+int b200_flash_prefill_tc(void* out, const void* q, const void* k, const void* v,
+                          int batch, int S, int kv_len, int q_pos0, int n_q, int n_kv, int hd,
+                          int64_t q_bs, int64_t q_rs, int64_t q_hs,
+                          int64_t k_bs, int64_t k_rs, int64_t k_hs,
+                          int64_t v_bs, int64_t v_rs, int64_t v_hs,
+                          int64_t o_bs, int64_t o_rs, int64_t o_hs,
+                          int causal, float scale, int* status, int flags, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * a9. MoE router: fp32 softmax over E logits -> top-k (ties: lowest expert index) ->

@@ -305,7 +305,8 @@ def test_moe_grouped_gemm(dev):
 @pytest.mark.parametrize("S,n_q,n_kv,hd,causal", [(64, 4, 1, 128, True), (200, 8, 2, 128, True),
                                                   (1000, 32, 8, 128, True), (512, 16, 16, 64, False),
                                                   (77, 4, 4, 64, False), (1500, 20, 20, 64, False)])
-def test_flash_prefill(dev, S, n_q, n_kv, hd, causal):
+@pytest.mark.parametrize("impl", ["tc", "mma"])
+def test_flash_prefill(dev, S, n_q, n_kv, hd, causal, impl):
     from hoid_optimized_models_b200 import ops
     from oracle.ref_decoder import causal_attention
     g = torch.Generator().manual_seed(S)
@@ -325,6 +326,7 @@ def test_flash_prefill(dev, S, n_q, n_kv, hd, causal):
         ref = torch.einsum("hsk,hkd->shd", p, vv)
     out = torch.empty(1, S, n_q, hd, dtype=torch.bfloat16, device=dev)
     ops.flash_prefill(out, q.to(dev).view(1, S, n_q, hd), kc.to(dev).unsqueeze(0),
-                      vc.to(dev).unsqueeze(0), S, causal, hd ** -0.5)
+                      vc.to(dev).unsqueeze(0), S, causal, hd ** -0.5, impl=impl)
+    ops.check_status(dev)
     # P and the output are rounded to bf16
     assert rel_err(out[0], ref) < 2e-2
