@@ -7,7 +7,9 @@
 
 namespace b200 {
 
-constexpr int kNormMaxChunks = 8;  // 8-element chunks per thread -> N <= threads * 64
+constexpr int kNormChunkCap = 8;  // 8-element chunks per thread -> N <= threads * 64
+// The kernels are instantiated for 1, 2, 4 and 8 chunks per thread so that narrow rows do not
+// pay the register (= occupancy) cost of wide ones.
 
 __device__ __forceinline__ void load8(const void* p, int dtype, size_t chunk, float* f) {
   if (dtype == B200_F32) {
@@ -41,6 +43,7 @@ struct RmsArgs {
   int N, in_dtype, out_dtype; float eps;
 };
 
+template <int kNormMaxChunks>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(RmsArgs p) {
   __shared__ float red[32];
   const int nchunk = p.N >> 3;
@@ -91,6 +94,7 @@ struct LnArgs {
   int N, in_dtype, out_dtype; float eps;
 };
 
+template <int kNormMaxChunks>
 __global__ void __launch_bounds__(256) add_layernorm_kernel(LnArgs p) {
   __shared__ float red[32];
   const int nchunk = p.N >> 3;
@@ -165,10 +169,16 @@ extern "C" int b200_add_rmsnorm(void* resid_out, void* norm_out, int out_dtype,
   if (!norm_out || !a || !w) return B200_ERR_ARG;
   if (rows <= 0 || N <= 0 || (N & 7) != 0) return B200_ERR_SHAPE;
   const int threads = norm_threads(N);
-  if ((N >> 3) > threads * kNormMaxChunks) return B200_ERR_SHAPE;
+  if ((N >> 3) > threads * kNormChunkCap) return B200_ERR_SHAPE;
   RmsArgs p{resid_out, norm_out, a, b, (const uint16_t*)w, N, in_dtype, out_dtype, eps};
-  cudaError_t e = launch(add_rmsnorm_kernel, dim3(rows), dim3(threads), 0, (cudaStream_t)stream,
-                         (flags & B200_FLAG_PDL) != 0, p);
+  const int cpt = ((N >> 3) + threads - 1) / threads;
+  const bool pdl = (flags & B200_FLAG_PDL) != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  if (cpt <= 1) e = launch(add_rmsnorm_kernel<1>, dim3(rows), dim3(threads), 0, st, pdl, p);
+  else if (cpt <= 2) e = launch(add_rmsnorm_kernel<2>, dim3(rows), dim3(threads), 0, st, pdl, p);
+  else if (cpt <= 4) e = launch(add_rmsnorm_kernel<4>, dim3(rows), dim3(threads), 0, st, pdl, p);
+  else e = launch(add_rmsnorm_kernel<8>, dim3(rows), dim3(threads), 0, st, pdl, p);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
@@ -179,10 +189,16 @@ extern "C" int b200_add_layernorm(void* resid_out, void* norm_out, int out_dtype
   if (!norm_out || !x || !gamma || !beta) return B200_ERR_ARG;
   if (rows <= 0 || N <= 0 || (N & 7) != 0) return B200_ERR_SHAPE;
   const int threads = norm_threads(N);
-  if ((N >> 3) > threads * kNormMaxChunks) return B200_ERR_SHAPE;
+  if ((N >> 3) > threads * kNormChunkCap) return B200_ERR_SHAPE;
   LnArgs p{resid_out, norm_out, x, (const uint16_t*)bias, resid, (const uint16_t*)gamma,
            (const uint16_t*)beta, N, in_dtype, out_dtype, eps};
-  cudaError_t e = launch(add_layernorm_kernel, dim3(rows), dim3(threads), 0, (cudaStream_t)stream,
-                         (flags & B200_FLAG_PDL) != 0, p);
+  const int cpt = ((N >> 3) + threads - 1) / threads;
+  const bool pdl = (flags & B200_FLAG_PDL) != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  if (cpt <= 1) e = launch(add_layernorm_kernel<1>, dim3(rows), dim3(threads), 0, st, pdl, p);
+  else if (cpt <= 2) e = launch(add_layernorm_kernel<2>, dim3(rows), dim3(threads), 0, st, pdl, p);
+  else if (cpt <= 4) e = launch(add_layernorm_kernel<4>, dim3(rows), dim3(threads), 0, st, pdl, p);
+  else e = launch(add_layernorm_kernel<8>, dim3(rows), dim3(threads), 0, st, pdl, p);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }

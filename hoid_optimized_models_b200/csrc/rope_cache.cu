@@ -1,4 +1,4 @@
-// (QK-RMSNorm +) rotate-half RoPE + KV-cache write, one warp per (token, head).
+// (QK-RMSNorm +) rotate-half RoPE + KV-cache write, hd/8 lanes per (token, head).
 //
 // Heads of the packed projection row are laid out q[0..n_q), k[0..n_kv),
 // v[0..n_kv).  q heads go to q_out, k heads are normalised/rotated straight
@@ -14,80 +14,97 @@ struct RopeArgs {
   int s, n_q, n_kv, hd, max_seq, q_dtype, qkv_dtype; float eps;
 };
 
-__device__ __forceinline__ float ld_elem(const void* p, int dtype, size_t i) {
-  return dtype == B200_F32 ? reinterpret_cast<const float*>(p)[i]
-                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+__device__ __forceinline__ void ld4(const void* p, int dtype, size_t i, float* f) {
+  if (dtype == B200_F32) {
+    const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  } else {
+    const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p) + i);
+    f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  }
+}
+__device__ __forceinline__ void st4(void* p, int dtype, size_t i, const float* f) {
+  if (dtype == B200_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = make_float4(f[0], f[1], f[2], f[3]);
+  } else {
+    uint2 v;
+    v.x = pack_bf16(f[0], f[1]); v.y = pack_bf16(f[2], f[3]);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p) + i) = v;
+  }
 }
 
+// A group of LPH = hd/8 lanes owns one (token, head): lane l of the group holds dims
+// [4l, 4l+4) of the first half and the matching four of the second half, so every access is
+// 8 or 16 bytes wide and a warp covers 32 / LPH heads.
 __global__ void __launch_bounds__(128) qk_rope_cache_kernel(RopeArgs a) {
+  const int hd = a.hd, half = hd >> 1;
+  const int lph = half >> 2;                       // lanes per head: 16 (hd 128) or 8 (hd 64)
   const int lane = threadIdx.x & 31;
+  const int sub = lane / lph, l = lane - sub * lph;
+  const int hpw = 32 / lph;                        // heads per warp
   const int slots = a.n_q + 2 * a.n_kv;
-  const long slot = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const long slot = ((long)blockIdx.x * 4 + (threadIdx.x >> 5)) * hpw + sub;
   pdl_launch_dependents();
   pdl_wait();
-  if (slot >= (long)a.s * slots) return;
-  const int token = (int)(slot / slots);
-  const int h = (int)(slot - (long)token * slots);
+  const bool active = slot < (long)a.s * slots;
+  const int token = active ? (int)(slot / slots) : 0;
+  const int h = active ? (int)(slot - (long)token * slots) : 0;
   const int pos = a.pos_dev[0] + token;
-  if (pos < 0 || pos >= a.max_seq) return;  // never write outside the cache
-  const int hd = a.hd, half = hd >> 1;
+  const bool in_cache = pos >= 0 && pos < a.max_seq;   // never write outside the cache
   const size_t src0 = ((size_t)token * slots + h) * hd;
 
   if (h < a.n_q + a.n_kv) {
     const bool is_q = h < a.n_q;
     const uint16_t* nw = is_q ? a.qn_w : a.kn_w;
-    float lo[2], hi[2];
-    float ss = 0.f;
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int p = lane + t * 32;
-      lo[t] = hi[t] = 0.f;
-      if (p < half) {
-        lo[t] = ld_elem(a.qkv, a.qkv_dtype, src0 + p);
-        hi[t] = ld_elem(a.qkv, a.qkv_dtype, src0 + p + half);
-        ss += lo[t] * lo[t] + hi[t] * hi[t];
-      }
+    float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) {
+      ld4(a.qkv, a.qkv_dtype, src0 + 4 * l, lo);
+      ld4(a.qkv, a.qkv_dtype, src0 + half + 4 * l, hi);
     }
     float inv = 1.f;
-    if (nw != nullptr) {
-      ss = warp_sum(ss);
+    if (nw != nullptr) {                             // warp-uniform: all heads or none are normed
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+      // only the lanes of this head take part: other groups of the warp may hold a V head
+      const unsigned gmask = (lph == 32 ? 0xffffffffu : ((1u << lph) - 1u)) << (sub * lph);
+      for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(gmask, ss, o);
       inv = rsqrtf(ss / (float)hd + a.eps);
     }
+    if (!active || (!is_q && !in_cache)) return;
+    if (nw != nullptr) {
+      float wl[4], wh[4];
+      ld4(nw, B200_BF16, 4 * l, wl);
+      ld4(nw, B200_BF16, half + 4 * l, wh);
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int p = lane + t * 32;
-      if (p < half) {
-        float x = lo[t], y = hi[t];
-        if (nw != nullptr) {
-          x = x * inv * __uint_as_float((uint32_t)nw[p] << 16);
-          y = y * inv * __uint_as_float((uint32_t)nw[p + half] << 16);
-        }
-        const float c = a.cos_t[(size_t)pos * half + p];
-        const float sn = a.sin_t[(size_t)pos * half + p];
-        const float r0 = x * c - y * sn;
-        const float r1 = y * c + x * sn;
-        if (is_q) {
-          const size_t d = ((size_t)token * a.n_q + h) * hd;
-          if (a.q_dtype == B200_F32) {
-            reinterpret_cast<float*>(a.q_out)[d + p] = r0;
-            reinterpret_cast<float*>(a.q_out)[d + p + half] = r1;
-          } else {
-            reinterpret_cast<__nv_bfloat16*>(a.q_out)[d + p] = __float2bfloat16(r0);
-            reinterpret_cast<__nv_bfloat16*>(a.q_out)[d + p + half] = __float2bfloat16(r1);
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.kcache) +
-                               ((size_t)(h - a.n_q) * a.max_seq + pos) * hd;
-          dst[p] = __float2bfloat16(r0);
-          dst[p + half] = __float2bfloat16(r1);
-        }
-      }
+      for (int e = 0; e < 4; ++e) { lo[e] = lo[e] * inv * wl[e]; hi[e] = hi[e] * inv * wh[e]; }
+    }
+    float c[4], sn[4];
+    ld4(a.cos_t, B200_F32, (size_t)pos * half + 4 * l, c);
+    ld4(a.sin_t, B200_F32, (size_t)pos * half + 4 * l, sn);
+    float r0[4], r1[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      r0[e] = lo[e] * c[e] - hi[e] * sn[e];
+      r1[e] = hi[e] * c[e] + lo[e] * sn[e];
+    }
+    if (is_q) {
+      const size_t d = ((size_t)token * a.n_q + h) * hd;
+      st4(a.q_out, a.q_dtype, d + 4 * l, r0);
+      st4(a.q_out, a.q_dtype, d + half + 4 * l, r1);
+    } else {
+      const size_t d = ((size_t)(h - a.n_q) * a.max_seq + pos) * hd;
+      st4(a.kcache, B200_BF16, d + 4 * l, r0);
+      st4(a.kcache, B200_BF16, d + half + 4 * l, r1);
     }
   } else {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.vcache) +
-                         ((size_t)(h - a.n_q - a.n_kv) * a.max_seq + pos) * hd;
-    for (int d = lane; d < hd; d += 32)
-      dst[d] = __float2bfloat16(ld_elem(a.qkv, a.qkv_dtype, src0 + d));
+    if (!active || !in_cache) return;
+    const size_t d = ((size_t)(h - a.n_q - a.n_kv) * a.max_seq + pos) * hd;
+    float x[4], y[4];
+    ld4(a.qkv, a.qkv_dtype, src0 + 8 * l, x);
+    ld4(a.qkv, a.qkv_dtype, src0 + 8 * l + 4, y);
+    st4(a.vcache, B200_BF16, d + 8 * l, x);
+    st4(a.vcache, B200_BF16, d + 8 * l + 4, y);
   }
 }
 
@@ -108,7 +125,8 @@ extern "C" int b200_qk_rope_cache(void* q_out, int q_dtype, void* kcache, void* 
   RopeArgs a{q_out, (uint16_t*)kcache, (uint16_t*)vcache, qkv, (const uint16_t*)qn_w,
              (const uint16_t*)kn_w, cos_t, sin_t, pos_dev, s, n_q, n_kv, hd, max_seq,
              q_dtype, qkv_dtype, eps};
-  const long warps = (long)s * (n_q + 2 * n_kv);
+  const int hpw = 32 / (hd / 8);   // heads per warp
+  const long warps = ((long)s * (n_q + 2 * n_kv) + hpw - 1) / hpw;
   const unsigned grid = (unsigned)((warps + 3) / 4);
   cudaError_t e = launch(qk_rope_cache_kernel, dim3(grid), dim3(128), 0, (cudaStream_t)stream,
                          (flags & B200_FLAG_PDL) != 0, a);
