@@ -5,13 +5,13 @@
 //   warp 1     MMA issuer (one lane): S_j = Q K_j^T (M128 N128, K = head dim) into one of two
 //              S accumulators in tensor memory, and O_j = P_j V_j (V consumed in its natural
 //              [key][dim] layout as an MN-major operand) into one of two O-tile accumulators
-//   warps 2-9  softmax: two threads per query row (= TMEM lane), one per half of the key
-//              columns / output dims.  Two passes over S_j with tcgen05.ld (row max, exchanged
-//              between the two halves through shared memory, then exp2 / row sum), P_j written
-//              as bf16 into a 128-byte-swizzled shared tile that the second MMA reads; O_{j-1}
-//              is pulled from tensor memory one tile later and folded into fp32 registers with
-//              the online softmax correction, so the MMA of tile j+1 overlaps the softmax of
-//              tile j.
+//   warps 2-17 softmax: four threads per query row (= TMEM lane), each owning 32 key columns
+//              and a quarter of the output dims.  A thread pulls its 32 scores with one
+//              tcgen05.ld, the row maximum is exchanged between the four through shared memory,
+//              O_{j-1} is folded from tensor memory into fp32 registers with the online-softmax
+//              correction, and P_j = exp2(...) is written as bf16 into the 128-byte-swizzled
+//              shared tile the second MMA reads.  S is double-buffered, so the tensor core works
+//              on S_{j+1} and O_j while the softmax warps are busy with tile j.
 // The score matrix never leaves the SM.  Causal tiles above the diagonal are never visited.
 // Every mbarrier wait is bounded (status word + clean TMEM release on expiry).
 #include "sm100.cuh"
@@ -19,7 +19,8 @@
 namespace b200 {
 
 constexpr int FA_BM = 128, FA_BN = 128;
-constexpr int kFaThreads = 320;   // TMA warp, MMA warp, 8 softmax warps
+constexpr int kFaParts = 4;        // softmax threads per query row
+constexpr int kFaThreads = 64 + 128 * kFaParts;   // TMA warp, MMA warp, 16 softmax warps
 constexpr uint32_t kAtomBytes = 128 * 128;   // a 128-row x 64-column bf16 box: 16 KiB
 
 struct FaArgs {
@@ -81,13 +82,13 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   unsigned char* gen = smem_raw;
   const uint32_t sQ = base;
   const uint32_t sKV = sQ + kQBytes;                    // 2 stages x (K | V)
-  const uint32_t sP = sKV + 2 * kStage;                 // 2 buffers
+  const uint32_t sP = sKV + 2 * kStage;                 // one buffer (freed by the O_j commit)
   unsigned char* gP = gen + kQBytes + 2 * kStage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kQBytes + 2 * kStage + 2 * kPBytes);
-  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7,8 p_full | 9,10 o_full
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kQBytes + 2 * kStage + kPBytes);
+  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7 p_full | 9 o_full
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xch = reinterpret_cast<float*>(tmem_slot + 4);   // [2 parities][2 halves][128 rows]
+  float* xch = reinterpret_cast<float*>(tmem_slot + 4);   // [2 parities][4 parts][128 rows] + seq
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -100,7 +101,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   if (tid == 0) {
     mbar_init(bar(0), 1);
     for (int i = 1; i <= 6; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(7), 256); mbar_init(bar(8), 256);
+    mbar_init(bar(7), 128 * kFaParts); mbar_init(bar(8), 1);
     mbar_init(bar(9), 1); mbar_init(bar(10), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -113,14 +114,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                  ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (tid < 128) reinterpret_cast<int*>(xch + 512)[tid] = 0;   // 256 16-bit exchange sequence numbers
+  for (int i = tid; i < 64 * kFaParts; i += kFaThreads)
+    reinterpret_cast<int*>(xch + 256 * kFaParts)[i] = 0;   // 16-bit exchange sequence numbers
   pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base;            // S buffers at columns 0 and 128
-  const uint32_t tO = tmem_base + 256;      // O-tile buffers at columns 256 and 256 + HD
+  const uint32_t tO = tmem_base + 256;      // O-tile accumulator
 
   // keys this query tile can see
   int kv_end = a.kv_len;
@@ -179,76 +181,84 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int j = 0; j < ntiles && ok; ++j) {
         const int st = j & 1;
         if (j + 1 < ntiles) { if (!issue_s(j + 1)) { ok = false; break; } }
-        if (!mbar_wait(bar(7 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar(7), j & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sv = sKV + st * kStage + kQBytes;
-        const uint32_t sp = sP + st * kPBytes;
+        const uint32_t sp = sP;
 #pragma unroll
         for (int k = 0; k < FA_BN / 16; ++k) {
           // A = P (K-major over keys): 16 keys = 32 bytes inside a 64-key atom
           const uint64_t da = umma_desc_k(sp + (k >> 2) * kAtomBytes + (k & 3) * 32);
           // B = V (MN-major over dims): 16 keys = two 8-row groups = 2048 bytes
           const uint64_t db = umma_desc_mn(sv + k * 2048, kAtomBytes, 1024);
-          tc_mma(tO + st * HD, da, db, idesc_o, k != 0 ? 1u : 0u);
+          tc_mma(tO, da, db, idesc_o, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar(9 + st));    // O tile ready
+        tc_commit(bar(9));         // O tile ready, P buffer free
         tc_commit(bar(3 + st));    // K/V stage free
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax warps
+    constexpr int NP = kFaParts;
     const int slab = warp & 3;                        // TMEM lanes [32 slab, 32 slab + 32)
-    const int half = (warp - 2) >> 2;                 // which half of the columns / dims
+    const int part = (warp - 2) >> 2;                 // which 32 key columns / quarter of the dims
     const int row = slab * 32 + lane;                 // query row inside the tile = TMEM lane
     const int qpos = a.q_pos0 + m0 + row;             // absolute position for the causal rule
     const uint32_t lane_addr = (uint32_t)(slab * 32) << 16;
-    constexpr int OD = HD / 2;                        // output dims owned by this thread
+    constexpr int OD = HD / NP;                       // output dims owned by this thread (32 / 16)
     float o_acc[OD];
 #pragma unroll
     for (int d = 0; d < OD; ++d) o_acc[d] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
     bool ok = true;
-    // Exchange one float per tile with the thread that owns the other half of this row:
-    // value slots are double-buffered by tile parity, a per-thread sequence number publishes
-    // them, and the reader's wait is bounded like every other wait in this kernel.
-    volatile float* xval = xch;                                        // [2][2][128]
-    volatile unsigned short* xseq = reinterpret_cast<volatile unsigned short*>(xch + 512);   // [2][128]
-    auto exchange = [&](int seq, float mine, float* other) -> bool {
-      xval[(seq & 1) * 256 + half * 128 + row] = mine;
-      __threadfence_block();
-      xseq[half * 128 + row] = (unsigned short)seq;
-      const long long t0 = clock64();
-      int spins = 0;
-      // the partner is never more than one tile ahead, so equality modulo 2^16 is enough
-      while (xseq[(half ^ 1) * 128 + row] != (unsigned short)seq &&
-             xseq[(half ^ 1) * 128 + row] != (unsigned short)(seq + 1)) {
-        if ((++spins & 255) == 0) {
-          if (*abort_flag) return false;
-          if (clock64() - t0 > kWaitBudget) { *abort_flag = 1; return false; }
-        }
-      }
-      __threadfence_block();
-      *other = xval[(seq & 1) * 256 + (half ^ 1) * 128 + row];
-      return true;
-    };
     auto ex2 = [](float x) -> float {
       float y;
       asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
       return y;
     };
+    // Exchange one float per tile between the NP threads of a row: value slots are
+    // double-buffered by sequence parity, a per-thread 16-bit sequence number publishes them,
+    // and the reader's wait is bounded like every other wait in this kernel.
+    volatile float* xval = xch;                                                   // [2][NP][128]
+    volatile unsigned short* xseq = reinterpret_cast<volatile unsigned short*>(xch + 256 * NP);
+    auto publish = [&](int seq, float mine) {
+      xval[((seq & 1) * NP + part) * 128 + row] = mine;
+      __threadfence_block();
+      xseq[part * 128 + row] = (unsigned short)seq;
+    };
+    auto collect = [&](int seq, float* others) -> bool {   // others[NP - 1]
+      const long long t0 = clock64();
+#pragma unroll
+      for (int o = 1; o < NP; ++o) {
+        const int p2 = (part + o) & (NP - 1);
+        int spins = 0;
+        // a partner is never more than one tile ahead, so these two values are the only ones
+        while (xseq[p2 * 128 + row] != (unsigned short)seq &&
+               xseq[p2 * 128 + row] != (unsigned short)(seq + 1)) {
+          if ((++spins & 255) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitBudget) { *abort_flag = 1; return false; }
+          }
+        }
+      }
+      __threadfence_block();
+#pragma unroll
+      for (int o = 1; o < NP; ++o)
+        others[o - 1] = xval[((seq & 1) * NP + ((part + o) & (NP - 1))) * 128 + row];
+      return true;
+    };
 
     auto fold_o = [&](int j, float corr) -> bool {
       // o_acc = o_acc * corr + O_j  (O_j was produced with the row maximum after tile j)
-      const int st = j & 1;
-      if (!mbar_wait(bar(9 + st), (j >> 1) & 1, abort_flag)) return false;
+      if (!mbar_wait(bar(9), j & 1, abort_flag)) return false;
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < OD / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(tO + st * HD + half * OD + lane_addr + c * 32, r);
+      for (int c = 0; c < OD / 16; ++c) {   // 16 columns at a time keeps the register count low
+        uint32_t r[16];
+        tc_ld16(tO + part * OD + c * 16 + lane_addr, r);
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], corr, __uint_as_float(r[i]));
+        for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = fmaf(o_acc[c * 16 + i], corr, __uint_as_float(r[i]));
       }
       return true;
     };
@@ -257,71 +267,70 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const int st = j & 1;
       if (!mbar_wait(bar(5 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int key0 = j * FA_BN + half * 64;          // first key of this thread's columns
-      // columns at or beyond `valid` are masked (end of the keys, or above the diagonal)
-      int valid = a.kv_len - key0;
-      if (a.causal) valid = min(valid, qpos - key0 + 1);
-      const uint32_t s_addr = tS + st * FA_BN + half * 64 + lane_addr;
-      // pass 1: row maximum over this half, then exchange with the other half
-      float mt = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tc_ld32(s_addr + c * 32, r);
-        tc_wait_ld();
+      const int key0 = j * FA_BN + part * 32;          // first key of this thread's columns
+      uint32_t r[32];
+      tc_ld32(tS + st * FA_BN + part * 32 + lane_addr, r);
+      tc_wait_ld();
+      float sv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          mt = fmaxf(mt, (c * 32 + i < valid) ? __uint_as_float(r[i]) : -INFINITY);
+      for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
+      // only the last tile(s) need masking: end of the keys, or the causal diagonal
+      const bool need_mask = (j * FA_BN + FA_BN > a.kv_len) ||
+                             (a.causal && j * FA_BN + FA_BN - 1 > a.q_pos0 + m0);
+      if (need_mask) {
+        int valid = a.kv_len - key0;
+        if (a.causal) valid = min(valid, qpos - key0 + 1);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[i] = (i < valid) ? sv[i] : -INFINITY;
       }
-      float mt_other;
-      if (!exchange(j + 1, mt, &mt_other)) { ok = false; break; }
-      mt = fmaxf(mt, mt_other);
+      float mt = sv[0];
+#pragma unroll
+      for (int i = 1; i < 32; ++i) mt = fmaxf(mt, sv[i]);
+      publish(j + 1, mt);
+      // while the partners catch up: fold the previous tile's output (this also proves that
+      // the tensor core is done reading the P buffer)
+      if (j > 0) { if (!fold_o(j - 1, corr_prev)) { ok = false; break; } }
+      float mo[NP - 1];
+      if (!collect(j + 1, mo)) { ok = false; break; }
+#pragma unroll
+      for (int o = 0; o < NP - 1; ++o) mt = fmaxf(mt, mo[o]);
       const float m_new = fmaxf(m_run, mt * a.scale_log2);
       const float mu = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = ex2(m_run - mu);
-      // pass 2: p = exp2(s * scale - m), row sum, P tile (bf16, 128-byte swizzle, K-major);
-      // this half's 64 keys are exactly one 64-key atom of the P tile
+      // p = exp2(s * scale - m), row sum, P tile (bf16, 128-byte swizzle, K-major): this
+      // thread's 32 keys are four 16-byte chunks of atom part / 2
       float ps = 0.f;
-      unsigned char* prow = gP + st * kPBytes + half * kAtomBytes + row * 128;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tc_ld32(s_addr + c * 32, r);
-        tc_wait_ld();
-        float p[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float e = ex2(fmaf(__uint_as_float(r[i]), a.scale_log2, -mu));
-          p[i] = (c * 32 + i < valid) ? e : 0.f;
-          ps += p[i];
-        }
+      for (int i = 0; i < 32; ++i) { sv[i] = ex2(fmaf(sv[i], a.scale_log2, -mu)); ps += sv[i]; }
+      unsigned char* prow = gP + (part >> 1) * kAtomBytes + row * 128;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16(p[q4 * 8 + 0], p[q4 * 8 + 1]); w.y = pack_bf16(p[q4 * 8 + 2], p[q4 * 8 + 3]);
-          w.z = pack_bf16(p[q4 * 8 + 4], p[q4 * 8 + 5]); w.w = pack_bf16(p[q4 * 8 + 6], p[q4 * 8 + 7]);
-          const int chunk = c * 4 + q4;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
-        }
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 w;
+        w.x = pack_bf16(sv[q4 * 8 + 0], sv[q4 * 8 + 1]); w.y = pack_bf16(sv[q4 * 8 + 2], sv[q4 * 8 + 3]);
+        w.z = pack_bf16(sv[q4 * 8 + 4], sv[q4 * 8 + 5]); w.w = pack_bf16(sv[q4 * 8 + 6], sv[q4 * 8 + 7]);
+        const int chunk = (part & 1) * 4 + q4;
+        *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
       }
       l_run = l_run * corr + ps;
       m_run = m_new;
+      corr_prev = corr;
       // make the P tile visible to the tensor core (async proxy) and hand it over
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
-      mbar_arrive(bar(7 + st));
-      // fold the previous tile's output while the tensor core works on this one
-      if (j > 0) { if (!fold_o(j - 1, corr_prev)) { ok = false; break; } }
-      corr_prev = corr;
+      mbar_arrive(bar(7));
     }
     if (ok && ntiles > 0) ok = fold_o(ntiles - 1, corr_prev);
-    // the row sum is split between the two halves
-    float l_other = 0.f;
-    if (ok) ok = exchange(ntiles + 1, l_run, &l_other);
-    l_run += l_other;
+    // the row sum is split between the NP threads of the row
+    if (ok) {
+      publish(ntiles + 1, l_run);
+      float lo[NP - 1];
+      ok = collect(ntiles + 1, lo);
+#pragma unroll
+      for (int o = 0; o < NP - 1; ++o) l_run += lo[o];
+    }
     if (ok && m0 + row < a.S) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint16_t* dst = a.o + (long)b * a.o_bs + (long)(m0 + row) * a.o_rs + (long)head * a.o_hs + half * OD;
+      uint16_t* dst = a.o + (long)b * a.o_bs + (long)(m0 + row) * a.o_rs + (long)head * a.o_hs + part * OD;
 #pragma unroll
       for (int d = 0; d < OD; d += 8) {
         uint4 w;
@@ -361,8 +370,9 @@ static bool split_strides(int64_t bs, int64_t rs, int64_t hs, int* batch_rows, i
 template <int HD>
 static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                      const FaArgs& a, dim3 grid, cudaStream_t st, bool pdl) {
-  // tiles (Q, 2 x K, 2 x V, 2 x P) + 11 barriers + TMEM slot / flags + exchange area
-  constexpr size_t smem = (size_t)(HD / 64) * kAtomBytes * 5 + 2 * 2 * kAtomBytes + 88 + 16 + 2048 + 512;
+  // tiles (Q, 2 x K, 2 x V, P) + 11 barriers + TMEM slot / flags + exchange values and sequence numbers
+  constexpr size_t smem = (size_t)(HD / 64) * kAtomBytes * 5 + 2 * kAtomBytes + 88 + 16 +
+                          (size_t)2 * kFaParts * 128 * 4 + (size_t)kFaParts * 128 * 2;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
