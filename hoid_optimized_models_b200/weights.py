@@ -114,3 +114,65 @@ def make_encoder_weights(cfg, seed: int = 1234, device="cpu") -> Dict[str, torch
             w[p + name + ".bias"] = _normal((H,), seed, i, slot + 1, device)
             slot += 2
     return w
+
+
+def make_whisper_weights(cfg, seed: int = 1234, device="cpu") -> Dict[str, torch.Tensor]:
+    """Whisper-architecture encoder-decoder weights under HuggingFace
+    `WhisperForConditionalGeneration` names (the ones
+    models/whisper-large-v3/whisper_decoder_optimized.py:189-228 reads).  Matrices and biases
+    N(0, 0.02^2), LayerNorm gamma 1 + N(0, 0.02^2), beta N(0, 0.02^2); k_proj has no bias."""
+    w: Dict[str, torch.Tensor] = {}
+    D, F = cfg.d_model, cfg.ffn
+    slot = [0]
+
+    def nxt():
+        slot[0] += 1
+        return slot[0]
+
+    def lin(name, n_out, n_in, layer, bias=True):
+        w[name + ".weight"] = _normal((n_out, n_in), seed, layer, nxt(), device)
+        if bias:
+            w[name + ".bias"] = _normal((n_out,), seed, layer, nxt(), device)
+
+    def ln(name, layer):
+        w[name + ".weight"] = _normal((D,), seed, layer, nxt(), device, mean=1.0)
+        w[name + ".bias"] = _normal((D,), seed, layer, nxt(), device)
+
+    def attn(prefix, layer):
+        lin(prefix + ".q_proj", D, D, layer)
+        lin(prefix + ".k_proj", D, D, layer, bias=False)
+        lin(prefix + ".v_proj", D, D, layer)
+        lin(prefix + ".out_proj", D, D, layer)
+
+    e = "model.encoder."
+    w[e + "conv1.weight"] = _normal((D, cfg.n_mels, 3), seed, 900, nxt(), device)
+    w[e + "conv1.bias"] = _normal((D,), seed, 900, nxt(), device)
+    w[e + "conv2.weight"] = _normal((D, D, 3), seed, 900, nxt(), device)
+    w[e + "conv2.bias"] = _normal((D,), seed, 900, nxt(), device)
+    w[e + "embed_positions.weight"] = _normal((cfg.n_ctx, D), seed, 900, nxt(), device)
+    for i in range(cfg.enc_layers):
+        slot[0] = 0
+        p = f"{e}layers.{i}."
+        attn(p + "self_attn", 100 + i)
+        ln(p + "self_attn_layer_norm", 100 + i)
+        lin(p + "fc1", F, D, 100 + i)
+        lin(p + "fc2", D, F, 100 + i)
+        ln(p + "final_layer_norm", 100 + i)
+    slot[0] = 50
+    ln(e + "layer_norm", 900)
+    d = "model.decoder."
+    w[d + "embed_tokens.weight"] = _normal((cfg.vocab, D), seed, 901, nxt(), device)
+    w[d + "embed_positions.weight"] = _normal((cfg.max_target, D), seed, 901, nxt(), device)
+    for i in range(cfg.dec_layers):
+        slot[0] = 0
+        p = f"{d}layers.{i}."
+        attn(p + "self_attn", 200 + i)
+        ln(p + "self_attn_layer_norm", 200 + i)
+        attn(p + "encoder_attn", 200 + i)
+        ln(p + "encoder_attn_layer_norm", 200 + i)
+        lin(p + "fc1", F, D, 200 + i)
+        lin(p + "fc2", D, F, 200 + i)
+        ln(p + "final_layer_norm", 200 + i)
+    slot[0] = 80
+    ln(d + "layer_norm", 901)
+    return w

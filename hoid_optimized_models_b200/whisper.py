@@ -1,0 +1,269 @@
+"""Whisper-large-v3-architecture encoder and cached greedy decoder on the b200 ops.
+
+Mirrors the reference's `OptimizedWhisperEncoder` (models/whisper-large-v3/whisper_optimized.py:518-671)
+and `OptimizedWhisperDecoder` (whisper_decoder_optimized.py:181-476): static buffers, CUDA-graph
+capture, `set_encoder()` to project the window's cross-attention K/V, one graph replay per token.
+
+Encoder dataflow (all tensor-core GEMMs with fused epilogues):
+    mel^T (time-major, zero-padded) -> conv1 as a GEMM over an overlapping-row view (+ bias + GELU)
+    -> conv2 (stride 2) the same way (+ bias + GELU + positional embedding as the residual)
+    -> 32 x [layernorm, gemm q|k|v + bias, flash_prefill (bidirectional), gemm out + bias + residual,
+             layernorm, gemm fc1 + bias + GELU, gemm fc2 + bias + residual] -> layernorm
+The convolutions need no im2col: a k=3 window over a time-major [T, C] buffer is three adjacent
+rows, i.e. one row of a [T_out, 3 C] matrix whose row stride is (stride * C) elements.
+
+Decoder step (fp32 activations, weights streamed once per token):
+    embed + position -> 32 x [layernorm, gemv q|k|v + bias, cache write, flash_decode (self),
+    gemv out + bias + residual, layernorm, gemv cross-q + bias, flash_decode over the encoder K/V
+    (row stride 1280), gemv out + bias + residual, layernorm, gemv fc1 + bias + GELU,
+    gemv fc2 + bias + residual] -> layernorm -> gemv tied head -> argmax -> greedy_advance
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from . import ops
+from .configs import WhisperConfig
+
+
+def _conv_as_gemm_weight(w: torch.Tensor) -> torch.Tensor:
+    """[C_out, C_in, 3] -> [C_out, 3 * C_in] with the tap index major, matching a window of three
+    adjacent time-major rows."""
+    return w.permute(0, 2, 1).reshape(w.shape[0], -1).contiguous()
+
+
+class WhisperEncoder:
+    def __init__(self, cfg: WhisperConfig, weights: Dict[str, torch.Tensor], device="cuda"):
+        self.cfg, self.device = cfg, torch.device(device)
+        dev, D = self.device, cfg.d_model
+        g = lambda n: weights["model.encoder." + n].to(dev)
+        self.w1, self.b1 = _conv_as_gemm_weight(g("conv1.weight")), g("conv1.bias")
+        self.w2, self.b2 = _conv_as_gemm_weight(g("conv2.weight")), g("conv2.bias")
+        self.pos = g("embed_positions.weight")
+        self.layers: List[Dict[str, torch.Tensor]] = []
+        for i in range(cfg.enc_layers):
+            p = f"layers.{i}."
+            a = p + "self_attn."
+            self.layers.append({
+                "ln1": (g(p + "self_attn_layer_norm.weight"), g(p + "self_attn_layer_norm.bias")),
+                "wqkv": torch.cat([g(a + n + ".weight") for n in ("q_proj", "k_proj", "v_proj")], 0).contiguous(),
+                "bqkv": torch.cat([g(a + "q_proj.bias"), torch.zeros(D, dtype=torch.bfloat16, device=dev),
+                                   g(a + "v_proj.bias")], 0).contiguous(),
+                "wo": g(a + "out_proj.weight"), "bo": g(a + "out_proj.bias"),
+                "ln2": (g(p + "final_layer_norm.weight"), g(p + "final_layer_norm.bias")),
+                "wf1": g(p + "fc1.weight"), "bf1": g(p + "fc1.bias"),
+                "wf2": g(p + "fc2.weight"), "bf2": g(p + "fc2.bias"),
+            })
+        self.ln_f = (g("layer_norm.weight"), g("layer_norm.bias"))
+        T, S = cfg.n_frames, cfg.n_ctx
+        bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+        # time-major inputs with one zero row of padding on each side
+        self.x0 = bf(T + 2, cfg.n_mels)
+        self.x1 = bf(T + 2, D)
+        self.a0 = torch.as_strided(self.x0, (T, 3 * cfg.n_mels), (cfg.n_mels, 1))
+        self.a1 = torch.as_strided(self.x1, (S, 3 * D), (2 * D, 1))
+        self.x, self.h = bf(S, D), bf(S, D)
+        self.qkv, self.ctx, self.act = bf(S, 3 * D), bf(S, D), bf(S, cfg.ffn)
+        self.out = bf(S, D)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_forward = 2 + 7 * cfg.enc_layers + 1
+
+    def load_inputs(self, mel: torch.Tensor) -> None:
+        """mel: [n_mels, n_frames] log-mel features."""
+        self.x0[1:-1].copy_(mel.t())
+
+    def forward_static(self, collect: Optional[list] = None) -> torch.Tensor:
+        cfg = self.cfg
+        S, D, nh, hd = cfg.n_ctx, cfg.d_model, cfg.heads, cfg.head_dim
+        ops.gemm(self.x1[1:-1], self.a0, self.w1, bias=self.b1, epilogue=ops.EPI_GELU)
+        ops.gemm(self.x, self.a1, self.w2, bias=self.b2, resid=self.pos, epilogue=ops.EPI_GELU)
+        x, h = self.x, self.h
+        qkv4 = self.qkv.view(1, S, 3, nh, hd)
+        q, k, v = qkv4[:, :, 0], qkv4[:, :, 1].permute(0, 2, 1, 3), qkv4[:, :, 2].permute(0, 2, 1, 3)
+        ctx4 = self.ctx.view(1, S, nh, hd)
+        for L in self.layers:
+            ops.layernorm(h, x, L["ln1"][0], L["ln1"][1], cfg.eps)
+            ops.gemm(self.qkv, h, L["wqkv"], bias=L["bqkv"])
+            ops.flash_prefill(ctx4, q, k, v, S, False, hd ** -0.5)
+            ops.gemm(x, self.ctx, L["wo"], bias=L["bo"], resid=x)
+            ops.layernorm(h, x, L["ln2"][0], L["ln2"][1], cfg.eps)
+            ops.gemm(self.act, h, L["wf1"], bias=L["bf1"], epilogue=ops.EPI_GELU)
+            ops.gemm(x, self.act, L["wf2"], bias=L["bf2"], resid=x)
+            if collect is not None:
+                collect.append(x.clone())
+        ops.layernorm(self.out, x, self.ln_f[0], self.ln_f[1], cfg.eps)
+        return self.out
+
+    def capture(self, warmup: int = 2) -> None:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(warmup):
+                self.forward_static()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.forward_static()
+
+    @torch.no_grad()
+    def encode(self, mel: torch.Tensor) -> torch.Tensor:
+        self.load_inputs(mel)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.forward_static()
+        return self.out
+
+
+class WhisperDecoder:
+    def __init__(self, cfg: WhisperConfig, weights: Dict[str, torch.Tensor], device="cuda",
+                 max_new_tokens: int = 448):
+        self.cfg, self.device = cfg, torch.device(device)
+        dev, D, H, hd = self.device, cfg.d_model, cfg.heads, cfg.head_dim
+        g = lambda n: weights["model.decoder." + n].to(dev)
+        zero_b = torch.zeros(D, dtype=torch.bfloat16, device=dev)
+        self.embed_tok, self.embed_pos = g("embed_tokens.weight"), g("embed_positions.weight")
+        self.layers: List[Dict[str, torch.Tensor]] = []
+        for i in range(cfg.dec_layers):
+            p = f"layers.{i}."
+            a, c = p + "self_attn.", p + "encoder_attn."
+            self.layers.append({
+                "ln1": (g(p + "self_attn_layer_norm.weight"), g(p + "self_attn_layer_norm.bias")),
+                "wqkv": torch.cat([g(a + n + ".weight") for n in ("q_proj", "k_proj", "v_proj")], 0).contiguous(),
+                "bqkv": torch.cat([g(a + "q_proj.bias"), zero_b, g(a + "v_proj.bias")], 0).contiguous(),
+                "wo": g(a + "out_proj.weight"), "bo": g(a + "out_proj.bias"),
+                "ln2": (g(p + "encoder_attn_layer_norm.weight"), g(p + "encoder_attn_layer_norm.bias")),
+                "wcq": g(c + "q_proj.weight"), "bcq": g(c + "q_proj.bias"),
+                "wck": g(c + "k_proj.weight"),
+                "wcv": g(c + "v_proj.weight"), "bcv": g(c + "v_proj.bias"),
+                "wco": g(c + "out_proj.weight"), "bco": g(c + "out_proj.bias"),
+                "ln3": (g(p + "final_layer_norm.weight"), g(p + "final_layer_norm.bias")),
+                "wf1": g(p + "fc1.weight"), "bf1": g(p + "fc1.bias"),
+                "wf2": g(p + "fc2.weight"), "bf2": g(p + "fc2.bias"),
+            })
+        self.ln_f = (g("layer_norm.weight"), g("layer_norm.bias"))
+        L, T, S = cfg.dec_layers, cfg.max_target, cfg.n_ctx
+        self.kv = torch.zeros(L, 2, H, T, hd, dtype=torch.bfloat16, device=dev)      # self-attention cache
+        self.cross_k = torch.zeros(L, S, D, dtype=torch.bfloat16, device=dev)         # per window
+        self.cross_v = torch.zeros(L, S, D, dtype=torch.bfloat16, device=dev)
+        # the cache-write op rotates by (cos, sin): identity tables make it a plain write
+        self.cos = torch.ones(T, hd // 2, dtype=torch.float32, device=dev)
+        self.sin = torch.zeros(T, hd // 2, dtype=torch.float32, device=dev)
+        f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
+        self.state = torch.zeros(4, dtype=torch.int32, device=dev)      # {position, kv_len, generated}
+        self.pos, self.kv_len = self.state[0:1], self.state[1:2]
+        self.enc_len = torch.full((1,), S, dtype=torch.int32, device=dev)
+        self.tok = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.tok_log = torch.zeros(max_new_tokens, dtype=torch.int32, device=dev)
+        self.e_tok, self.e_pos = f32(D), f32(D)
+        self.x, self.h = f32(D), f32(D)
+        self.qkv, self.q, self.attn, self.cq = f32(3 * D), f32(D), f32(D), f32(D)
+        self.act = f32(cfg.ffn)
+        self.logits = f32(cfg.vocab)
+        self.cand = f32(2)
+        self.self_splits = max(1, min(148 // H, (T + 63) // 64))
+        self.cross_splits = max(1, min(148 // H, (S + 63) // 64))
+        self.ws_self = ops.flash_decode_workspace(H, H, hd, self.self_splits, dev)
+        self.ws_cross = ops.flash_decode_workspace(H, H, hd, self.cross_splits, dev)
+        self.am_ws = ops.argmax_workspace(dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 3 + 13 * cfg.dec_layers + 4
+
+    @torch.no_grad()
+    def set_encoder(self, enc_out: torch.Tensor) -> None:
+        """Project the window's encoder states [n_ctx, D] (bf16) to every layer's cross K / V."""
+        for i, L in enumerate(self.layers):
+            ops.gemm(self.cross_k[i], enc_out, L["wck"])
+            ops.gemm(self.cross_v[i], enc_out, L["wcv"], bias=L["bcv"])
+
+    def step_static(self) -> None:
+        cfg = self.cfg
+        D, H, hd = cfg.d_model, cfg.heads, cfg.head_dim
+        scale = hd ** -0.5
+        ops.embed_gather(self.e_tok, self.embed_tok, self.tok)
+        ops.embed_gather(self.e_pos, self.embed_pos, self.pos)
+        x, h = self.x, self.h
+        first = True
+        for i, L in enumerate(self.layers):
+            if first:   # residual stream = token + position embedding, fused with the first norm
+                ops.add_layernorm(h, x, self.e_tok, L["ln1"][0], L["ln1"][1], cfg.eps, resid=self.e_pos)
+                first = False
+            else:
+                ops.layernorm(h, x, L["ln1"][0], L["ln1"][1], cfg.eps)
+            ops.gemv(self.qkv, h, L["wqkv"], bias=L["bqkv"])
+            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
+                              self.pos, H, H)
+            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
+                             self.ws_self, H, H, self.self_splits, scale)
+            ops.gemv(x, self.attn, L["wo"], bias=L["bo"], resid=x)
+            ops.layernorm(h, x, L["ln2"][0], L["ln2"][1], cfg.eps)
+            ops.gemv(self.cq, h, L["wcq"], bias=L["bcq"])
+            ops.flash_decode(self.attn, self.cq, self.cross_k[i], self.cross_v[i], self.enc_len,
+                             self.ws_cross, H, H, self.cross_splits, scale,
+                             kv_head_stride=hd, kv_row_stride=D)
+            ops.gemv(x, self.attn, L["wco"], bias=L["bco"], resid=x)
+            ops.layernorm(h, x, L["ln3"][0], L["ln3"][1], cfg.eps)
+            ops.gemv(self.act, h, L["wf1"], bias=L["bf1"], epilogue=ops.EPI_GELU)
+            ops.gemv(x, self.act, L["wf2"], bias=L["bf2"], resid=x)
+        ops.layernorm(h, x, self.ln_f[0], self.ln_f[1], cfg.eps)
+        ops.gemv(self.logits, h, self.embed_tok)
+        ops.argmax(self.cand, self.logits, self.am_ws)
+        ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
+
+    def capture(self, warmup: int = 2) -> None:
+        saved = (self.state.clone(), self.tok.clone(), self.tok_log.clone())
+        self.state.zero_()
+        self.state[1] = 1
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(warmup):
+                self.step_static()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.step_static()
+        torch.cuda.synchronize()
+        self.state.copy_(saved[0]); self.tok.copy_(saved[1]); self.tok_log.copy_(saved[2])
+
+    def set_step(self, tok: int, pos: int, generated: int = 0) -> None:
+        self.tok.fill_(tok)
+        self.state.copy_(torch.tensor([pos, pos + 1, generated, 0], dtype=torch.int32))
+
+    def _run(self) -> None:
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step_static()
+
+    @torch.no_grad()
+    def generate(self, prefix: List[int], n_new: int, collect_logits: Optional[list] = None) -> List[int]:
+        """Feeds the forced prefix token by token (teacher forcing), then decodes n_new tokens
+        greedily.  Returns the generated tokens."""
+        for p, t in enumerate(prefix):
+            self.set_step(t, p, 0)
+            self._run()
+            if collect_logits is not None:
+                collect_logits.append(self.logits.float().cpu().clone())
+        # the step for the last prefix token has already produced the first new token
+        out = [int(self.tok.item())]
+        pos = len(prefix)
+        self.state.copy_(torch.tensor([pos, pos + 1, 0, 0], dtype=torch.int32))
+        for _ in range(n_new - 1):
+            self._run()
+            if collect_logits is not None:
+                collect_logits.append(self.logits.float().cpu().clone())
+        out.extend(self.tok_log[:n_new - 1].tolist())
+        return out
+
+
+class OptimizedWhisperEncoder(WhisperEncoder):
+    """Name-compatible with models/whisper-large-v3/whisper_optimized.py:518."""
+
+
+class OptimizedWhisperDecoder(WhisperDecoder):
+    """Name-compatible with models/whisper-large-v3/whisper_decoder_optimized.py:181."""

@@ -71,6 +71,19 @@ def main():
     np.savez_compressed(os.path.join(HERE, "encoder_xlmr.npz"), ids=eids.numpy(),
                         hidden_cls=torch.stack([h[:, 0] for h in hs]).numpy(), pooled=pooled.numpy())
     print("xlmr", pooled.shape)
+    # Whisper architecture (encoder + teacher-forced decoder)
+    from hoid_optimized_models_b200.configs import WHISPER_LARGE_V3
+    from hoid_optimized_models_b200.weights import make_whisper_weights
+    from oracle import ref_whisper as W
+    wcfg = replace(WHISPER_LARGE_V3, name="whisper-tiny", d_model=128, enc_layers=2, dec_layers=2,
+                   heads=4, ffn=256, n_mels=16, n_frames=60, n_ctx=30, max_target=24, vocab=300)
+    ww = make_whisper_weights(wcfg, SEED)
+    mel = torch.randn(16, 60, generator=torch.Generator().manual_seed(SEED)).clamp(-1.5, 1.5)
+    dids = torch.randint(3, 300, (9,), generator=torch.Generator().manual_seed(SEED + 1))
+    enc, lg = W.hf_forward(W.hf_model(wcfg, ww), mel, dids)
+    np.savez_compressed(os.path.join(HERE, "whisper.npz"), mel=mel.numpy(), dec_ids=dids.numpy(),
+                        enc_tail=enc[-4:].numpy(), logits_tail=lg[-2:].numpy())
+    print("whisper", enc.shape, lg.shape)
     with open(os.path.join(HERE, "versions.json"), "w") as f:
         json.dump(meta, f, indent=1)
 

@@ -104,3 +104,22 @@ def test_encoder_restatement_matches_golden_and_hf():
     pytest.importorskip("transformers")
     hs, p2 = E.hf_forward(E.hf_model(cfg, w), ids)
     assert float((p2 - pooled).abs().max()) <= 1e-5
+
+
+def test_whisper_restatement_matches_golden_and_hf():
+    from hoid_optimized_models_b200.configs import WHISPER_LARGE_V3
+    from hoid_optimized_models_b200.weights import make_whisper_weights
+    from oracle import ref_whisper as W
+    cfg = replace(WHISPER_LARGE_V3, name="whisper-tiny", d_model=128, enc_layers=2, dec_layers=2,
+                  heads=4, ffn=256, n_mels=16, n_frames=60, n_ctx=30, max_target=24, vocab=300)
+    gold = np.load(os.path.join(GOLD, "whisper.npz"))
+    w = make_whisper_weights(cfg, 1234)
+    mel, ids = torch.from_numpy(gold["mel"]), torch.from_numpy(gold["dec_ids"])
+    enc = W.encoder_forward(cfg, w, mel)
+    lg = W.decoder_forward(cfg, w, enc, ids)
+    assert np.abs(enc[-4:].numpy() - gold["enc_tail"]).max() <= 1e-4 * np.abs(gold["enc_tail"]).max()
+    assert np.abs(lg[-2:].numpy() - gold["logits_tail"]).max() <= 1e-4 * np.abs(gold["logits_tail"]).max()
+    pytest.importorskip("transformers")
+    enc2, lg2 = W.hf_forward(W.hf_model(cfg, w), mel, ids)
+    assert float((enc2 - enc).abs().max()) <= 1e-4 * float(enc2.abs().max())
+    assert float((lg2 - lg).abs().max()) <= 1e-4 * float(lg2.abs().max())

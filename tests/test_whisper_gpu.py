@@ -1,0 +1,55 @@
+"""Whisper-large-v3-architecture encoder and cached decoder on the GPU against the fp32 CPU
+oracle, at the real layer widths (d_model 1280, 20 heads, FFN 5120, 128 mel bins x 3000 frames,
+1500 encoder positions) with reduced depth and vocabulary.  Tolerances: encoder residual streams
+<= 2e-2 max relative error per layer, decoder logits cosine >= 0.999 per step, greedy tokens equal
+to the oracle's (teacher forced) except where its top-2 margin is within twice the logit error."""
+from dataclasses import replace
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_whisper_arch(dev):
+    from hoid_optimized_models_b200 import ops
+    from hoid_optimized_models_b200.configs import WHISPER_LARGE_V3
+    from hoid_optimized_models_b200.weights import make_whisper_weights
+    from hoid_optimized_models_b200.whisper import WhisperDecoder, WhisperEncoder
+    from oracle import ref_whisper as W
+    cfg = replace(WHISPER_LARGE_V3, name="whisper-L2", enc_layers=2, dec_layers=2, vocab=2048)
+    w = make_whisper_weights(cfg, 5)
+    mel = torch.randn(cfg.n_mels, cfg.n_frames, generator=torch.Generator().manual_seed(5)).clamp(-1.5, 1.5)
+    enc = WhisperEncoder(cfg, w, device=dev)
+    enc.load_inputs(mel.to(dev).to(torch.bfloat16))
+    hid = []
+    out = enc.forward_static(collect=hid).float().cpu()
+    ops.check_status(dev)
+    ref_out, ref_hid = W.encoder_forward(cfg, w, mel.to(torch.bfloat16).float(), keep_hidden=True)
+    for l in range(cfg.enc_layers):
+        err = float((hid[l].float().cpu() - ref_hid[l]).abs().max() / ref_hid[l].abs().max())
+        assert err < 2e-2, f"encoder layer {l}: {err}"
+    assert float((out - ref_out).abs().max() / ref_out.abs().max()) < 2e-2
+    enc.capture()
+    assert torch.equal(enc.encode(mel.to(dev).to(torch.bfloat16)).float().cpu(), out)
+
+    dec = WhisperDecoder(cfg, w, device=dev)
+    dec.set_encoder(enc.out)
+    ops.check_status(dev)
+    dec.capture()
+    prefix, n_new = [7, 1000, 33, 512], 12
+    logits = []
+    toks = dec.generate(prefix, n_new, collect_logits=logits)
+    seq = torch.tensor(prefix + toks[:-1])
+    # the oracle sees the GPU's own (bf16) encoder output, so only the decoder is compared here
+    lg_ref = W.decoder_forward(cfg, w, enc.out.float().cpu(), seq)
+    got = torch.stack(logits)
+    cos = torch.nn.functional.cosine_similarity(got, lg_ref, dim=-1)
+    assert float(cos.min()) >= 0.999, float(cos.min())
+    err = (got - lg_ref).abs().max(-1).values
+    top2 = lg_ref.topk(2, -1).values
+    margin = top2[:, 0] - top2[:, 1]
+    ref_toks = lg_ref.argmax(-1).tolist()[len(prefix) - 1:]
+    for j, (a, b) in enumerate(zip(toks, ref_toks)):
+        k = len(prefix) - 1 + j
+        assert a == b or float(margin[k]) <= 2 * float(err[k]), f"step {j}: {a} vs {b}, margin {float(margin[k])}"
