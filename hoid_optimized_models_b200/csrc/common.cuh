@@ -59,6 +59,23 @@ __device__ __forceinline__ void unpack8(const uint4& w, float* f) {
   f[6] = bf16lo(w.w); f[7] = bf16hi(w.w);
 }
 
+// Exact-erf GELU: erf by Abramowitz & Stegun 7.1.26 (absolute error <= 1.5e-7 plus the ~1e-7
+// of the approximate reciprocal / exp2, far below bf16 resolution): two special-function-unit
+// operations and about a dozen FMAs per element, so that it fits in a GEMM epilogue.
+__device__ __forceinline__ float gelu_erf(float v) {
+  const float z = fabsf(v) * 0.70710678118654752440f;
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.f)));
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+  const float erf_abs = 1.f - poly * t * e;
+  return 0.5f * v * (1.f + copysignf(erf_abs, v));
+}
+
 // Programmatic dependent launch: let the next kernel in the stream start its
 // independent prologue, and wait for the previous kernel's results.  Both are
 // no-ops when the launch carries no programmatic-serialization attribute.

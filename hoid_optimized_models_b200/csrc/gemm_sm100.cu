@@ -6,9 +6,14 @@
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (cta_group::1,
 //               kind::f16, M128 N256 K16) with fp32 accumulators in tensor memory;
 //               tcgen05.commit releases ring stages and publishes accumulators
-//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time, fused bias / residual /
-//               SwiGLU / GELU, bf16 stores.  Two 256-column accumulators alternate so
-//               the epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 2..9  epilogue (two warps per 32-lane slab, alternating 64-column groups): tcgen05.ld 32 columns at a time, fused bias / residual /
+//               SwiGLU / GELU.  bf16 results leave through a per-warp swizzled staging
+//               tile and a TMA store (the residual arrives the same way with a TMA
+//               load), so every global access of the epilogue is a full coalesced box
+//               instead of 32 row-strided 64-byte pieces.  Two accumulators alternate,
+//               so the epilogue of tile i overlaps the main loop of tile i+1.
+// The N extent of the tile (256 / 128 / 64) is chosen per problem so that small
+// problems (e.g. M = 1500) still give every SM a tile.
 //
 // Grouped mode (MoE experts): rows of X are sorted by expert, `offsets[e]` is the
 // first row of expert e, W is [E, N, K]; M-tiles never straddle an expert for
@@ -21,16 +26,18 @@
 
 namespace b200 {
 
-constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int kStages = 4;
-constexpr int kGemmThreads = 192;
+constexpr int BM = 128, BK = 64;
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t kABytes = BM * BK * 2;   // 16 KiB
-constexpr uint32_t kBBytes = BN * BK * 2;   // 32 KiB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr int kMaxExperts = 256;
+constexpr int kMaxExperts = 128;
+constexpr uint32_t kStageBoxBytes = 32 * 128;   // epilogue staging box: 32 rows x 64 bf16
+constexpr int kEpiWarps = 8;                    // two per TMEM lane slab, alternating column groups
+// ring depth: 192 KiB of operand stages whatever the tile width
+constexpr int gemm_stages(int bn) { return bn == 256 ? 4 : (bn == 128 ? 6 : 8); }
 
 struct GemmArgs {
   uint16_t* y; const uint16_t* bias; const uint16_t* resid; const int* offsets;
+  int tma_epilogue;   // bf16 plain / bias / GELU / residual output goes through TMA boxes
   int* status;
   int M, N, K, ldy, ldr, epilogue, n_groups, y_dtype;
 };
@@ -45,15 +52,16 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
   return d;
 }
-// bf16 x bf16 -> fp32, both operands K-major, M = BM, N = BN.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                            ((uint32_t)(BM >> 4) << 24);
+// bf16 x bf16 -> fp32, both operands K-major, M = BM, N = bn.
+constexpr uint32_t gemm_idesc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
 
 // ---------------------------------------------------------------- tile schedule
 struct Tile { int row0, row_end, n0, wrow0; bool valid; };
 
 struct Sched {
-  int mt, nt, total;
+  int mt, nt, total, bn;
   const int* cum;      // grouped: smem prefix of tiles per group [n_groups + 1]
   const int* offs;     // grouped: smem row offsets [n_groups + 1]
   int n_groups, M, N;
@@ -63,33 +71,40 @@ struct Sched {
     if (!r.valid) { r.row0 = r.row_end = r.n0 = r.wrow0 = 0; return r; }
     if (n_groups == 0) {
       const int tm = t % mt, tn = t / mt;
-      r.row0 = tm * BM; r.row_end = min(M, r.row0 + BM); r.n0 = tn * BN; r.wrow0 = r.n0;
+      r.row0 = tm * BM; r.row_end = min(M, r.row0 + BM); r.n0 = tn * bn; r.wrow0 = r.n0;
     } else {
       int lo = 0, hi = n_groups - 1;           // last group with cum[g] <= t
       while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (cum[mid] <= t) lo = mid; else hi = mid - 1; }
       const int local = t - cum[lo];
       const int tn = local % nt, tm = local / nt;
       r.row0 = offs[lo] + tm * BM; r.row_end = min(offs[lo + 1], r.row0 + BM);
-      r.n0 = tn * BN; r.wrow0 = lo * N + r.n0;
+      r.n0 = tn * bn; r.wrow0 = lo * N + r.n0;
     }
     return r;
   }
 };
 
-__device__ __forceinline__ float gelu_erf(float v) {
-  return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
-}
 
+template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+            const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_r,
             GemmArgs a) {
+  constexpr int kStages = gemm_stages(BN);
+  constexpr uint32_t kBBytes = BN * BK * 2;
+  constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // 512 / 256 / 128: powers of two
+  constexpr uint32_t kIdesc = gemm_idesc(BN);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // carve: [stages x (A|B)] 1024-aligned, then barriers and bookkeeping
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + kStages * kStageBytes);
-  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  const uint32_t s_stage = base + kStages * kStageBytes;           // 8 warps x 4 KiB staging
+  unsigned char* g_stage = gen_base + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + kStages * kStageBytes +
+                                               kEpiWarps * kStageBoxBytes);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, then 8 x resid
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_cum = reinterpret_cast<int*>(tmem_slot + 4);
   int* s_off = s_cum + (kMaxExperts + 1);
@@ -104,22 +119,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(tfull_bar(s), 1); mbar_init(tempty_bar(s), 4); }
+    for (int s = 0; s < 2; ++s) { mbar_init(tfull_bar(s), 1); mbar_init(tempty_bar(s), kEpiWarps); }
+    for (int s = 0; s < kEpiWarps; ++s) mbar_init(smem_u32(bars + 2 * kStages + 4 + s), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    if (a.tma_epilogue) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_y) : "memory");
+      if (a.resid != nullptr) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_r) : "memory");
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+                 ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
 
   pdl_wait();  // offsets / X / residual come from earlier kernels
 
   Sched sch;
-  sch.M = a.M; sch.N = a.N; sch.n_groups = a.n_groups;
+  sch.M = a.M; sch.N = a.N; sch.n_groups = a.n_groups; sch.bn = BN;
   sch.nt = (a.N + BN - 1) / BN;
   sch.cum = s_cum; sch.offs = s_off;
   if (a.n_groups > 0) {
@@ -199,17 +219,91 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   } else {
     // ------------------------------------------------------------ epilogue warps
     const int slab = warp & 3;  // TMEM lanes [32*slab, 32*slab+32) belong to this warp
-    int acc = 0; uint32_t acc_phase = 0;
+    const int half = (warp - 2) >> 2;   // the slab's two warps take alternate column groups
+    const int ew = warp - 2;            // epilogue warp index: staging box and residual barrier
+    int acc = 0; uint32_t acc_phase = 0, res_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; ok && t < sch.total; t += gridDim.x) {
       const Tile tl = sch.get(t);
+      // bias of the tile's columns, 8 per lane, fetched while the main loop is still running;
+      // the per-column value is broadcast with a shuffle later (no dependent global load and no
+      // shared memory in the per-chunk path)
+      float bias8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (a.bias != nullptr && lane * 8 < BN && tl.n0 + lane * 8 < a.N)
+        unpack8(*reinterpret_cast<const uint4*>(a.bias + tl.n0 + lane * 8), bias8);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = tl.row0 + slab * 32 + lane;
       const bool row_ok = row < tl.row_end;
       const uint32_t taddr = tmem_base + ((uint32_t)(slab * 32) << 16) + (uint32_t)(acc * BN);
+      // TMA boxes clip at the matrix edge but cannot mask rows of the NEXT expert, so a grouped
+      // tile that ends inside the matrix takes the direct path
+      const bool tma_tile = a.tma_epilogue && (tl.row_end - tl.row0 == BM || tl.row_end == a.M);
+      if (tma_tile) {
+        const uint32_t rbar = smem_u32(bars + 2 * kStages + 4 + ew);
+        const uint32_t sbox = s_stage + ew * kStageBoxBytes;
+        unsigned char* myrow = g_stage + ew * kStageBoxBytes + lane * 128;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+        for (int g = half; g < BN / 64; g += 2) {
+          const int col0 = tl.n0 + g * 64;
+          if (col0 >= a.N) break;  // warp-uniform
+          // the previous store from this warp's staging box must have finished READING it
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+          if (a.resid != nullptr) {
+            if (lane == 0) {
+              mbar_expect_tx(rbar, kStageBoxBytes);
+              tma_load_2d(sbox, &map_r, rbar, col0, tl.row0 + slab * 32);
+            }
+            if (!mbar_wait(rbar, res_phase, abort_flag)) { ok = false; break; }
+            res_phase ^= 1;
+          }
+          uint32_t r[2][32];
+          tc_ld32(taddr + g * 64, r[0]);
+          tc_ld32(taddr + g * 64 + 32, r[1]);
+          tc_wait_ld();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h][j]);
+            if (a.bias != nullptr) {
+              const int src = (g * 64 + h * 32) >> 3;   // lane holding the first of these columns
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] += __shfl_sync(0xffffffffu, bias8[j & 7], src + (j >> 3));
+            }
+            if (a.epilogue == B200_EPI_GELU) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4* slot = reinterpret_cast<uint4*>(myrow + (((h * 4 + q4) ^ (lane & 7)) << 4));
+              if (a.resid != nullptr) {
+                float r8[8];
+                unpack8(*slot, r8);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[q4 * 8 + e] += r8[e];
+              }
+              uint4 w;
+              w.x = pack_bf16(v[q4 * 8 + 0], v[q4 * 8 + 1]); w.y = pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3]);
+              w.z = pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5]); w.w = pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7]);
+              *slot = w;
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(&map_y), "r"(sbox), "r"(col0), "r"(tl.row0 + slab * 32) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        if (!ok) break;
+      } else {
+#pragma unroll 1
+      for (int c = half; c < BN / 32; c += 2) {
         const int col0 = tl.n0 + c * 32;
         if (col0 >= a.N) break;  // warp-uniform
         uint32_t r[32];
@@ -281,6 +375,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -289,23 +384,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   }
 
   // ---------------------------------------------------------------- teardown
+  if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores landed
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag && a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                  : "memory");
   }
 }
 
 // ---------------------------------------------------------------- host side
-constexpr size_t kGemmSmem = 1024 + (size_t)kStages * kStageBytes + 256 + 2 * (kMaxExperts + 1) * 4;
+template <int BN>
+static int gemm_launch_bn(const CUtensorMap& mx, const void* w, uint64_t wrows, int K, int ldw,
+                          const CUtensorMap& my, const CUtensorMap& mr, const GemmArgs& a,
+                          int max_tiles_m, cudaStream_t stream, bool pdl) {
+  constexpr int kStages = gemm_stages(BN);
+  constexpr size_t smem = 1024 + (size_t)kStages * (kABytes + BN * BK * 2) +
+                          kEpiWarps * kStageBoxBytes + 256 + 2 * (kMaxExperts + 1) * 4;
+  CUtensorMap mw;
+  int rc = make_map(&mw, w, wrows, (uint64_t)K, (uint64_t)ldw, BN, BK);
+  if (rc != B200_OK) return rc;
+  const int nt = (a.N + BN - 1) / BN;
+  long tiles = (long)max_tiles_m * nt;
+  int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
+  if (grid < 1) grid = 1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  cudaError_t e = launch(gemm_kernel<BN>, dim3(grid), dim3(kGemmThreads), smem, stream, pdl, mx, mw,
+                         my, mr, a);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
 
 static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
-                       int ldx, int ldw, int ldy, const void* bias, const void* resid, int ldr, int epilogue,
-                       const int* offsets, int n_groups, int max_tiles_m, int* status, int flags,
-                       cudaStream_t stream) {
+                       int ldx, int ldw, int ldy, const void* bias, const void* resid, int ldr,
+                       int epilogue, const int* offsets, int n_groups, int max_tiles_m, int* status,
+                       int flags, cudaStream_t stream) {
   if (!x || !w || !y) return B200_ERR_ARG;
   if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (N & 7)) return B200_ERR_SHAPE;
   if ((ldx & 7) || (ldw & 7) || (ldy & 7) || (resid && (ldr & 7))) return B200_ERR_ALIGN;
@@ -319,32 +439,32 @@ static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M
   int rc = get_encode();
   if (rc != B200_OK) return rc;
 
-  CUtensorMap mx, mw;
-  const uint64_t wrows = n_groups > 0 ? (uint64_t)n_groups * N : (uint64_t)N;
-  if ((rc = make_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, BM, BK)) != B200_OK) return rc;
-  if ((rc = make_map(&mw, w, wrows, (uint64_t)K, (uint64_t)ldw, BN, BK)) != B200_OK) return rc;
-
   GemmArgs a;
   a.y = (uint16_t*)y; a.bias = (const uint16_t*)bias; a.resid = (const uint16_t*)resid;
   a.offsets = offsets; a.status = status;
   a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.ldr = ldr; a.epilogue = epilogue; a.n_groups = n_groups;
   a.y_dtype = y_dtype;
+  a.tma_epilogue = (y_dtype == B200_BF16 && epilogue != B200_EPI_SWIGLU) ? 1 : 0;
 
-  const int nt = (N + BN - 1) / BN;
-  long tiles = (long)max_tiles_m * nt;
-  int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
-  if (grid < 1) grid = 1;
-
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kGemmSmem) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
+  CUtensorMap mx, my, mr;
+  const uint64_t wrows = n_groups > 0 ? (uint64_t)n_groups * N : (uint64_t)N;
+  if ((rc = make_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, BM, BK)) != B200_OK) return rc;
+  my = mx; mr = mx;   // placeholders when the TMA epilogue is off
+  if (a.tma_epilogue) {
+    if ((rc = make_map(&my, y, (uint64_t)M, (uint64_t)N, (uint64_t)ldy, 32, 64)) != B200_OK) return rc;
+    if (resid && (rc = make_map(&mr, resid, (uint64_t)M, (uint64_t)N, (uint64_t)ldr, 32, 64)) != B200_OK)
+      return rc;
   }
-  cudaError_t e = launch(gemm_kernel, dim3(grid), dim3(kGemmThreads), kGemmSmem, stream,
-                         (flags & B200_FLAG_PDL) != 0, mx, mw, a);
-  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+  // tile width: the widest that still gives (almost) every SM a tile
+  const long tiles256 = (long)max_tiles_m * ((N + 255) / 256);
+  const long tiles128 = (long)max_tiles_m * ((N + 127) / 128);
+  const bool pdl = (flags & B200_FLAG_PDL) != 0;
+  const int forced = g_tuning[B200_TUNE_GEMM_BN];
+  int bn = tiles256 >= 2 * kNumSMs ? 256 : (tiles128 >= kNumSMs ? 128 : 64);
+  if (forced == 256 || forced == 128 || forced == 64) bn = forced;
+  if (bn == 256) return gemm_launch_bn<256>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);
+  if (bn == 128) return gemm_launch_bn<128>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);
+  return gemm_launch_bn<64>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);
 }
 
 }  // namespace b200

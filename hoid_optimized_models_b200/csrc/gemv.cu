@@ -41,9 +41,6 @@ struct GemvArgs {
 constexpr int kMaxExpertSegs = 256;
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
-__device__ __forceinline__ float gelu_erf_f(float v) {
-  return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
-}
 
 // U    : 16-byte loads per lane per batch (two batches are in flight)
 // MINB : CTAs per SM the register budget is sized for
@@ -218,7 +215,7 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   } else {
     for (int t = tid; t < nrows; t += kGemvThreads) {
       float v = row_value(t);
-      if (a.epilogue == B200_EPI_GELU) v = gelu_erf_f(v);
+      if (a.epilogue == B200_EPI_GELU) v = gelu_erf(v);
       const int oi = r0 + t + (MODE == 1 ? (int)blockIdx.y * a.N : 0);
       if (a.resid != nullptr) {
         v += (a.resid_dtype == B200_F32)

@@ -140,7 +140,7 @@ __global__ void greedy_select_kernel(int* tok_out, const Best* cand, int n, int*
 
 using namespace b200;
 
-namespace b200 { int g_tuning[16] = {3, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; }
+namespace b200 { int g_tuning[16] = {0}; }
 
 extern "C" int b200_set_tuning(int key, int value) {
   if (key < 0 || key >= 16) return B200_ERR_ARG;

@@ -5,9 +5,9 @@ Mirrors the reference's `OptimizedBgeM3` (models/bge-m3/bge_optimized.py:282-393
 
     word / position gather -> add_layernorm (token-type row as bias)
     per layer: gemm[q|k|v packed, + bias] -> flash_prefill (bidirectional, straight from the
-               packed projection) -> gemm[out_proj + bias + residual] -> layernorm
-               -> gemm[fc1 + bias + exact-erf GELU epilogue] -> gemm[fc2 + bias + residual]
-               -> layernorm
+               packed projection) -> gemm[out_proj + bias] -> residual + layernorm
+               -> gemm[fc1 + bias + exact-erf GELU epilogue] -> gemm[fc2 + bias]
+               -> residual + layernorm
     cls_pool_l2 -> fp32 [batch, hidden]
 
 (7 launches per layer against the reference's 10; bias, residual and GELU are GEMM epilogues.)
@@ -84,11 +84,13 @@ class XlmrEncoder:
         for L in self.layers:
             ops.gemm(self.qkv, h, L["wqkv"], bias=L["bqkv"])
             ops.flash_prefill(ctx4, q, k, v, S, False, hd ** -0.5)
-            ops.gemm(x, self.ctx, L["wo"], bias=L["bo"], resid=h)
-            ops.layernorm(h, x, L["ln1"][0], L["ln1"][1], cfg.eps)
+            # the residual add rides in the (memory-bound, coalesced) LayerNorm rather than in
+            # the epilogue of these short-K GEMMs, where it could not be hidden
+            ops.gemm(x, self.ctx, L["wo"], bias=L["bo"])
+            ops.layernorm(h, x, L["ln1"][0], L["ln1"][1], cfg.eps, resid=h)
             ops.gemm(self.act, h, L["w1"], bias=L["b1"], epilogue=ops.EPI_GELU)
-            ops.gemm(x, self.act, L["w2"], bias=L["b2"], resid=h)
-            ops.layernorm(h, x, L["ln2"][0], L["ln2"][1], cfg.eps)
+            ops.gemm(x, self.act, L["w2"], bias=L["b2"])
+            ops.layernorm(h, x, L["ln2"][0], L["ln2"][1], cfg.eps, resid=h)
             if collect is not None:
                 collect.append(h.clone())
         ops.cls_pool_l2(self.pooled, h, S)

@@ -7,8 +7,8 @@ capture, `set_encoder()` to project the window's cross-attention K/V, one graph 
 Encoder dataflow (all tensor-core GEMMs with fused epilogues):
     mel^T (time-major, zero-padded) -> conv1 as a GEMM over an overlapping-row view (+ bias + GELU)
     -> conv2 (stride 2) the same way (+ bias + GELU + positional embedding as the residual)
-    -> 32 x [layernorm, gemm q|k|v + bias, flash_prefill (bidirectional), gemm out + bias + residual,
-             layernorm, gemm fc1 + bias + GELU, gemm fc2 + bias + residual] -> layernorm
+    -> 32 x [gemm q|k|v + bias, flash_prefill (bidirectional), gemm out + bias, residual + layernorm,
+             gemm fc1 + bias + GELU, gemm fc2 + bias, residual + layernorm]
 The convolutions need no im2col: a k=3 window over a time-major [T, C] buffer is three adjacent
 rows, i.e. one row of a [T_out, 3 C] matrix whose row stride is (stride * C) elements.
 
@@ -66,7 +66,7 @@ class WhisperEncoder:
         self.a1 = torch.as_strided(self.x1, (S, 3 * D), (2 * D, 1))
         self.x, self.h = bf(S, D), bf(S, D)
         self.qkv, self.ctx, self.act = bf(S, 3 * D), bf(S, D), bf(S, cfg.ffn)
-        self.out = bf(S, D)
+        self.out, self.o = bf(S, D), bf(S, D)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_forward = 2 + 7 * cfg.enc_layers + 1
 
@@ -83,17 +83,23 @@ class WhisperEncoder:
         qkv4 = self.qkv.view(1, S, 3, nh, hd)
         q, k, v = qkv4[:, :, 0], qkv4[:, :, 1].permute(0, 2, 1, 3), qkv4[:, :, 2].permute(0, 2, 1, 3)
         ctx4 = self.ctx.view(1, S, nh, hd)
-        for L in self.layers:
-            ops.layernorm(h, x, L["ln1"][0], L["ln1"][1], cfg.eps)
+        # Pre-LN blocks: every GEMM output o is folded into the residual stream by the next
+        # LayerNorm launch (x += o; h = LN(x)), which is memory-bound and coalesced, instead of by
+        # the epilogue of these short-K GEMMs.
+        o = self.o
+        ops.layernorm(h, x, self.layers[0]["ln1"][0], self.layers[0]["ln1"][1], cfg.eps)
+        for i, L in enumerate(self.layers):
             ops.gemm(self.qkv, h, L["wqkv"], bias=L["bqkv"])
             ops.flash_prefill(ctx4, q, k, v, S, False, hd ** -0.5)
-            ops.gemm(x, self.ctx, L["wo"], bias=L["bo"], resid=x)
-            ops.layernorm(h, x, L["ln2"][0], L["ln2"][1], cfg.eps)
+            ops.gemm(o, self.ctx, L["wo"], bias=L["bo"])
+            ops.add_layernorm(h, x, o, L["ln2"][0], L["ln2"][1], cfg.eps, resid=x)
             ops.gemm(self.act, h, L["wf1"], bias=L["bf1"], epilogue=ops.EPI_GELU)
-            ops.gemm(x, self.act, L["wf2"], bias=L["bf2"], resid=x)
+            ops.gemm(o, self.act, L["wf2"], bias=L["bf2"])
+            nxt = self.layers[i + 1]["ln1"] if i + 1 < len(self.layers) else self.ln_f
+            dst = h if i + 1 < len(self.layers) else self.out
+            ops.add_layernorm(dst, x, o, nxt[0], nxt[1], cfg.eps, resid=x)
             if collect is not None:
                 collect.append(x.clone())
-        ops.layernorm(self.out, x, self.ln_f[0], self.ln_f[1], cfg.eps)
         return self.out
 
     def capture(self, warmup: int = 2) -> None:

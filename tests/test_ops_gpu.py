@@ -255,6 +255,30 @@ def test_gemm_plain(dev, M, N, K):
     assert rel_err(y[rows.to(dev)], ref) < 8e-3   # one bf16 rounding of the output
 
 
+@pytest.mark.parametrize("bn", [256, 128, 64])
+def test_gemm_tile_widths(dev, bn):
+    """Every tile width, forced through the tuning knob, on shapes with M / N / K tails."""
+    from hoid_optimized_models_b200 import ops, _lib
+    g = torch.Generator(device=dev).manual_seed(bn)
+    try:
+        _lib.lib().b200_set_tuning(1, bn)
+        for (M, N, K) in [(300, 1280, 1280), (1500, 136, 72), (129, 512, 4096)]:
+            x = bf(torch.randn(M, K, generator=g, device=dev))
+            w = bf(torch.randn(N, K, generator=g, device=dev) * 0.05)
+            b = bf(torch.randn(N, generator=g, device=dev))
+            r = bf(torch.randn(M, N, generator=g, device=dev))
+            y = r.clone()
+            ops.gemm(y, x, w, bias=b, resid=y)
+            ops.check_status(dev)
+            ref = r.float() + x.float() @ w.float().T + b.float()
+            assert rel_err(y, ref) < 1e-2, (bn, M, N, K)
+            yf = torch.empty(M, N, dtype=torch.float32, device=dev)
+            ops.gemm(yf, x, w)
+            assert rel_err(yf, x.float() @ w.float().T) < 1e-4, (bn, M, N, K)
+    finally:
+        _lib.lib().b200_set_tuning(1, 0)
+
+
 def test_gemm_epilogues(dev):
     from hoid_optimized_models_b200 import ops
     g = torch.Generator(device=dev).manual_seed(5)
