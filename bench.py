@@ -256,6 +256,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--ttft-runs", type=int, default=3)
+    ap.add_argument("--tp-allreduce", default="fused", choices=["fused", "fused-flags", "nccl"],
+                    help="N>1: all-reduce fused into the GEMVs over peer memory (tagged pairs, or "
+                         "data + sequence flags), or NCCL calls")
     ap.add_argument("--workload", default="llama-3.1-8b",
                     help="llama-3.1-8b (headline) | qwen3-4b | qwen3-30b-a3b | xlm-roberta-large | whisper-large-v3")
     ap.add_argument("--skip-prefill", action="store_true",
@@ -274,7 +277,8 @@ def main():
     K = args.steps
     config = {"workload": f"{cfg.name} batch-1 greedy decode, {args.prompt}-token prompt + {K + W} steps "
                           f"(BASELINE config 2)", "prompt_tokens": args.prompt,
-              "parallelism": f"tp{world}", "cache_policy": "inputs larger than L2 "
+              "parallelism": f"tp{world}",
+              "tp_allreduce": (args.tp_allreduce if world > 1 else None), "cache_policy": "inputs larger than L2 "
               "(every step streams all weights, 15 GB / TP)"}
 
     if args.impl == "reference":
@@ -299,8 +303,8 @@ def main():
     group = None
     if world > 1:
         import torch.distributed as dist
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
+            del os.environ["NCCL_DEBUG"]           # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
 
@@ -308,11 +312,14 @@ def main():
     from hoid_optimized_models_b200.decoder import Llama31Optimized
     from hoid_optimized_models_b200.weights import make_decoder_weights
     ops.set_pdl(not args.no_pdl)
+    if args.tp_allreduce == "fused-flags":
+        ops.set_tuning(2, 1)                       # B200_TUNE_TP_PROTOCOL
 
     weights = make_decoder_weights(cfg, 1234, dev)
     max_seq = args.prompt + W + K + 8
     eng = Llama31Optimized(cfg, weights, max_seq=max_seq, device=dev, tp_rank=rank, tp_size=world,
-                           group=group, max_new_tokens=W + K + 8, free_source_weights=True)
+                           group=group, max_new_tokens=W + K + 8, free_source_weights=True,
+                           fused_allreduce=args.tp_allreduce != "nccl")
     del weights
     torch.cuda.empty_cache()
     ids = torch.randint(0, cfg.vocab, (args.prompt,), generator=torch.Generator().manual_seed(2))

@@ -33,7 +33,13 @@ SIGNATURES = {
     "b200_sm_count": (_i, []),
     "b200_set_tuning": (_i, [_i, _i]),
     "b200_gemv_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _p]),
-    "b200_add_rmsnorm": (_i, [_p, _p, _i, _p, _p, _i, _p, _i, _i, _f, _i, _p]),
+    "b200_tp_buffer_bytes": (_l, [_i, _i]),
+    "b200_tp_alloc": (_i, [_p, _p, _l]),
+    "b200_tp_open": (_i, [_p, _p]),
+    "b200_tp_create": (_i, [_p, _i, _i, _i]),
+    "b200_tp_advance": (_i, [_i, _i, _i, _p]),
+    "b200_gemv_bf16_tp": (_i, [_p, _p, _p, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p]),
+    "b200_add_rmsnorm": (_i, [_p, _p, _i, _p, _i, _p, _i, _p, _i, _i, _f, _i, _p]),
     "b200_add_layernorm": (_i, [_p, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _f, _i, _p]),
     "b200_qk_rope_cache": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
                                 _f, _i, _p]),

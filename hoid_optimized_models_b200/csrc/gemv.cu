@@ -13,12 +13,37 @@
 // launch wait, so under B200_FLAG_PDL weight streaming overlaps the tail of
 // the previous kernel in the stream.  Loads go out in bursts of U per lane
 // (4 KB contiguous per warp): bursts measured much faster than a rolling window.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace b200 {
 
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
+
+// ---------------------------------------------------------------------------------------------
+// All-reduce fused into the GEMVs of a tensor-parallel decode step (one process per GPU, peer
+// memory over NVLink, no collective library call):
+//   * a row-parallel GEMV (o_proj, down_proj) does not write y.  Its CTAs store their partial
+//     rows into slot `rank` of EVERY rank's inbox with plain peer stores; the CTA that finishes
+//     last publishes the sequence number with a system-scope release store to every rank;
+//   * the NEXT GEMV on each rank waits (bounded) until all ranks' sequence numbers have arrived,
+//     and stages x = sum over ranks of inbox[rank] in rank order while it would have staged x
+//     anyway.  Every rank adds the same values in the same order, so all ranks stay bit-identical.
+// Two inbox slots alternate by sequence parity: a rank can be at most one all-reduce ahead of
+// its slowest peer, because the next one needs that peer's contribution.
+constexpr int kTpMaxRanks = 8;
+constexpr long long kTpWaitTicks = 4000000000LL;   // ~2 s: every wait on a peer is bounded
+struct TpLink {
+  float* inbox[kTpMaxRanks];        // inbox of rank p (peer-mapped): [2 slots][world][H] fp32, or
+                                    // [2 slots][world][H] {fp32 value, u32 tag} pairs (ll)
+  unsigned* flags[kTpMaxRanks];     // flags of rank p: [2 slots][world] published sequence numbers
+  int* local_counter;               // CTA arrival counter of the publishing kernel (this rank)
+  const int* seq_base;              // device scalar: sequence number of the step's first all-reduce
+  int world, rank, H;
+  int ll;                           // 1: tagged-pair protocol, 0: data + sequence flags
+};
 
 struct GemvArgs {
   const void* x;
@@ -36,11 +61,25 @@ struct GemvArgs {
   long expert_stride;        // elements between consecutive experts' matrices
   int segs_per_expert;       // MODE 2: 256-element segments of one expert's K range
   int expert_lo, n_local;    // experts [expert_lo, expert_lo + n_local) live in w (expert parallel)
+  // tensor-parallel fusion (see the comment above tp_consume / tp_publish)
+  TpLink tp;
+  int tp_in, tp_out;         // sequence offsets of the all-reduce to consume / to feed (-1 = none)
+  float* x_out;              // consumer: CTA 0 stores the reduced vector here (nullable)
+  int* status;
 };
 
 constexpr int kMaxExpertSegs = 256;
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_v2(uint2* p, uint2 v) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
 
 // U    : 16-byte loads per lane per batch (two batches are in flight)
 // MINB : CTAs per SM the register budget is sized for
@@ -55,7 +94,7 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 //            of the virtual matrix is the concatenation of row r of every chosen
 //            expert's matrix, so the sum over the selected experts happens in the dot
 //            product itself (one pass, no partial buffers, fixed order).
-template <int U, int MINB, int MODE>
+template <int U, int MINB, int MODE, bool TP = false>
 __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long seg_off[MODE == 2 ? kMaxExpertSegs : 1];
@@ -130,9 +169,72 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   // stage x (fp32, segment-swizzled: [seg][half][lane] float4) and zero the row partials
   float ss = 0.f;
   float4* xs4 = reinterpret_cast<float4*>(xs);
+  unsigned tp_slot = 0;
+  if (TP && a.tp_in >= 0) {
+    // wait for every rank's contribution to all-reduce number seq (bounded, like every wait)
+    const unsigned seq = (unsigned)(a.tp.seq_base[0] + a.tp_in);
+    tp_slot = seq & 1u;
+    if (!a.tp.ll) {
+      if (tid < a.tp.world) {
+        const volatile unsigned* f = a.tp.flags[a.tp.rank] + tp_slot * a.tp.world + tid;
+        const long long t0 = clock64();
+        int spins = 0;
+        while (*f != seq + 1u) {
+          if ((++spins & 63) == 0) {
+            // an earlier wait already gave up: do not spend the budget again
+            if (a.status != nullptr && *reinterpret_cast<volatile int*>(a.status) != 0) break;
+            if (clock64() - t0 > kTpWaitTicks) {
+              if (a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
+              break;
+            }
+          }
+        }
+        __threadfence_system();
+      }
+      __syncthreads();
+    }
+  }
   for (int i = tid; i < (K >> 2); i += kGemvThreads) {
     float4 v;
-    if (a.x_dtype == B200_F32) {
+    if (TP && a.tp_in >= 0) {
+      if (a.tp.ll) {
+        // every 8-byte {value, tag} pair arrives atomically: poll the data itself, no flag
+        const unsigned tag = (unsigned)(a.tp.seq_base[0] + a.tp_in) + 1u;
+        const uint4* box = reinterpret_cast<const uint4*>(a.tp.inbox[a.tp.rank]) +
+                           (size_t)tp_slot * a.tp.world * (K >> 1) + 2 * i;
+        v = make_float4(0.f, 0.f, 0.f, 0.f);
+        long long t0 = 0;
+        for (int r = 0; r < a.tp.world; ++r) {
+          const uint4* q = box + (size_t)r * (K >> 1);
+          uint4 e0, e1;
+          int spins = 0;
+          while (true) {
+            e0 = ld_volatile_v4(q);
+            e1 = ld_volatile_v4(q + 1);
+            if (e0.y == tag && e0.w == tag && e1.y == tag && e1.w == tag) break;
+            if ((++spins & 63) == 0) {
+              if (a.status != nullptr && *reinterpret_cast<volatile int*>(a.status) != 0) break;
+              if (t0 == 0) t0 = clock64();
+              if (clock64() - t0 > kTpWaitTicks) {
+                if (a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
+                break;
+              }
+            }
+          }
+          v.x += __uint_as_float(e0.x); v.y += __uint_as_float(e0.z);
+          v.z += __uint_as_float(e1.x); v.w += __uint_as_float(e1.z);
+        }
+      } else {
+        const float4* box = reinterpret_cast<const float4*>(a.tp.inbox[a.tp.rank]) +
+                            (size_t)tp_slot * a.tp.world * (K >> 2) + i;
+        v = __ldcg(box);                                     // peers wrote this: bypass L1
+        for (int r = 1; r < a.tp.world; ++r) {
+          const float4 o = __ldcg(box + (size_t)r * (K >> 2));
+          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+        }
+      }
+      if (a.x_out != nullptr && blockIdx.x == 0) reinterpret_cast<float4*>(a.x_out)[i] = v;
+    } else if (a.x_dtype == B200_F32) {
       v = reinterpret_cast<const float4*>(a.x)[i];
     } else {
       uint2 u = reinterpret_cast<const uint2*>(a.x)[i];
@@ -222,13 +324,44 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
                  ? reinterpret_cast<const float*>(a.resid)[oi]
                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.resid)[oi]);
       }
-      if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = v;
+      if (TP && a.tp_out >= 0) {
+        // partial row (+ residual on the lead rank) into slot `rank` of every rank's inbox
+        const unsigned seq = (unsigned)(a.tp.seq_base[0] + a.tp_out);
+        const size_t off = ((size_t)(seq & 1u) * a.tp.world + a.tp.rank) * a.tp.H + oi;
+        if (a.tp.ll) {
+          for (int p = 0; p < a.tp.world; ++p)
+            st_volatile_v2(reinterpret_cast<uint2*>(a.tp.inbox[p]) + off,
+                           make_uint2(__float_as_uint(v), seq + 1u));
+        } else {
+          for (int p = 0; p < a.tp.world; ++p) a.tp.inbox[p][off] = v;
+        }
+      } else if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = v;
       else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(v);
+    }
+  }
+  if (TP && a.tp_out >= 0 && !a.tp.ll) {
+    // The CTA that arrives last knows every partial row of this rank has been stored.  One
+    // system fence per CTA, by the thread that signals: the barrier orders the other threads'
+    // stores before it, and the fence is cumulative.  (A fence in every warp serialises per SM
+    // on the NVLink round trip.)
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      const int old = atomicAdd(a.tp.local_counter, 1);
+      if (old == (int)gridDim.x - 1) {
+        *a.tp.local_counter = 0;
+        __threadfence_system();
+        const unsigned seq = (unsigned)(a.tp.seq_base[0] + a.tp_out);
+        for (int p = 0; p < a.tp.world; ++p) {
+          unsigned* f = a.tp.flags[p] + (seq & 1u) * a.tp.world + a.tp.rank;
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq + 1u) : "memory");
+        }
+      }
     }
   }
 }
 
-template <int U, int MINB, int MODE = 0>
+template <int U, int MINB, int MODE = 0, bool TP = false>
 static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pdl, int n_slots = 1) {
   // MINB CTAs per SM (shared between the routing slots in MODE 1); grow the grid in whole
   // waves until the per-CTA row block is small
@@ -242,11 +375,11 @@ static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pd
   const size_t smem = (size_t)a.K * 4 + (size_t)rpc * kGemvWarps * 4 + 128;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemv_kernel<U, MINB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(gemv_kernel<U, MINB, MODE, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          200 * 1024);
     attr_set = true;
   }
-  return launch(gemv_kernel<U, MINB, MODE>, dim3(grid, n_slots), dim3(kGemvThreads), smem, st, pdl, a);
+  return launch(gemv_kernel<U, MINB, MODE, TP>, dim3(grid, n_slots), dim3(kGemvThreads), smem, st, pdl, a);
 }
 
 }  // namespace b200
@@ -272,6 +405,7 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   a.eps = eps;
   a.expert_ids = nullptr; a.slot_scale = nullptr; a.expert_stride = 0; a.segs_per_expert = 0;
   a.expert_lo = 0; a.n_local = 0;
+  a.tp_in = -1; a.tp_out = -1; a.x_out = nullptr; a.status = nullptr;
   const bool sw = epilogue == B200_EPI_SWIGLU;
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;
@@ -304,6 +438,7 @@ extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, co
   a.eps = eps;
   a.expert_ids = ids; a.slot_scale = wts; a.expert_stride = (long)2 * inter * hidden;
   a.segs_per_expert = 0; a.expert_lo = expert_lo; a.n_local = n_local;
+  a.tp_in = -1; a.tp_out = -1; a.x_out = nullptr; a.status = nullptr;
   cudaError_t e = gemv_launch<8, 2, 1>(a, true, (cudaStream_t)stream,
                                        (flags & B200_FLAG_PDL) != 0, top_k);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
@@ -328,7 +463,114 @@ extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const
   a.eps = 0.f;
   a.expert_ids = ids; a.slot_scale = nullptr; a.expert_stride = (long)hidden * inter;
   a.segs_per_expert = segs; a.expert_lo = expert_lo; a.n_local = n_local;
+  a.tp_in = -1; a.tp_out = -1; a.x_out = nullptr; a.status = nullptr;
   cudaError_t e = gemv_launch<8, 2, 2>(a, false, (cudaStream_t)stream,
                                        (flags & B200_FLAG_PDL) != 0);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel link: peer-mapped inboxes set up once per process.
+namespace {
+struct TpContext { b200::TpLink link; void* local; bool used; };
+TpContext g_tp[4];
+constexpr size_t kTpAlign = 256;
+size_t tp_flag_bytes(int world) { return ((size_t)2 * world * 4 + kTpAlign - 1) & ~(kTpAlign - 1); }
+}  // namespace
+
+/* Bytes of the per-rank communication buffer: [flags | arrival counter + seq_base | inbox]. */
+extern "C" int64_t b200_tp_buffer_bytes(int world, int H) {
+  if (world <= 0 || world > kTpMaxRanks || H <= 0) return 0;
+  return (int64_t)(tp_flag_bytes(world) + kTpAlign + (size_t)2 * world * H * 8);
+}
+
+/* cudaMalloc + zero the communication buffer (set-up time only) and return its IPC handle. */
+extern "C" int b200_tp_alloc(void** ptr, void* ipc_handle_64, int64_t bytes) {
+  if (!ptr || !ipc_handle_64 || bytes <= 0) return B200_ERR_ARG;
+  void* p = nullptr;
+  if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) return B200_ERR_LAUNCH;
+  if (cudaMemset(p, 0, (size_t)bytes) != cudaSuccess) return B200_ERR_LAUNCH;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) return B200_ERR_LAUNCH;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(ipc_handle_64, &h, 64);
+  *ptr = p;
+  return cudaDeviceSynchronize() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+/* Map a peer's buffer from its IPC handle. */
+extern "C" int b200_tp_open(void** ptr, const void* ipc_handle_64) {
+  if (!ptr || !ipc_handle_64) return B200_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, ipc_handle_64, 64);
+  return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess
+             ? B200_OK : B200_ERR_LAUNCH;
+}
+
+/* Register the link: bufs[p] is rank p's buffer as mapped in THIS process (bufs[rank] = own). */
+extern "C" int b200_tp_create(void* const* bufs, int world, int rank, int H) {
+  if (!bufs || world <= 0 || world > kTpMaxRanks || rank < 0 || rank >= world || H <= 0 || (H & 3))
+    return B200_ERR_ARG;
+  int id = -1;
+  for (int i = 0; i < 4; ++i) if (!g_tp[i].used) { id = i; break; }
+  if (id < 0) return B200_ERR_ARG;
+  TpLink& l = g_tp[id].link;
+  for (int p = 0; p < world; ++p) {
+    if (!bufs[p]) return B200_ERR_ARG;
+    l.flags[p] = (unsigned*)bufs[p];
+    l.inbox[p] = (float*)((char*)bufs[p] + tp_flag_bytes(world) + kTpAlign);
+  }
+  char* own = (char*)bufs[rank] + tp_flag_bytes(world);
+  l.local_counter = (int*)own;
+  l.seq_base = (const int*)(own + 64);
+  l.world = world; l.rank = rank; l.H = H; l.ll = 1;
+  g_tp[id].local = bufs[rank];
+  g_tp[id].used = true;
+  return id;
+}
+
+__global__ void tp_advance_kernel(int* seq_base, int inc) {
+  b200::pdl_launch_dependents();
+  b200::pdl_wait();
+  if (threadIdx.x == 0) seq_base[0] += inc;
+}
+
+/* seq_base += inc (number of fused all-reduces issued since the last advance): once per step. */
+extern "C" int b200_tp_advance(int ctx, int inc, int flags, b200_stream_t stream) {
+  if (ctx < 0 || ctx >= 4 || !g_tp[ctx].used) return B200_ERR_ARG;
+  cudaError_t e = launch(tp_advance_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream,
+                         (flags & B200_FLAG_PDL) != 0, (int*)g_tp[ctx].link.seq_base, inc);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+/* b200_gemv_bf16 with the all-reduce fused in (fp32 activations, dense weights):
+ *   tp_in  >= 0 : x is ignored; x = sum over ranks of the inbox of all-reduce (seq_base + tp_in),
+ *                 K must equal the link's H; x_out (nullable) receives the reduced vector
+ *   tp_out >= 0 : y is ignored; y (+ bias + resid) is pushed to every rank as this rank's share of
+ *                 all-reduce (seq_base + tp_out); N must equal the link's H */
+extern "C" int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, int N, int ldw,
+                                 const void* norm_w, float eps, const void* bias,
+                                 const void* resid, int epilogue, int ctx, int tp_in, int tp_out,
+                                 void* x_out, int* status, int flags, b200_stream_t stream) {
+  if (ctx < 0 || ctx >= 4 || !g_tp[ctx].used) return B200_ERR_ARG;
+  if (!w || (tp_in < 0 && !x) || (tp_out < 0 && !y)) return B200_ERR_ARG;
+  if (K <= 0 || N <= 0 || (K & 255) != 0 || ldw < K || K > 32768) return B200_ERR_SHAPE;
+  if ((ldw & 7) != 0 || ((uintptr_t)w & 15) != 0) return B200_ERR_ALIGN;
+  const TpLink& l = g_tp[ctx].link;
+  if ((tp_in >= 0 && K != l.H) || (tp_out >= 0 && (N != l.H || epilogue != B200_EPI_NONE)))
+    return B200_ERR_SHAPE;
+  if (epilogue == B200_EPI_SWIGLU && ((N & 1) != 0 || resid != nullptr)) return B200_ERR_SHAPE;
+  GemvArgs a;
+  a.x = x; a.w = (const uint16_t*)w; a.y = y;
+  a.norm_w = (const uint16_t*)norm_w; a.bias = (const uint16_t*)bias; a.resid = resid;
+  a.K = K; a.N = N; a.ldw = ldw; a.rpc = 0;
+  a.x_dtype = B200_F32; a.y_dtype = B200_F32; a.resid_dtype = B200_F32; a.epilogue = epilogue;
+  a.eps = eps;
+  a.expert_ids = nullptr; a.slot_scale = nullptr; a.expert_stride = 0; a.segs_per_expert = 0;
+  a.expert_lo = 0; a.n_local = 0;
+  a.tp = l; a.tp_in = tp_in; a.tp_out = tp_out;
+  if (g_tuning[B200_TUNE_TP_PROTOCOL] == 1) a.tp.ll = 0;     // data + sequence flags a.x_out = (float*)x_out; a.status = status;
+  cudaError_t e = gemv_launch<8, 2, 0, true>(a, epilogue == B200_EPI_SWIGLU, (cudaStream_t)stream,
+                                    (flags & B200_FLAG_PDL) != 0);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }

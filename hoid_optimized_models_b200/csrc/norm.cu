@@ -38,9 +38,11 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16(v));
 }
 
+// The residual stream (a, resid_out) may be fp32 while the delta b and the normalised output
+// are bf16: an fp32 stream keeps the error against an fp32 model flat over depth.
 struct RmsArgs {
   void* resid_out; void* norm_out; const void* a; const void* b; const uint16_t* w;
-  int N, in_dtype, out_dtype; float eps;
+  int N, resid_dtype, b_dtype, out_dtype; float eps;
 };
 
 template <int kNormMaxChunks>
@@ -56,19 +58,19 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(RmsArgs p) {
   for (int c = 0; c < kNormMaxChunks; ++c) {
     const int i = threadIdx.x + c * blockDim.x;
     if (i < nchunk) {
-      load8(p.a, p.in_dtype, row0 + i, v[c]);
+      load8(p.a, p.resid_dtype, row0 + i, v[c]);
       if (p.b != nullptr) {
         float t[8];
-        load8(p.b, p.in_dtype, row0 + i, t);
+        load8(p.b, p.b_dtype, row0 + i, t);
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[c][e] += t[e];
       }
-      // the residual stream is stored in out_dtype; normalise the stored value
-      if (p.out_dtype == B200_BF16) {
+      // normalise the value the residual stream stores
+      if (p.resid_dtype == B200_BF16) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[c][e] = round_bf16(v[c][e]);
       }
-      if (p.resid_out != nullptr) store8(p.resid_out, p.out_dtype, row0 + i, v[c]);
+      if (p.resid_out != nullptr) store8(p.resid_out, p.resid_dtype, row0 + i, v[c]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss = fmaf(v[c][e], v[c][e], ss);
     }
@@ -163,14 +165,14 @@ static int norm_threads(int N) {
 using namespace b200;
 
 extern "C" int b200_add_rmsnorm(void* resid_out, void* norm_out, int out_dtype,
-                                const void* a, const void* b, int in_dtype,
+                                const void* a, int resid_dtype, const void* b, int b_dtype,
                                 const void* w, int rows, int N, float eps,
                                 int flags, b200_stream_t stream) {
   if (!norm_out || !a || !w) return B200_ERR_ARG;
   if (rows <= 0 || N <= 0 || (N & 7) != 0) return B200_ERR_SHAPE;
   const int threads = norm_threads(N);
   if ((N >> 3) > threads * kNormChunkCap) return B200_ERR_SHAPE;
-  RmsArgs p{resid_out, norm_out, a, b, (const uint16_t*)w, N, in_dtype, out_dtype, eps};
+  RmsArgs p{resid_out, norm_out, a, b, (const uint16_t*)w, N, resid_dtype, b_dtype, out_dtype, eps};
   const int cpt = ((N >> 3) + threads - 1) / threads;
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;

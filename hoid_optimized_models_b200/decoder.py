@@ -11,7 +11,9 @@ decode (6 launches per layer, fp32 activations, one CUDA graph for the whole ste
     -> gemv[down_proj, + residual];  lm_head gemv (fp32 logits) -> argmax -> greedy_select,
     which feeds the next step's token and position on the device.
 
-prefill (bf16 activations)
+prefill (bf16 activations and residual stream, the reference's own precision; an fp32 stream
+was measured to change the distance from an fp32 model by under 10% at the Llama widths, where
+the rounding of the GEMM operands dominates)
     add_rmsnorm -> gemm[q|k|v] -> qk_rope_cache -> flash_prefill (reads the cache) ->
     gemm[o_proj + residual] -> add_rmsnorm -> gemm[gate|up, SwiGLU epilogue] ->
     gemm[down + residual]; logits for the last position only.
@@ -38,7 +40,7 @@ class DenseDecoder:
     def __init__(self, cfg: DecoderConfig, weights: Dict[str, torch.Tensor], max_seq: int,
                  device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None,
                  n_splits: Optional[int] = None, max_new_tokens: int = 1024,
-                 free_source_weights: bool = False):
+                 free_source_weights: bool = False, fused_allreduce: bool = True):
         self.moe = cfg.n_experts > 0   # expert parallelism: attention replicated, experts sharded
         tpart.check_divisible(cfg, tp_size)
         self.cfg, self.device, self.max_seq = cfg, torch.device(device), max_seq
@@ -129,6 +131,11 @@ class DenseDecoder:
         self.n_splits = n_splits
         self.fd_ws = ops.flash_decode_workspace(self.n_q, self.n_kv, hd, n_splits, dev)
         self.am_ws = ops.argmax_workspace(dev)
+        # tensor-parallel decode: all-reduces fused into the GEMVs over peer memory (dense models)
+        self.link = None
+        if att_tp > 1 and fused_allreduce:
+            from .comm import PeerLink
+            self.link = PeerLink(group, tp_rank, tp_size, H)
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = 1 + (8 if self.moe else 6) * cfg.layers + 3
@@ -148,6 +155,9 @@ class DenseDecoder:
         lead = self.tp_rank == 0
         ops.embed_gather(self.h, self.embed, self.tok)
         h, h2 = self.h, self.h2
+        if self.link is not None:
+            self._step_fused_tp(collect)
+            return
         for i in range(cfg.layers):
             ops.gemv(self.qkv, h, self.wqkv[i], norm_w=self.ln1[i], eps=cfg.eps)
             ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
@@ -197,6 +207,39 @@ class DenseDecoder:
             ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand_all)
         else:
             ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
+
+    def _step_fused_tp(self, collect: Optional[list] = None) -> None:
+        """Dense tensor-parallel step with every all-reduce fused into the GEMVs around it: the
+        row-parallel GEMVs push their partial sums to all ranks, the next GEMV reduces them while
+        staging its input.  2 * layers all-reduces per step, none of them a library call."""
+        cfg, ctx, h = self.cfg, self.link.ctx, self.h
+        lead = self.tp_rank == 0
+        L = cfg.layers
+        for i in range(L):
+            if i == 0:
+                ops.gemv(self.qkv, h, self.wqkv[0], norm_w=self.ln1[0], eps=cfg.eps)
+            else:
+                ops.gemv_tp_consume(self.qkv, self.wqkv[i], ctx, 2 * i - 1, x_out=h,
+                                    norm_w=self.ln1[i], eps=cfg.eps)
+                if collect is not None:
+                    collect.append(h.clone())
+            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
+                              self.pos, self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i],
+                              kn_w=self.kn[i])
+            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
+                             self.fd_ws, self.n_q, self.n_kv, self.n_splits, self.scale)
+            ops.gemv_tp_publish(self.attn, self.wo[i], ctx, 2 * i, resid=h if lead else None)
+            ops.gemv_tp_consume(self.act, self.wgu[i], ctx, 2 * i, x_out=h, norm_w=self.ln2[i],
+                                eps=cfg.eps, epilogue=EPI_SWIGLU)
+            ops.gemv_tp_publish(self.act, self.wd[i], ctx, 2 * i + 1, resid=h if lead else None)
+        ops.gemv_tp_consume(self.logits, self.lm_head, ctx, 2 * L - 1, x_out=h,
+                            norm_w=self.final_norm_w, eps=cfg.eps)
+        if collect is not None:
+            collect.append(h.clone())
+        ops.tp_advance(ctx, 2 * L)
+        ops.argmax(self.cand, self.logits, self.am_ws, idx_base=self.tp_rank * self.vocab_local)
+        torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2), group=self.group)
+        ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand_all)
 
     def capture(self, warmup: int = 3) -> None:
         """Warm up on a side stream, then record step_static into one CUDA graph.  The step state

@@ -26,6 +26,11 @@ def set_pdl(enabled: bool) -> None:
     _PDL = bool(enabled)
 
 
+def set_tuning(key: int, value: int) -> None:
+    """Process-wide kernel tuning knob (the B200_TUNE_* keys of include/b200ops.h)."""
+    check(_lib.lib().b200_set_tuning(key, value), "b200_set_tuning")
+
+
 def _flags() -> int:
     return FLAG_PDL if _PDL else 0
 
@@ -77,18 +82,45 @@ def gemv(y: Tensor, x: Tensor, w: Tensor, norm_w: Optional[Tensor] = None, eps: 
         epilogue, _flags(), _stream()), "b200_gemv_bf16")
 
 
+# ----------------------------------------------------------------------------- fused TP GEMV
+# Plain functions (not custom ops): they write peer memory / read inboxes that torch does not
+# know about.  All tensors are fp32 activations and bf16 weights.
+def gemv_tp_publish(x: Tensor, w: Tensor, ctx: int, tp_out: int, resid: Optional[Tensor] = None,
+                    bias: Optional[Tensor] = None) -> None:
+    """This rank's share of all-reduce `tp_out`: (resid +) W x (+ bias) pushed to every rank."""
+    N, K = w.shape
+    check(_lib.lib().b200_gemv_bf16_tp(
+        _ptr(x), _ptr(w), None, K, N, w.stride(0), None, 0.0, _ptr(bias), _ptr(resid), EPI_NONE,
+        ctx, -1, tp_out, None, status_word(x.device).data_ptr(), _flags(), _stream()),
+        "b200_gemv_bf16_tp")
+
+
+def gemv_tp_consume(y: Tensor, w: Tensor, ctx: int, tp_in: int, x_out: Optional[Tensor] = None,
+                    norm_w: Optional[Tensor] = None, eps: float = 0.0,
+                    epilogue: int = EPI_NONE) -> None:
+    """y = W (rmsnorm of) x with x = the sum over ranks of all-reduce `tp_in`; x_out gets x."""
+    N, K = w.shape
+    check(_lib.lib().b200_gemv_bf16_tp(
+        None, _ptr(w), _ptr(y), K, N, w.stride(0), _ptr(norm_w), eps, None, None, epilogue,
+        ctx, tp_in, -1, _ptr(x_out), status_word(y.device).data_ptr(), _flags(), _stream()),
+        "b200_gemv_bf16_tp")
+
+
+def tp_advance(ctx: int, inc: int) -> None:
+    check(_lib.lib().b200_tp_advance(ctx, inc, _flags(), _stream()), "b200_tp_advance")
+
+
 # ----------------------------------------------------------------------------- norms
 def _rmsnorm_call(resid_out, norm_out, a, b, w, eps):
     _bf16(w, "w")
     N = w.numel()
     rows = a.numel() // N
-    if b is not None and b.dtype != a.dtype:
-        raise TypeError("a and b must share a dtype")
-    if resid_out is not None and resid_out.dtype != norm_out.dtype:
-        raise TypeError("resid_out and norm_out must share a dtype")
+    if resid_out is not None and resid_out.dtype != a.dtype:
+        raise TypeError("resid_out and a (the residual stream) must share a dtype")
     check(_lib.lib().b200_add_rmsnorm(
-        _ptr(resid_out), _ptr(norm_out), _dt(norm_out), _ptr(a), _ptr(b), _dt(a), _ptr(w),
-        rows, N, eps, _flags(), _stream()), "b200_add_rmsnorm")
+        _ptr(resid_out), _ptr(norm_out), _dt(norm_out), _ptr(a), _dt(a), _ptr(b),
+        _dt(b) if b is not None else _dt(a), _ptr(w), rows, N, eps, _flags(), _stream()),
+        "b200_add_rmsnorm")
 
 
 # Mutated arguments of a custom op are always leading, required, positional parameters.
@@ -102,7 +134,7 @@ def rmsnorm(norm_out: Tensor, a: Tensor, w: Tensor, eps: float) -> None:
 def add_rmsnorm(norm_out: Tensor, resid_out: Tensor, a: Tensor, b: Tensor, w: Tensor,
                 eps: float) -> None:
     """resid_out = a + b (rounded to its dtype); norm_out = rmsnorm(resid_out) * w.
-    resid_out may alias a."""
+    resid_out may alias a; a / resid_out may be fp32 with b and norm_out bf16."""
     _rmsnorm_call(resid_out, norm_out, a, b, w, eps)
 
 

@@ -56,7 +56,8 @@ enum {
 int b200_version(void);
 /* Kernel tuning knobs (process-wide, host side): key B200_TUNE_GEMV selects the GEMV
  * variant (loads per batch / CTAs per SM / row mapping); 0 is the measured best. */
-enum { B200_TUNE_GEMV = 0, B200_TUNE_GEMM_BN = 1 /* force the GEMM tile width: 256 / 128 / 64 */ };
+enum { B200_TUNE_GEMV = 0, B200_TUNE_GEMM_BN = 1 /* force the GEMM tile width: 256 / 128 / 64 */,
+       B200_TUNE_TP_PROTOCOL = 2 /* fused all-reduce: 0 tagged pairs, 1 data + sequence flags */ };
 int b200_set_tuning(int key, int value);
 /* Number of SMs the library sizes its grids for (148 on B200). */
 int b200_sm_count(void);
@@ -85,17 +86,44 @@ int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y, int y_dty
                    int epilogue, int flags, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------
+ * (e) Tensor-parallel decode without a collective library call: the all-reduce that follows
+ * o_proj / down_proj (no counterpart in the single-GPU reference; its call sites are
+ * models/llama31-8b/llama31_optimized.py:407,414) is fused into the GEMVs on both sides of it.
+ * Set-up (once per process, may allocate): every rank allocates b200_tp_buffer_bytes() with
+ * b200_tp_alloc, exchanges the 64-byte IPC handles, maps its peers with b200_tp_open and
+ * registers the table with b200_tp_create (returns a context id >= 0).
+ * Per step: b200_gemv_bf16_tp with tp_out >= 0 pushes this rank's partial y into every rank's
+ * inbox over NVLink, as 8-byte {value, sequence tag} pairs that arrive atomically (or, with
+ * tuning key B200_TUNE_TP_PROTOCOL = 1, as plain stores followed by one system-scope release
+ * flag per rank); with tp_in >= 0 it waits - bounded, status receives B200_ERR_TIMEOUT on
+ * expiry - for all ranks and stages x as the sum of the inboxes in rank order.  tp_in / tp_out number the all-reduces
+ * inside one step; b200_tp_advance adds the per-step count to the device-side base so that a
+ * captured graph can be replayed.  All ranks must issue the same sequence of calls.
+ */
+int64_t b200_tp_buffer_bytes(int world, int H);
+int b200_tp_alloc(void** ptr, void* ipc_handle_64, int64_t bytes);
+int b200_tp_open(void** ptr, const void* ipc_handle_64);
+int b200_tp_create(void* const* bufs, int world, int rank, int H);
+int b200_tp_advance(int ctx, int inc, int flags, b200_stream_t stream);
+int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, int N, int ldw,
+                      const void* norm_w, float eps, const void* bias, const void* resid,
+                      int epilogue, int ctx, int tp_in, int tp_out, void* x_out, int* status,
+                      int flags, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
  * a6. (residual add +) RMSNorm over rows.
- *   sum = a (+ b)                       [rows, N]
- *   resid_out <- sum (optional, rounded to its dtype first, as the reference does)
+ *   sum = a (+ b)                       [rows, N]; a and resid_out (the residual stream) have
+ *                                       resid_dtype, the delta b has b_dtype, norm_out out_dtype
+ *   resid_out <- sum (optional, rounded to resid_dtype first, as the reference does in bf16)
  *   norm_out  <- sum * rsqrt(mean(sum^2) + eps) * w
+ * An fp32 residual stream with bf16 deltas keeps the error against an fp32 model flat over depth.
  * Reference: models/qwen3-4b/kernels/fused_residual_rmsnorm_multi_k.cu:2-54,
  * models/qwen3-30b-a3b/kernels/fullcta_add_rmsnorm_k.cu:2-45,
  * models/llama31-8b/kernels/rmsnorm_prefetch16_k.cu:4-22 (b = NULL).
  * N % 8 == 0, N <= 16384.
  */
 int b200_add_rmsnorm(void* resid_out, void* norm_out, int out_dtype,
-                     const void* a, const void* b, int in_dtype,
+                     const void* a, int resid_dtype, const void* b, int b_dtype,
                      const void* w, int rows, int N, float eps,
                      int flags, b200_stream_t stream);
 

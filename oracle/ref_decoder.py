@@ -147,14 +147,23 @@ def layer_weights(weights, i: int, name: str) -> torch.Tensor:
 
 @torch.no_grad()
 def decoder_forward(cfg, weights: Dict[str, torch.Tensor], ids: torch.Tensor,
-                    logits_rows: Optional[Sequence[int]] = None, keep_hidden: bool = True):
+                    logits_rows: Optional[Sequence[int]] = None, keep_hidden: bool = True,
+                    act_dtype: Optional[torch.dtype] = None):
     """Full-sequence causal forward in fp32, one layer resident at a time.
+
+    With act_dtype=torch.bfloat16 every tensor an eager bf16 run materialises (norm output, each
+    linear output, the rotated q/k, the attention output, silu(gate), silu(gate)*up, each
+    residual sum) is rounded to bf16 while all arithmetic inside an op stays fp32 - the numerics
+    of the reference's own bf16 eager path (and of HuggingFace in torch_dtype=bfloat16).  The
+    distance of that run from the fp32 run is the error floor any bf16-operand pipeline has at
+    a given depth; the full-size parity test measures the CUDA path against it.
 
     Returns (hidden, logits, router): hidden[l] is the residual stream after l layers ([S, H];
     the last entry has the final norm applied, like HF's output_hidden_states), logits are
     the rows `logits_rows` (default: all) and router[l] the per-layer router logits (MoE)."""
     S = ids.numel()
     H, hd = cfg.hidden, cfg.head_dim
+    r = (lambda t: t) if act_dtype is None else (lambda t: t.to(act_dtype).float())
     x = weights["model.embed_tokens.weight"][ids.long()].float()
     ang = torch.arange(S, dtype=torch.float64)[:, None] * inv_freq(cfg)[None, :]
     cos, sin = ang.cos().float(), ang.sin().float()
@@ -162,17 +171,17 @@ def decoder_forward(cfg, weights: Dict[str, torch.Tensor], ids: torch.Tensor,
     router = []
     for i in range(cfg.layers):
         L = lambda n: layer_weights(weights, i, n)
-        hn = rmsnorm(x, L("input_layernorm.weight"), cfg.eps)
-        q = (hn @ L("self_attn.q_proj.weight").T).view(S, cfg.n_q, hd)
-        k = (hn @ L("self_attn.k_proj.weight").T).view(S, cfg.n_kv, hd)
-        v = (hn @ L("self_attn.v_proj.weight").T).view(S, cfg.n_kv, hd)
+        hn = r(rmsnorm(x, L("input_layernorm.weight"), cfg.eps))
+        q = r(hn @ L("self_attn.q_proj.weight").T).view(S, cfg.n_q, hd)
+        k = r(hn @ L("self_attn.k_proj.weight").T).view(S, cfg.n_kv, hd)
+        v = r(hn @ L("self_attn.v_proj.weight").T).view(S, cfg.n_kv, hd)
         if cfg.qk_norm:
-            q = rmsnorm(q, L("self_attn.q_norm.weight"), cfg.eps)
-            k = rmsnorm(k, L("self_attn.k_norm.weight"), cfg.eps)
-        q, k = rope_rotate(q, cos, sin), rope_rotate(k, cos, sin)
-        att = causal_attention(q, k, v, hd ** -0.5).reshape(S, cfg.n_q * hd)
-        x = x + att @ L("self_attn.o_proj.weight").T
-        hn = rmsnorm(x, L("post_attention_layernorm.weight"), cfg.eps)
+            q = r(rmsnorm(q, L("self_attn.q_norm.weight"), cfg.eps))
+            k = r(rmsnorm(k, L("self_attn.k_norm.weight"), cfg.eps))
+        q, k = r(rope_rotate(q, cos, sin)), r(rope_rotate(k, cos, sin))
+        att = r(causal_attention(q, k, v, hd ** -0.5).reshape(S, cfg.n_q * hd))
+        x = r(x + r(att @ L("self_attn.o_proj.weight").T))
+        hn = r(rmsnorm(x, L("post_attention_layernorm.weight"), cfg.eps))
         if cfg.n_experts:
             rl = hn @ L("mlp.gate.weight").T
             router.append(rl)
@@ -182,13 +191,15 @@ def decoder_forward(cfg, weights: Dict[str, torch.Tensor], ids: torch.Tensor,
             y = torch.zeros_like(x)
             for e in eids.unique().tolist():
                 tok, slot = (eids == e).nonzero(as_tuple=True)
-                t = hn[tok] @ gu[e].T
-                a = F.silu(t[:, :cfg.moe_inter]) * t[:, cfg.moe_inter:]
-                y.index_add_(0, tok, (a @ dn[e].T) * ew[tok, slot][:, None])
-            x = x + y
+                t = r(hn[tok] @ gu[e].T)
+                a = r(r(F.silu(t[:, :cfg.moe_inter])) * t[:, cfg.moe_inter:])
+                y.index_add_(0, tok, r(r(a @ dn[e].T) * ew[tok, slot][:, None]))
+            x = r(x + r(y))
         else:
-            a = F.silu(hn @ L("mlp.gate_proj.weight").T) * (hn @ L("mlp.up_proj.weight").T)
-            x = x + a @ L("mlp.down_proj.weight").T
+            g = r(hn @ L("mlp.gate_proj.weight").T)
+            u = r(hn @ L("mlp.up_proj.weight").T)
+            a = r(r(F.silu(g)) * u)
+            x = r(x + r(a @ L("mlp.down_proj.weight").T))
         if keep_hidden and i + 1 < cfg.layers:
             hidden.append(x.clone())
     xn = rmsnorm(x, weights["model.norm.weight"].float(), cfg.eps)

@@ -13,7 +13,12 @@ pytestmark = pytest.mark.gpu
 N_NEW = 33  # first token from prefill + 32 decode steps
 
 
-def _run(dev, cfg, P, seed):
+def _run(dev, cfg, P, seed, bf16_floor=False):
+    """bf16_floor: also run the oracle with the reference's bf16 eager numerics (every
+    materialised tensor rounded to bf16) and accept, per layer, the larger of the fixed tolerance
+    and 1.25 x that run's own distance from the fp32 oracle.  Independent operand roundings make
+    any bf16 pipeline drift from fp32 like a random walk over depth (about 1% rms per layer at
+    the Llama widths); the fixed 2e-2 alone only holds for the first few layers."""
     from hoid_optimized_models_b200.decoder import DenseDecoder
     from hoid_optimized_models_b200.weights import make_decoder_weights
     from oracle.ref_decoder import decoder_forward
@@ -48,12 +53,21 @@ def _run(dev, cfg, P, seed):
     full = torch.cat((ids, torch.tensor(toks[:-1])))
     rows = list(range(P - 1, P + N_NEW - 1))
     hidden, logits_ref, router_ref = decoder_forward(cfg, w, full, logits_rows=rows)
+    floor_hid, floor_cos, floor_logit = None, None, 0.0
+    if bf16_floor:
+        h16, l16, _ = decoder_forward(cfg, w, full, logits_rows=rows, act_dtype=torch.bfloat16)
+        floor_hid = [float((h16[l + 1][:P] - hidden[l + 1][:P]).abs().max() / hidden[l + 1][:P].abs().max())
+                     for l in range(cfg.layers - 1)]
+        floor_cos = float(torch.nn.functional.cosine_similarity(l16[1:], logits_ref[1:], dim=-1).min())
+        floor_logit = float((l16[1:] - logits_ref[1:]).abs().max())
+        del h16
     # MoE: a token whose k-th and (k+1)-th expert probabilities are closer than the bf16 noise
     # of the router input may legitimately be routed differently from the fp32 oracle; such
     # tokens (few, each with a tiny oracle margin) are left out of the hidden-state comparison
     # from that layer on.  Given identical router logits the choice is bit-exact
     # (tests/test_moe_gpu.py).
     keep = torch.ones(P, dtype=torch.bool)
+    layer_err = []
     for l in range(cfg.layers):
         if cfg.n_experts:
             from oracle.ref_decoder import moe_route
@@ -70,17 +84,31 @@ def _run(dev, cfg, P, seed):
             assert int((~keep).sum()) <= max(2, P // 8), f"too many re-routed tokens: {int((~keep).sum())}"
         ref = hidden[l + 1][:P] if l + 1 < cfg.layers else None
         if ref is not None:
-            err = float((hid[l].float().cpu() - ref)[keep].abs().max() / ref.abs().max())
-            assert err < 2e-2, f"prefill layer {l}: {err} ({int((~keep).sum())} tokens re-routed)"
+            d = (hid[l].float().cpu() - ref)[keep]
+            err = float(d.abs().max() / ref.abs().max())
+            at = int(d.abs().max(-1).values.argmax())
+            print(f"prefill layer {l}: max rel err {err:.4e} (token {at}), rms rel err "
+                  f"{float(d.pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()):.4e}, "
+                  f"{int((~keep).sum())} tokens re-routed")
+            layer_err.append(err)
+    for l, err in enumerate(layer_err):
+        tol = 2e-2 if floor_hid is None else max(2e-2, 1.25 * floor_hid[l])
+        if floor_hid is not None:
+            print(f"prefill layer {l}: {err:.4e} against bf16-eager floor {floor_hid[l]:.4e}")
+        assert err < tol, f"prefill layer {l}: {err} (tolerance {tol})"
     # decode step 0 hidden states (position P)
     for l in range(cfg.layers - 1):
         ref = hidden[l + 1][P]
         err = float((step_hidden[l].cpu() - ref).abs().max() / ref.abs().max())
-        assert err < 2e-2, f"decode layer {l}: {err}"
+        tol = 2e-2 if floor_hid is None else max(2e-2, 1.25 * floor_hid[l])
+        assert err < tol, f"decode layer {l}: {err} (tolerance {tol})"
     greedy_ref = logits_ref.argmax(-1).tolist()
     got = torch.stack(step_logits)
     cos = torch.nn.functional.cosine_similarity(got, logits_ref[1:], dim=-1)
-    assert float(cos.min()) >= 0.999, f"logit cosine {float(cos.min())}"
+    cos_tol = 0.999 if floor_cos is None else min(0.999, 1.0 - 1.5 * (1.0 - floor_cos))
+    print(f"logit cosine min {float(cos.min()):.6f} (required {cos_tol:.6f}"
+          + (f", bf16-eager floor {floor_cos:.6f})" if floor_cos is not None else ")"))
+    assert float(cos.min()) >= cos_tol, f"logit cosine {float(cos.min())}"
     # Greedy parity.  Random-init heads produce near-ties: a token may differ from the oracle's
     # only where the oracle's own top-2 margin is inside the measured logit error of that step
     # (bf16 KV cache and bf16 prefill activations against an fp32 oracle).  Teacher forcing
@@ -88,7 +116,9 @@ def _run(dev, cfg, P, seed):
     err = (got - logits_ref[1:]).abs().max(-1).values          # per decode step
     # a decode step whose token is routed to a different expert at a near-tie (MoE only, see
     # the prefill check above) shows a larger logit error; the cosine bound above still holds
-    loud = int((err >= 3e-2 * float(logits_ref.abs().max())).sum())
+    loud = int((err >= max(3e-2 * float(logits_ref.abs().max()), 1.5 * floor_logit)).sum())
+    print(f"max logit error {float(err.max()):.4f} (bf16-eager floor {floor_logit:.4f}, max |logit| "
+          f"{float(logits_ref.abs().max()):.3f})")
     assert loud <= (3 if cfg.n_experts else 0), f"logit error {float(err.max())} on {loud} steps"
     top2 = logits_ref.topk(2, -1).values
     margin = top2[:, 0] - top2[:, 1]

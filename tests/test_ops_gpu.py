@@ -95,6 +95,26 @@ def test_add_rmsnorm(dev, rows, N, dt):
     assert rel_err(out2, rmsnorm(a.float(), w.float(), 1e-6)) < tol
 
 
+@pytest.mark.parametrize("rows,N", [(5, 4096), (3, 2560), (2, 2048)])
+def test_add_rmsnorm_fp32_stream(dev, rows, N):
+    """fp32 residual stream, bf16 delta, bf16 normalised output (the prefill layout)."""
+    from hoid_optimized_models_b200 import ops
+    from oracle.ref_decoder import rmsnorm
+    g = torch.Generator().manual_seed(rows + N)
+    a = torch.randn(rows, N, generator=g)
+    b = bf(torch.randn(rows, N, generator=g))
+    w = bf(1 + 0.1 * torch.randn(N, generator=g))
+    s = a + b.float()
+    res = a.clone().to(dev)
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
+    ops.add_rmsnorm(out, res, res, b.to(dev), w.to(dev), 1e-6)     # in place on the stream
+    assert torch.equal(res.cpu(), s)
+    assert rel_err(out, rmsnorm(s, w.float(), 1e-6)) < 1e-2
+    out2 = torch.empty_like(out)
+    ops.rmsnorm(out2, res, w.to(dev), 1e-6)
+    assert torch.equal(out2, out)
+
+
 @pytest.mark.parametrize("rows,N", [(7, 1024), (3, 1280), (1, 4096)])
 def test_add_layernorm(dev, rows, N):
     from hoid_optimized_models_b200 import ops

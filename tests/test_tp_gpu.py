@@ -1,5 +1,7 @@
-"""Tensor-parallel (Llama architecture) and expert-parallel (Qwen3-MoE architecture) engines on
-2 GPUs against the single-GPU engine: same greedy tokens, logits within 1e-3 relative.
+"""Tensor-parallel (Llama architecture; all-reduce fused into the GEMVs over peer memory, and
+through NCCL) and expert-parallel (Qwen3-MoE architecture) engines on 2 GPUs against the
+single-GPU engine: same greedy tokens, logits within 1e-2 relative (the tensor-parallel prefill
+all-reduces bf16 partial projections, a rounding the single-GPU prefill does not have).
 Skipped when fewer than two GPUs are visible."""
 import os
 import socket
@@ -28,7 +30,7 @@ def _cfg(moe):
     return replace(LLAMA31_8B, name="llama-tp-test", layers=2, vocab=4096)
 
 
-def _worker(rank, size, port, moe, out):
+def _worker(rank, size, port, moe, fused, out):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch.distributed as dist
@@ -36,15 +38,20 @@ def _worker(rank, size, port, moe, out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=size, device_id=dev)
     try:
+        from hoid_optimized_models_b200 import ops
         from hoid_optimized_models_b200.decoder import DenseDecoder
         from hoid_optimized_models_b200.weights import make_decoder_weights
+        if fused == "flags":
+            ops.set_tuning(2, 1)                    # B200_TUNE_TP_PROTOCOL: data + sequence flags
         cfg = _cfg(moe)
         w = make_decoder_weights(cfg, 21)
         ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(21)).to(dev)
         eng = DenseDecoder(cfg, w, max_seq=P + N_NEW + 2, device=dev, tp_rank=rank, tp_size=size,
-                           group=dist.group.WORLD)
+                           group=dist.group.WORLD, fused_allreduce=bool(fused))
+        assert (eng.link is not None) == (bool(fused) and not moe)
         toks = eng.generate(ids, N_NEW)
-        logits = eng.logits.float().cpu()
+        ops.check_status(dev)                        # no bounded wait gave up
+        logits = eng.logits.float().cpu().tolist()   # plain data: the child exits right after
         out.put((rank, toks, logits))
         out.close()
         out.join_thread()
@@ -59,8 +66,9 @@ def _worker(rank, size, port, moe, out):
         os._exit(0)
 
 
-@pytest.mark.parametrize("moe", [False, True])
-def test_two_ranks_match_one(dev, moe):
+@pytest.mark.parametrize("moe,fused", [(False, "pairs"), (False, "flags"), (False, ""), (True, "")],
+                         ids=["dense-fused-pairs", "dense-fused-flags", "dense-nccl", "moe-nccl"])
+def test_two_ranks_match_one(dev, moe, fused):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from hoid_optimized_models_b200.decoder import DenseDecoder
@@ -74,7 +82,7 @@ def test_two_ranks_match_one(dev, moe):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, moe, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, moe, fused, out)) for r in range(2)]
     for p in procs:
         p.start()
     res = sorted([out.get(timeout=600) for _ in procs], key=lambda r: r[0])
@@ -83,6 +91,7 @@ def test_two_ranks_match_one(dev, moe):
         assert p.exitcode == 0
     for rank, toks, _ in res:
         assert toks == toks_ref, f"rank {rank}: {toks} vs {toks_ref}"
-    full = res[0][2] if moe else torch.cat([r[2] for r in res])   # dense: vocabulary-sharded logits
+    # dense: vocabulary-sharded logits
+    full = torch.tensor(res[0][2]) if moe else torch.cat([torch.tensor(r[2]) for r in res])
     err = float((full - logits_ref).abs().max() / logits_ref.abs().max())
-    assert err < 1e-3, err
+    assert err < 1e-2, err
