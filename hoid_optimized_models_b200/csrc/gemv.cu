@@ -397,7 +397,7 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_GELU) return B200_ERR_ARG;
   if (K > 32768) return B200_ERR_SHAPE;
 
-  GemvArgs a;
+  GemvArgs a{};
   a.x = x; a.w = (const uint16_t*)w; a.y = y;
   a.norm_w = (const uint16_t*)norm_w; a.bias = (const uint16_t*)bias; a.resid = resid;
   a.K = K; a.N = N; a.ldw = ldw; a.rpc = 0;
@@ -430,7 +430,7 @@ extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, co
   if (top_k <= 0 || inter <= 0 || hidden <= 0 || (hidden & 255) != 0 || hidden > 32768)
     return B200_ERR_SHAPE;
   if (((uintptr_t)w_gu & 15) != 0 || ((uintptr_t)x & 15) != 0) return B200_ERR_ALIGN;
-  GemvArgs a;
+  GemvArgs a{};
   a.x = x; a.w = (const uint16_t*)w_gu; a.y = act; a.norm_w = (const uint16_t*)norm_w;
   a.bias = nullptr; a.resid = nullptr;
   a.K = hidden; a.N = 2 * inter; a.ldw = hidden; a.rpc = 0;
@@ -445,17 +445,18 @@ extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, co
 }
 
 /* Decode-time expert MLP, second half: y[d] = (resid[d] +) sum_slot w_down[ids[slot]][d, :] . act[slot, :]. */
-extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const void* w_down,
+static int moe_down_impl(const b200::TpLink* link, int tp_out, int* status,
+                         void* y, int y_dtype, const void* act, const void* w_down,
                                     const int* ids, int top_k, int inter, int hidden,
                                     int expert_lo, int n_local,
                                     const void* resid, int resid_dtype, int flags,
                                     b200_stream_t stream) {
-  if (!y || !act || !w_down || !ids) return B200_ERR_ARG;
+  if ((!y && link == nullptr) || !act || !w_down || !ids) return B200_ERR_ARG;
   if (top_k <= 0 || inter <= 0 || hidden <= 0 || (inter & 255) != 0) return B200_ERR_SHAPE;
   const int segs = inter >> 8;
   if (top_k * segs > kMaxExpertSegs || (long)top_k * inter > 32768) return B200_ERR_SHAPE;
   if (((uintptr_t)w_down & 15) != 0 || ((uintptr_t)act & 15) != 0) return B200_ERR_ALIGN;
-  GemvArgs a;
+  GemvArgs a{};
   a.x = act; a.w = (const uint16_t*)w_down; a.y = y; a.norm_w = nullptr; a.bias = nullptr;
   a.resid = resid;
   a.K = top_k * inter; a.N = hidden; a.ldw = inter; a.rpc = 0;
@@ -464,9 +465,25 @@ extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const
   a.expert_ids = ids; a.slot_scale = nullptr; a.expert_stride = (long)hidden * inter;
   a.segs_per_expert = segs; a.expert_lo = expert_lo; a.n_local = n_local;
   a.tp_in = -1; a.tp_out = -1; a.x_out = nullptr; a.status = nullptr;
-  cudaError_t e = gemv_launch<8, 2, 2>(a, false, (cudaStream_t)stream,
-                                       (flags & B200_FLAG_PDL) != 0);
+  cudaError_t e;
+  if (link != nullptr) {
+    if (hidden != link->H) return B200_ERR_SHAPE;
+    a.tp = *link; a.tp_out = tp_out; a.status = status;
+    if (g_tuning[B200_TUNE_TP_PROTOCOL] == 1) a.tp.ll = 0;
+    e = gemv_launch<8, 2, 2, true>(a, false, (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0);
+  } else {
+    e = gemv_launch<8, 2, 2>(a, false, (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0);
+  }
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const void* w_down,
+                                    const int* ids, int top_k, int inter, int hidden,
+                                    int expert_lo, int n_local,
+                                    const void* resid, int resid_dtype, int flags,
+                                    b200_stream_t stream) {
+  return moe_down_impl(nullptr, -1, nullptr, y, y_dtype, act, w_down, ids, top_k, inter, hidden,
+                       expert_lo, n_local, resid, resid_dtype, flags, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -560,7 +577,7 @@ extern "C" int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, i
   if ((tp_in >= 0 && K != l.H) || (tp_out >= 0 && (N != l.H || epilogue != B200_EPI_NONE)))
     return B200_ERR_SHAPE;
   if (epilogue == B200_EPI_SWIGLU && ((N & 1) != 0 || resid != nullptr)) return B200_ERR_SHAPE;
-  GemvArgs a;
+  GemvArgs a{};
   a.x = x; a.w = (const uint16_t*)w; a.y = y;
   a.norm_w = (const uint16_t*)norm_w; a.bias = (const uint16_t*)bias; a.resid = resid;
   a.K = K; a.N = N; a.ldw = ldw; a.rpc = 0;
@@ -569,8 +586,21 @@ extern "C" int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, i
   a.expert_ids = nullptr; a.slot_scale = nullptr; a.expert_stride = 0; a.segs_per_expert = 0;
   a.expert_lo = 0; a.n_local = 0;
   a.tp = l; a.tp_in = tp_in; a.tp_out = tp_out;
-  if (g_tuning[B200_TUNE_TP_PROTOCOL] == 1) a.tp.ll = 0;     // data + sequence flags a.x_out = (float*)x_out; a.status = status;
+  a.x_out = (float*)x_out; a.status = status;
+  if (g_tuning[B200_TUNE_TP_PROTOCOL] == 1) a.tp.ll = 0;     // data + sequence flags
   cudaError_t e = gemv_launch<8, 2, 0, true>(a, epilogue == B200_EPI_SWIGLU, (cudaStream_t)stream,
                                     (flags & B200_FLAG_PDL) != 0);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+/* b200_moe_decode_down under expert parallelism with the all-reduce fused in: this rank's experts'
+ * share of the layer output (+ fp32 resid on one rank) is pushed to every rank as all-reduce
+ * (seq_base + tp_out); the next b200_gemv_bf16_tp with the same tp_in reduces it. */
+extern "C" int b200_moe_decode_down_tp(const void* act, const void* w_down, const int* ids,
+                                       int top_k, int inter, int hidden, int expert_lo,
+                                       int n_local, const void* resid, int ctx, int tp_out,
+                                       int* status, int flags, b200_stream_t stream) {
+  if (ctx < 0 || ctx >= 4 || !g_tp[ctx].used || tp_out < 0) return B200_ERR_ARG;
+  return moe_down_impl(&g_tp[ctx].link, tp_out, status, nullptr, B200_F32, act, w_down, ids, top_k,
+                       inter, hidden, expert_lo, n_local, resid, B200_F32, flags, stream);
 }

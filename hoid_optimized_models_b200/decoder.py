@@ -131,9 +131,9 @@ class DenseDecoder:
         self.n_splits = n_splits
         self.fd_ws = ops.flash_decode_workspace(self.n_q, self.n_kv, hd, n_splits, dev)
         self.am_ws = ops.argmax_workspace(dev)
-        # tensor-parallel decode: all-reduces fused into the GEMVs over peer memory (dense models)
+        # multi-GPU decode: all-reduces fused into the GEMVs over peer memory
         self.link = None
-        if att_tp > 1 and fused_allreduce:
+        if tp_size > 1 and fused_allreduce:
             from .comm import PeerLink
             self.link = PeerLink(group, tp_rank, tp_size, H)
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
@@ -156,7 +156,10 @@ class DenseDecoder:
         ops.embed_gather(self.h, self.embed, self.tok)
         h, h2 = self.h, self.h2
         if self.link is not None:
-            self._step_fused_tp(collect)
+            if self.moe:
+                self._step_fused_ep(collect)
+            else:
+                self._step_fused_tp(collect)
             return
         for i in range(cfg.layers):
             ops.gemv(self.qkv, h, self.wqkv[i], norm_w=self.ln1[i], eps=cfg.eps)
@@ -240,6 +243,41 @@ class DenseDecoder:
         ops.argmax(self.cand, self.logits, self.am_ws, idx_base=self.tp_rank * self.vocab_local)
         torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2), group=self.group)
         ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand_all)
+
+    def _step_fused_ep(self, collect: Optional[list] = None) -> None:
+        """Expert-parallel step (attention replicated, experts sharded): the one all-reduce per
+        layer, after the routed experts, is pushed by the down projection and reduced by the next
+        layer's q|k|v GEMV (the lm_head GEMV after the last layer)."""
+        cfg, ctx, h = self.cfg, self.link.ctx, self.h
+        lead = self.tp_rank == 0
+        L = cfg.layers
+        for i in range(L):
+            if i == 0:
+                ops.gemv(self.qkv, h, self.wqkv[0], norm_w=self.ln1[0], eps=cfg.eps)
+            else:
+                ops.gemv_tp_consume(self.qkv, self.wqkv[i], ctx, i - 1, x_out=h,
+                                    norm_w=self.ln1[i], eps=cfg.eps)
+                if collect is not None:
+                    collect.append(h.clone())
+            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
+                              self.pos, self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i],
+                              kn_w=self.kn[i])
+            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
+                             self.fd_ws, self.n_q, self.n_kv, self.n_splits, self.scale)
+            ops.gemv(h, self.attn, self.wo[i], resid=h)
+            ops.gemv(self.router_logits, h, self.w_router[i], norm_w=self.ln2[i], eps=cfg.eps)
+            ops.moe_router(self.topk_ids, self.topk_w, self.router_logits.view(1, -1))
+            ops.moe_decode_gate_up(self.act, h, self.wgu[i], self.topk_ids, self.topk_w,
+                                   norm_w=self.ln2[i], eps=cfg.eps, expert_lo=self.expert_lo)
+            ops.moe_decode_down_tp_publish(self.act, self.wd[i], self.topk_ids, ctx, i,
+                                           resid=h if lead else None, expert_lo=self.expert_lo)
+        ops.gemv_tp_consume(self.logits, self.lm_head, ctx, L - 1, x_out=h,
+                            norm_w=self.final_norm_w, eps=cfg.eps)
+        if collect is not None:
+            collect.append(h.clone())
+        ops.tp_advance(ctx, L)
+        ops.argmax(self.cand, self.logits, self.am_ws, idx_base=0)
+        ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
 
     def capture(self, warmup: int = 3) -> None:
         """Warm up on a side stream, then record step_static into one CUDA graph.  The step state

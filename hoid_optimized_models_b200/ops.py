@@ -106,6 +106,17 @@ def gemv_tp_consume(y: Tensor, w: Tensor, ctx: int, tp_in: int, x_out: Optional[
         "b200_gemv_bf16_tp")
 
 
+def moe_decode_down_tp_publish(act: Tensor, w_down: Tensor, ids: Tensor, ctx: int, tp_out: int,
+                               resid: Optional[Tensor] = None, expert_lo: int = 0) -> None:
+    """This rank's experts' share of the layer output (+ resid) as all-reduce `tp_out`."""
+    _bf16(w_down, "w_down")
+    E, H, I = w_down.shape
+    check(_lib.lib().b200_moe_decode_down_tp(
+        _ptr(act), _ptr(w_down), _ptr(ids), ids.numel(), I, H, expert_lo, E, _ptr(resid), ctx,
+        tp_out, status_word(act.device).data_ptr(), _flags(), _stream()),
+        "b200_moe_decode_down_tp")
+
+
 def tp_advance(ctx: int, inc: int) -> None:
     check(_lib.lib().b200_tp_advance(ctx, inc, _flags(), _stream()), "b200_tp_advance")
 

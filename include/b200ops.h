@@ -109,6 +109,13 @@ int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, int N, int l
                       const void* norm_w, float eps, const void* bias, const void* resid,
                       int epilogue, int ctx, int tp_in, int tp_out, void* x_out, int* status,
                       int flags, b200_stream_t stream);
+/* Expert parallelism: b200_moe_decode_down whose output (this rank's experts' share, + fp32 resid
+ * on one rank) is pushed as all-reduce tp_out instead of being stored (the all-reduce after the
+ * routed experts has no counterpart in the single-GPU reference; its call site is
+ * models/qwen3-30b-a3b/qwen3_moe_optimized.py, the down projection of the expert MLP). */
+int b200_moe_decode_down_tp(const void* act, const void* w_down, const int* ids, int top_k,
+                            int inter, int hidden, int expert_lo, int n_local, const void* resid,
+                            int ctx, int tp_out, int* status, int flags, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * a6. (residual add +) RMSNorm over rows.
