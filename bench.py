@@ -164,48 +164,83 @@ def _time_graph(graph, steps, warmup):
 
 
 def run_secondary(args):
-    """The other benchmark configurations (single GPU): same protocol, one JSON line each.
-    Published reference numbers (one B200, real checkpoints) are quoted for context."""
+    """The other benchmark configurations: same protocol, one JSON line each.  The two decoders
+    also run multi-rank (Qwen3-4B head-sharded, Qwen3-30B-A3B expert-parallel); the encoder and
+    Whisper lines are single GPU.  Published reference numbers (one B200, real checkpoints) are
+    quoted for context."""
     from hoid_optimized_models_b200 import ops
     from hoid_optimized_models_b200 import configs as C
     from hoid_optimized_models_b200 import weights as Wt
-    dev = torch.device("cuda", 0)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     ops.set_pdl(not args.no_pdl)
+    if args.tp_allreduce == "fused-flags":
+        ops.set_tuning(2, 1)                       # B200_TUNE_TP_PROTOCOL
     peak, peak_kind = measured_peaks()
     K, W = args.steps, max(args.warmup, 3)
     name = args.workload
-    line = {"workload": name, "n_gpus": 1, "steps": K, "warmup": W, "dtype": "bf16", "data": "synthetic"}
+    group = None
+    if world > 1:
+        if name not in ("qwen3-4b", "qwen3-30b-a3b"):
+            raise SystemExit(f"{name} runs on one GPU")
+        import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
+            del os.environ["NCCL_DEBUG"]
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+
+    def over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+    def sync():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    line = {"workload": name, "n_gpus": world, "steps": K, "warmup": W, "dtype": "bf16", "data": "synthetic"}
     if name in ("qwen3-4b", "qwen3-30b-a3b"):
         from hoid_optimized_models_b200.decoder import DenseDecoder
         cfg = C.QWEN3_4B if name == "qwen3-4b" else C.QWEN3_30B_A3B
         P = args.prompt if args.prompt != PROMPT else 1024
         w = Wt.make_decoder_weights(cfg, 1234, dev)
         eng = DenseDecoder(cfg, w, max_seq=P + W + K + 8, device=dev, max_new_tokens=W + K + 8,
-                           free_source_weights=True)
+                           free_source_weights=True, tp_rank=rank, tp_size=world, group=group,
+                           fused_allreduce=args.tp_allreduce != "nccl")
         del w
         torch.cuda.empty_cache()
         ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(1)).to(dev)
         first = eng.prefill(ids)
         ttft = []
         for _ in range(args.ttft_runs):
-            torch.cuda.synchronize()
+            sync()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); first = eng.prefill(ids); e1.record(); torch.cuda.synchronize()
-            ttft.append(e0.elapsed_time(e1))
+            e0.record(); first = eng.prefill(ids); e1.record(); sync()
+            ttft.append(over_ranks(e0.elapsed_time(e1)))
         ops.check_status(dev)
         eng.capture()
         eng.set_step(first, P, 0)
-        ms = _time_graph(eng.graph, K, W)
+        sync()
+        ms = over_ranks(_time_graph(eng.graph, K, W))
+        sync()
+        ops.check_status(dev)
+        line["parallelism"] = ("ep" if cfg.n_experts else "tp") + str(world)
+        line["tp_allreduce"] = args.tp_allreduce if world > 1 else None
         nbytes = cfg.decode_bytes_per_token(P + W + K // 2)
         ref = {"qwen3-4b": {"decode_tok_per_s": 269.8, "ttft_ms": 9.58},
                "qwen3-30b-a3b": {"decode_tok_per_s": 241.1, "ttft_ms": 28.66}}[name]
         line.update({"metric": "decode_tok_per_s", "value": 1e3 / ms, "unit": "tok/s", "ms_per_step": ms,
                      "ttft_ms": statistics.median(ttft), "prompt_tokens": P,
                      "gpu_launches": eng.launches_per_step * K,
-                     "step_roofline": {"bytes_per_step": nbytes, "achieved_gbs": nbytes / ms / 1e6,
-                                       "frac_of_peak": nbytes / ms / 1e6 / peak, "peak_kind": peak_kind},
                      "published_reference": ref})
+        if world == 1:                # per-rank bytes are not a plain 1/N share under EP
+            line["step_roofline"] = {"bytes_per_step": nbytes, "achieved_gbs": nbytes / ms / 1e6,
+                                     "frac_of_peak": nbytes / ms / 1e6 / peak, "peak_kind": peak_kind}
     elif name == "xlm-roberta-large":
         from hoid_optimized_models_b200.encoder import XlmrEncoder
         cfg, B, S = C.XLMR_LARGE, 64, 512
@@ -241,7 +276,17 @@ def run_secondary(args):
                                              "encoder_forward_ms": 3.525}})
     else:
         raise SystemExit(f"unknown workload {name}")
-    print(json.dumps(line))
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        # graphs hold communicator kernels: drop them, meet, and leave without the teardown
+        eng.graph = None
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # ------------------------------------------------------------------------------ main

@@ -45,6 +45,8 @@ SIGNATURES = {
     "b200_qk_rope_cache": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
                                 _f, _i, _p]),
     "b200_flash_decode_workspace_bytes": (_l, [_i, _i, _i, _i]),
+    "b200_rope_flash_decode": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _f, _p, _p, _i, _i, _i, _l, _l,
+                                    _i, _i, _f, _i, _p]),
     "b200_flash_decode": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _l, _l, _i, _f, _i, _p]),
     "b200_flash_decode_static_max_bytes": (_l, []),
     "b200_flash_decode_static": (_i, [_p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _l, _l, _i, _f, _i, _p]),

@@ -25,12 +25,17 @@ struct FdArgs {
   int n_q, n_kv, n_splits, out_dtype, q_dtype;
   long head_stride, row_stride;  // elements
   float scale_log2;
+  // ROPE variant: q / k / v of the new position come straight from the packed fp32 projection
+  // row; the kernel applies (QK-RMSNorm +) RoPE itself and appends the row to the cache
+  const float* qkv; const float* cos_t; const float* sin_t;
+  const uint16_t* qn_w; const uint16_t* kn_w;
+  float eps; int max_seq;
 };
 
 // threads per CTA: the register file holds 512 threads at 128 registers (G <= 4)
 constexpr int fd_threads(int G) { return G <= 4 ? 512 : 256; }
 
-template <int HD, int G>
+template <int HD, int G, bool ROPE = false>
 __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
   constexpr int THREADS = fd_threads(G);
   constexpr int WARPS = THREADS / 32;
@@ -42,6 +47,7 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
   float* sw = srec + WARPS * REC;      // [max(WARPS, n_splits)][G] merge weights
   __shared__ float s_M[G], s_den[G];
   __shared__ int s_last;
+  __shared__ uint4 s_newk[ROPE ? HD / 8 : 1], s_newv[ROPE ? HD / 8 : 1];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane / LPK, dl = lane % LPK;
@@ -57,19 +63,90 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
 
   // q for the group's heads, pre-multiplied by scale * log2(e)
   float q[G][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const size_t qi = ((size_t)(kvh * G + g) * HD) + dl * 8;
-    if (a.q_dtype == B200_F32) {
-      const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.q) + qi);
-      float4 x = p[0], y = p[1];
-      q[g][0] = x.x; q[g][1] = x.y; q[g][2] = x.z; q[g][3] = x.w;
-      q[g][4] = y.x; q[g][5] = y.y; q[g][6] = y.z; q[g][7] = y.w;
-    } else {
-      unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.q) + qi), q[g]);
+  int pos_own = -1;                    // ROPE: the new position if this CTA's slice holds it
+  if (ROPE) {
+    // rotate-half RoPE on a head spread over LPK lanes: lane dl holds dims [8 dl, 8 dl + 8), its
+    // partner dl ^ (LPK / 2) the matching dims of the other half
+    constexpr int HL = LPK / 2;
+    const bool hi = dl >= HL;
+    const int pos = kv_len - 1;
+    const bool in_cache = pos >= 0 && pos < a.max_seq;
+    const size_t ci = (size_t)(in_cache ? pos : 0) * (HD / 2) + (size_t)(dl - (hi ? HL : 0)) * 8;
+    float cs[8], sn[8];
+    {
+      const float4* c4 = reinterpret_cast<const float4*>(a.cos_t + ci);
+      const float4* s4 = reinterpret_cast<const float4*>(a.sin_t + ci);
+      const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w;
+      cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w;
+      sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
     }
+    auto rope_head = [&](const float* src, const uint16_t* nw, float* o) {
+      const float4* p = reinterpret_cast<const float4*>(src + dl * 8);
+      const float4 x0 = p[0], x1 = p[1];
+      float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+      if (nw != nullptr) {
+        float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) q[g][e] *= a.scale_log2;
+        for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+#pragma unroll
+        for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+        const float inv = rsqrtf(ss / (float)HD + a.eps);
+        float w[8];
+        unpack8(*reinterpret_cast<const uint4*>(nw + dl * 8), w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * w[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[e], HL);
+        o[e] = hi ? (x[e] * cs[e] + other * sn[e]) : (x[e] * cs[e] - other * sn[e]);
+      }
+    };
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      rope_head(a.qkv + (size_t)(kvh * G + g) * HD, a.qn_w, q[g]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[g][e] *= a.scale_log2;
+    }
+    if (in_cache && pos >= k0 && pos < k1) {     // CTA-uniform: this slice ends with the new row
+      float kf[8];
+      rope_head(a.qkv + (size_t)(a.n_q + kvh) * HD, a.kn_w, kf);
+      const float4* vp = reinterpret_cast<const float4*>(
+          a.qkv + (size_t)(a.n_q + a.n_kv + kvh) * HD + dl * 8);
+      const float4 v0 = vp[0], v1 = vp[1];
+      uint4 kp, vq;
+      kp.x = pack_bf16(kf[0], kf[1]); kp.y = pack_bf16(kf[2], kf[3]);
+      kp.z = pack_bf16(kf[4], kf[5]); kp.w = pack_bf16(kf[6], kf[7]);
+      vq.x = pack_bf16(v0.x, v0.y); vq.y = pack_bf16(v0.z, v0.w);
+      vq.z = pack_bf16(v1.x, v1.y); vq.w = pack_bf16(v1.z, v1.w);
+      if (warp == 0 && sub == 0) {
+        // the row is handed to the loop through shared memory: the streaming loads below are
+        // non-coherent and must not read what this launch writes
+        s_newk[dl] = kp; s_newv[dl] = vq;
+        const size_t row = (size_t)kvh * a.head_stride + (size_t)pos * a.row_stride + dl * 8;
+        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(a.k) + row) = kp;
+        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(a.v) + row) = vq;
+      }
+      pos_own = pos;
+      __syncthreads();
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const size_t qi = ((size_t)(kvh * G + g) * HD) + dl * 8;
+      if (a.q_dtype == B200_F32) {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.q) + qi);
+        float4 x = p[0], y = p[1];
+        q[g][0] = x.x; q[g][1] = x.y; q[g][2] = x.z; q[g][3] = x.w;
+        q[g][4] = y.x; q[g][5] = y.y; q[g][6] = y.z; q[g][7] = y.w;
+      } else {
+        unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.q) + qi), q[g]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[g][e] *= a.scale_log2;
+    }
   }
 
   float m[G], l[G], acc[G][8];
@@ -94,7 +171,10 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
       const int key = base + u * WARPS * KPW + sub;
       kd[u] = make_uint4(0, 0, 0, 0);
       vd[u] = make_uint4(0, 0, 0, 0);
-      if (key < k1) {
+      if (ROPE && key == pos_own) {
+        kd[u] = s_newk[dl];
+        vd[u] = s_newv[dl];
+      } else if (key < k1) {
         kd[u] = ldg_stream(kb + (size_t)key * a.row_stride);
         vd[u] = ldg_stream(vb + (size_t)key * a.row_stride);
       }
@@ -263,17 +343,17 @@ static size_t fd_smem_bytes(int n_splits) {
   return (size_t)(WARPS * (G * HD + ((2 * G + 3) & ~3)) + wrows * G) * 4;
 }
 
-template <int HD, int G>
+template <int HD, int G, bool ROPE = false>
 static cudaError_t fd_launch(const FdArgs& a, cudaStream_t st, bool pdl) {
   const size_t smem = fd_smem_bytes<HD, G>(a.n_splits);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(flash_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         160 * 1024);
+    cudaFuncSetAttribute(flash_decode_kernel<HD, G, ROPE>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     attr_set = true;
   }
-  return launch(flash_decode_kernel<HD, G>, dim3(a.n_splits, a.n_kv), dim3(fd_threads(G)), smem, st,
-                pdl, a);
+  return launch(flash_decode_kernel<HD, G, ROPE>, dim3(a.n_splits, a.n_kv), dim3(fd_threads(G)),
+                smem, st, pdl, a);
 }
 
 static size_t fd_counter_bytes(int n_kv) { return ((size_t)n_kv * 4 + 255) & ~(size_t)255; }
@@ -300,7 +380,7 @@ extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_
   if ((kv_row_stride & 7) != 0 || (kv_head_stride & 7) != 0 || ((uintptr_t)kcache & 15) != 0 ||
       ((uintptr_t)vcache & 15) != 0 || ((uintptr_t)q & 15) != 0 || ((uintptr_t)workspace & 15) != 0)
     return B200_ERR_ALIGN;
-  FdArgs a;
+  FdArgs a{};
   a.out = out; a.q = q; a.k = (const uint16_t*)kcache; a.v = (const uint16_t*)vcache;
   a.kv_len = kv_len_dev;
   a.counters = (int*)workspace;
@@ -313,6 +393,49 @@ extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
 #define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) e = fd_launch<HD_, G_>(a, st, pdl); else
+  FD_CASE(128, 1) FD_CASE(128, 2) FD_CASE(128, 4) FD_CASE(128, 8)
+  FD_CASE(64, 1) FD_CASE(64, 2) FD_CASE(64, 4) FD_CASE(64, 8)
+  return B200_ERR_SHAPE;
+#undef FD_CASE
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+/* b200_qk_rope_cache + b200_flash_decode in one launch for the decode step: q, k and v of the
+ * new position (row kv_len - 1) are read from the packed fp32 projection row, (QK-RMSNorm +) RoPE
+ * is applied in the attention kernel's prologue, the new k / v row is appended to the cache by the
+ * CTA whose slice ends with it, and attention runs over rows [0, kv_len). */
+extern "C" int b200_rope_flash_decode(void* out, int out_dtype, const float* qkv, void* kcache,
+                                      void* vcache, const float* cos_t, const float* sin_t,
+                                      const void* qn_w, const void* kn_w, float eps,
+                                      const int* kv_len_dev, void* workspace, int n_q, int n_kv,
+                                      int hd, int64_t kv_head_stride, int64_t kv_row_stride,
+                                      int max_seq, int n_splits, float scale, int flags,
+                                      b200_stream_t stream) {
+  if (!out || !qkv || !kcache || !vcache || !cos_t || !sin_t || !kv_len_dev || !workspace)
+    return B200_ERR_ARG;
+  if ((qn_w == nullptr) != (kn_w == nullptr)) return B200_ERR_ARG;
+  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_splits <= 0 || n_splits > 1024 || max_seq <= 0)
+    return B200_ERR_SHAPE;
+  if ((kv_row_stride & 7) != 0 || (kv_head_stride & 7) != 0 || ((uintptr_t)kcache & 15) != 0 ||
+      ((uintptr_t)vcache & 15) != 0 || ((uintptr_t)qkv & 15) != 0 ||
+      ((uintptr_t)workspace & 15) != 0 || ((uintptr_t)cos_t & 15) != 0 ||
+      ((uintptr_t)sin_t & 15) != 0)
+    return B200_ERR_ALIGN;
+  FdArgs a{};
+  a.out = out; a.q = nullptr; a.k = (const uint16_t*)kcache; a.v = (const uint16_t*)vcache;
+  a.kv_len = kv_len_dev;
+  a.counters = (int*)workspace;
+  a.recs = (float*)((char*)workspace + fd_counter_bytes(n_kv));
+  a.n_q = n_q; a.n_kv = n_kv; a.n_splits = n_splits; a.out_dtype = out_dtype; a.q_dtype = B200_F32;
+  a.head_stride = kv_head_stride; a.row_stride = kv_row_stride;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.qkv = qkv; a.cos_t = cos_t; a.sin_t = sin_t;
+  a.qn_w = (const uint16_t*)qn_w; a.kn_w = (const uint16_t*)kn_w; a.eps = eps; a.max_seq = max_seq;
+  const int G = n_q / n_kv;
+  const bool pdl = (flags & B200_FLAG_PDL) != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) e = fd_launch<HD_, G_, true>(a, st, pdl); else
   FD_CASE(128, 1) FD_CASE(128, 2) FD_CASE(128, 4) FD_CASE(128, 8)
   FD_CASE(64, 1) FD_CASE(64, 2) FD_CASE(64, 4) FD_CASE(64, 8)
   return B200_ERR_SHAPE;

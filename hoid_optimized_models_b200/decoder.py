@@ -5,8 +5,9 @@ Mirrors the reference engines' interface — `capture()`, `step(tok, pos)`,
 (models/llama31-8b/llama31_optimized.py:317-520, models/qwen3-4b/qwen3_optimized.py:312-517)
 — but with a different dataflow:
 
-decode (6 launches per layer, fp32 activations, one CUDA graph for the whole step)
-    gemv[rmsnorm prologue, packed q|k|v] -> qk_rope_cache -> flash_decode (LSE combine fused)
+decode (5 launches per layer, fp32 activations, one CUDA graph for the whole step)
+    gemv[rmsnorm prologue, packed q|k|v] -> rope_flash_decode (QK-norm + RoPE + cache append in
+    the attention prologue, LSE combine fused)
     -> gemv[o_proj, + residual] -> gemv[rmsnorm prologue, gate|up interleaved, SwiGLU epilogue]
     -> gemv[down_proj, + residual];  lm_head gemv (fp32 logits) -> argmax -> greedy_select,
     which feeds the next step's token and position on the device.
@@ -40,7 +41,8 @@ class DenseDecoder:
     def __init__(self, cfg: DecoderConfig, weights: Dict[str, torch.Tensor], max_seq: int,
                  device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None,
                  n_splits: Optional[int] = None, max_new_tokens: int = 1024,
-                 free_source_weights: bool = False, fused_allreduce: bool = True):
+                 free_source_weights: bool = False, fused_allreduce: bool = True,
+                 fuse_rope: bool = True):
         self.moe = cfg.n_experts > 0   # expert parallelism: attention replicated, experts sharded
         tpart.check_divisible(cfg, tp_size)
         self.cfg, self.device, self.max_seq = cfg, torch.device(device), max_seq
@@ -138,7 +140,8 @@ class DenseDecoder:
             self.link = PeerLink(group, tp_rank, tp_size, H)
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.launches_per_step = 1 + (8 if self.moe else 6) * cfg.layers + 3
+        self.fuse_rope = fuse_rope
+        self.launches_per_step = 1 + ((8 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
 
     # ------------------------------------------------------------------ collectives
     def _all_reduce(self, t: torch.Tensor) -> None:
@@ -146,6 +149,22 @@ class DenseDecoder:
             torch.distributed.all_reduce(t, group=self.group)
 
     # ------------------------------------------------------------------ decode
+    def _attend(self, i: int) -> None:
+        """Layer i's attention for the new position: RoPE, cache append and split-KV attention
+        (one launch; two with fuse_rope=False)."""
+        cfg = self.cfg
+        if self.fuse_rope:
+            ops.rope_flash_decode(self.attn, self.kv[i, 0], self.kv[i, 1], self.fd_ws, self.qkv,
+                                  self.cos, self.sin, self.kv_len, self.n_q, self.n_kv,
+                                  self.n_splits, self.scale, eps=cfg.eps, qn_w=self.qn[i],
+                                  kn_w=self.kn[i])
+            return
+        ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
+                          self.pos, self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i],
+                          kn_w=self.kn[i])
+        ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
+                         self.fd_ws, self.n_q, self.n_kv, self.n_splits, self.scale)
+
     def step_static(self, collect: Optional[list] = None) -> None:
         """One decode step for the token in self.tok at position self.pos (device state).
         `collect` (eager only) receives a copy of the residual stream after every layer."""
@@ -163,11 +182,7 @@ class DenseDecoder:
             return
         for i in range(cfg.layers):
             ops.gemv(self.qkv, h, self.wqkv[i], norm_w=self.ln1[i], eps=cfg.eps)
-            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
-                              self.pos, self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i],
-                              kn_w=self.kn[i])
-            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
-                             self.fd_ws, self.n_q, self.n_kv, self.n_splits, self.scale)
+            self._attend(i)
             if tp:
                 ops.gemv(h2, self.attn, self.wo[i], resid=h if lead else None)
                 self._all_reduce(h2)
@@ -226,11 +241,7 @@ class DenseDecoder:
                                     norm_w=self.ln1[i], eps=cfg.eps)
                 if collect is not None:
                     collect.append(h.clone())
-            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
-                              self.pos, self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i],
-                              kn_w=self.kn[i])
-            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
-                             self.fd_ws, self.n_q, self.n_kv, self.n_splits, self.scale)
+            self._attend(i)
             ops.gemv_tp_publish(self.attn, self.wo[i], ctx, 2 * i, resid=h if lead else None)
             ops.gemv_tp_consume(self.act, self.wgu[i], ctx, 2 * i, x_out=h, norm_w=self.ln2[i],
                                 eps=cfg.eps, epilogue=EPI_SWIGLU)
@@ -259,11 +270,7 @@ class DenseDecoder:
                                     norm_w=self.ln1[i], eps=cfg.eps)
                 if collect is not None:
                     collect.append(h.clone())
-            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
-                              self.pos, self.n_q, self.n_kv, eps=cfg.eps, qn_w=self.qn[i],
-                              kn_w=self.kn[i])
-            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
-                             self.fd_ws, self.n_q, self.n_kv, self.n_splits, self.scale)
+            self._attend(i)
             ops.gemv(h, self.attn, self.wo[i], resid=h)
             ops.gemv(self.router_logits, h, self.w_router[i], norm_w=self.ln2[i], eps=cfg.eps)
             ops.moe_router(self.topk_ids, self.topk_w, self.router_logits.view(1, -1))

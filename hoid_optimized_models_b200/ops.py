@@ -226,6 +226,32 @@ def flash_decode(out: Tensor, q: Tensor, kcache: Tensor, vcache: Tensor, kv_len:
         _flags(), _stream()), "b200_flash_decode")
 
 
+@torch.library.custom_op("b200::rope_flash_decode",
+                         mutates_args=("out", "kcache", "vcache", "workspace"))
+def rope_flash_decode(out: Tensor, kcache: Tensor, vcache: Tensor, workspace: Tensor, qkv: Tensor,
+                      cos: Tensor, sin: Tensor, kv_len: Tensor, n_q: int, n_kv: int,
+                      n_splits: int, scale: float, eps: float = 0.0,
+                      qn_w: Optional[Tensor] = None, kn_w: Optional[Tensor] = None) -> None:
+    """qk_rope_cache + flash_decode in one launch: the packed fp32 q|k|v row of position
+    kv_len - 1 is normalised / rotated in the attention kernel, its k / v row appended to the
+    [n_kv, max_seq, hd] bf16 cache, and out[n_q, hd] attends to rows [0, kv_len)."""
+    _bf16(kcache, "kcache"); _bf16(vcache, "vcache"); _bf16(qn_w, "qn_w"); _bf16(kn_w, "kn_w")
+    if qkv.dtype != torch.float32 or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+        raise TypeError("qkv, cos and sin must be float32")
+    if kv_len.dtype != torch.int32:
+        raise TypeError("kv_len must be int32")
+    hd = qkv.numel() // (n_q + 2 * n_kv)
+    max_seq = kcache.shape[-2]
+    need = _lib.lib().b200_flash_decode_workspace_bytes(n_q, n_kv, hd, n_splits)
+    if workspace.numel() * workspace.element_size() < need:
+        raise RuntimeError("flash_decode workspace too small")
+    check(_lib.lib().b200_rope_flash_decode(
+        _ptr(out), _dt(out), _ptr(qkv), _ptr(kcache), _ptr(vcache), _ptr(cos), _ptr(sin),
+        _ptr(qn_w), _ptr(kn_w), eps, _ptr(kv_len), _ptr(workspace), n_q, n_kv, hd,
+        kcache.stride(-3), kcache.stride(-2), max_seq, n_splits, scale, _flags(), _stream()),
+        "b200_rope_flash_decode")
+
+
 # ----------------------------------------------------------------------------- GEMM
 _STATUS = {}
 

@@ -187,6 +187,21 @@ int b200_flash_decode(void* out, int out_dtype, const void* q, int q_dtype,
                       int64_t kv_head_stride, int64_t kv_row_stride,
                       int n_splits, float scale, int flags, b200_stream_t stream);
 
+/* a2 + a3 + a4 in one launch for the decode step (saves one launch per layer): q, k and v of
+ * the new position (row kv_len - 1) are read from the packed fp32 projection row
+ * [q heads | k heads | v heads]; the kernel applies (QK-RMSNorm +) rotate-half RoPE in its
+ * prologue exactly as b200_qk_rope_cache does, the CTA whose slice ends with the new row appends
+ * k / v (bf16) to the cache, and attention runs over rows [0, kv_len).  cos_t / sin_t are the
+ * [max_seq, hd / 2] fp32 tables; qn_w / kn_w nullable together.  Same workspace as
+ * b200_flash_decode.  Reference: the prepare_qkv + attention pair of
+ * models/llama31-8b/llama31_optimized.py:398-405 (qwen3: qwen3_optimized.py:395-404). */
+int b200_rope_flash_decode(void* out, int out_dtype, const float* qkv, void* kcache, void* vcache,
+                           const float* cos_t, const float* sin_t, const void* qn_w,
+                           const void* kn_w, float eps, const int* kv_len_dev, void* workspace,
+                           int n_q, int n_kv, int hd, int64_t kv_head_stride,
+                           int64_t kv_row_stride, int max_seq, int n_splits, float scale,
+                           int flags, b200_stream_t stream);
+
 /* Flash-decode without any allocation (no counterpart in the reference).
  *
  * Same computation and arguments as b200_flash_decode, minus the workspace: the split

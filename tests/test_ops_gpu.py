@@ -201,6 +201,51 @@ def test_flash_decode(dev, n_q, n_kv, hd, kv_len, n_splits):
         assert rel_err(out, ref) < 2e-5
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd,kv_len,n_splits,qk_norm", [
+    (32, 8, 128, 1, 4, False), (32, 8, 128, 37, 16, False), (32, 8, 128, 1500, 37, False),
+    (32, 8, 128, 8193, 18, False), (32, 8, 128, 1024, 16, True), (32, 4, 128, 1025, 37, True),
+    (16, 4, 128, 129, 8, False), (20, 20, 64, 300, 7, False), (8, 4, 64, 333, 5, True),
+    (4, 1, 128, 700, 74, False)])
+def test_rope_flash_decode_matches_two_kernels(dev, n_q, n_kv, hd, kv_len, n_splits, qk_norm):
+    """The fused launch against qk_rope_cache followed by flash_decode: same attention output,
+    same appended cache row, every other cache row untouched."""
+    from hoid_optimized_models_b200 import ops
+    g = torch.Generator().manual_seed(kv_len + n_splits)
+    max_seq = kv_len + 2
+    pos = kv_len - 1
+    qkv = torch.randn((n_q + 2 * n_kv) * hd, generator=g).to(dev)
+    kc = bf(torch.randn(n_kv, max_seq, hd, generator=g)).to(dev)
+    vc = bf(torch.randn(n_kv, max_seq, hd, generator=g)).to(dev)
+    ang = torch.arange(max_seq, dtype=torch.float64)[:, None] * \
+        (10000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))[None, :]
+    cos, sin = ang.cos().float().to(dev), ang.sin().float().to(dev)
+    qn = bf(1 + 0.1 * torch.randn(hd, generator=g)).to(dev) if qk_norm else None
+    kn = bf(1 + 0.1 * torch.randn(hd, generator=g)).to(dev) if qk_norm else None
+    kl = torch.tensor([kv_len], dtype=torch.int32, device=dev)
+    pd = torch.tensor([pos], dtype=torch.int32, device=dev)
+    ws = ops.flash_decode_workspace(n_q, n_kv, hd, n_splits, dev)
+    # two kernels
+    k2, v2 = kc.clone(), vc.clone()
+    q2 = torch.empty(n_q * hd, dtype=torch.float32, device=dev)
+    out2 = torch.empty(n_q, hd, dtype=torch.float32, device=dev)
+    ops.qk_rope_cache(q2, k2, v2, qkv, cos, sin, pd, n_q, n_kv, eps=1e-6, qn_w=qn, kn_w=kn)
+    ops.flash_decode(out2, q2, k2, v2, kl, ws, n_q, n_kv, n_splits, hd ** -0.5)
+    # one kernel, twice (the second call checks the counters and overwrites the same row)
+    k1, v1 = kc.clone(), vc.clone()
+    out1 = torch.empty(n_q, hd, dtype=torch.float32, device=dev)
+    for _ in range(2):
+        out1.zero_()
+        ops.rope_flash_decode(out1, k1, v1, ws, qkv, cos, sin, kl, n_q, n_kv, n_splits,
+                              hd ** -0.5, eps=1e-6, qn_w=qn, kn_w=kn)
+        assert rel_err(out1, out2.cpu()) < 2e-5
+        # the appended row: bf16 of the same fp32 arithmetic (an fma contraction may move one ulp)
+        assert rel_err(k1[:, pos], k2[:, pos].cpu()) < 1e-2
+        assert torch.equal(v1, v2)
+        keep = torch.ones(max_seq, dtype=torch.bool, device=dev)
+        keep[pos] = False
+        assert torch.equal(k1[:, keep], kc[:, keep])
+
+
 def test_flash_decode_strided_cross_kv(dev):
     """Whisper cross-attention layout: K/V rows are [1500, 20 * 64] projections."""
     from hoid_optimized_models_b200 import ops
