@@ -32,7 +32,7 @@ SIGNATURES = {
     "b200_version": (_i, []),
     "b200_sm_count": (_i, []),
     "b200_set_tuning": (_i, [_i, _i]),
-    "b200_gemv_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _p]),
+    "b200_gemv_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _f, _p, _p, _i, _i, _i, _p]),
     "b200_tp_buffer_bytes": (_l, [_i, _i]),
     "b200_tp_alloc": (_i, [_p, _p, _l]),
     "b200_tp_open": (_i, [_p, _p]),

@@ -50,6 +50,7 @@ struct GemvArgs {
   const uint16_t* w;
   void* y;
   const uint16_t* norm_w;
+  const uint16_t* norm_b;    // non-null: LayerNorm (mean / variance, norm_w = gamma, norm_b = beta)
   const uint16_t* bias;
   const void* resid;
   int K, N, ldw, rpc;  // rpc = rows per CTA
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   pdl_wait();
 
   // stage x (fp32, segment-swizzled: [seg][half][lane] float4) and zero the row partials
-  float ss = 0.f;
+  float ss = 0.f, sm = 0.f;
   float4* xs4 = reinterpret_cast<float4*>(xs);
   unsigned tp_slot = 0;
   if (TP && a.tp_in >= 0) {
@@ -241,11 +242,35 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
       v = make_float4(bf16lo(u.x), bf16hi(u.x), bf16lo(u.y), bf16hi(u.y));
     }
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    sm += (v.x + v.y) + (v.z + v.w);
     const int k = i << 2, seg = k >> 8, within = k & 255;
     xs4[seg * 64 + ((within >> 2) & 1) * 32 + (within >> 3)] = v;
   }
   for (int i = tid; i < a.rpc * kGemvWarps; i += kGemvThreads) part[i] = 0.f;
-  if (a.norm_w != nullptr) {
+  if (a.norm_w != nullptr && a.norm_b != nullptr) {
+    // LayerNorm prologue: two-pass statistics over the staged vector, like the stand-alone kernel
+    const float mean = block_sum(sm, red) / (float)K;
+    float qv = 0.f;
+    for (int i = tid; i < (K >> 2); i += kGemvThreads) {
+      const int k = i << 2, seg = k >> 8, within = k & 255;
+      const float4 v = xs4[seg * 64 + ((within >> 2) & 1) * 32 + (within >> 3)];
+      const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+      qv += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+    }
+    const float scale = rsqrtf(block_sum(qv, red) / (float)K + a.eps);
+    for (int i = tid; i < (K >> 2); i += kGemvThreads) {
+      const int k = i << 2, seg = k >> 8, within = k & 255;
+      const int si = seg * 64 + ((within >> 2) & 1) * 32 + (within >> 3);
+      const uint2 g = reinterpret_cast<const uint2*>(a.norm_w)[i];
+      const uint2 b = reinterpret_cast<const uint2*>(a.norm_b)[i];
+      float4 v = xs4[si];
+      v.x = (v.x - mean) * scale * bf16lo(g.x) + bf16lo(b.x);
+      v.y = (v.y - mean) * scale * bf16hi(g.x) + bf16hi(b.x);
+      v.z = (v.z - mean) * scale * bf16lo(g.y) + bf16lo(b.y);
+      v.w = (v.w - mean) * scale * bf16hi(g.y) + bf16hi(b.y);
+      xs4[si] = v;
+    }
+  } else if (a.norm_w != nullptr) {
     const float tot = block_sum(ss, red);
     const float scale = rsqrtf(tot / (float)K + a.eps);
     for (int i = tid; i < (K >> 2); i += kGemvThreads) {
@@ -387,9 +412,11 @@ static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pd
 using namespace b200;
 
 extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y, int y_dtype,
-                              int K, int N, int ldw, const void* norm_w, float eps,
+                              int K, int N, int ldw, const void* norm_w, const void* norm_beta,
+                              float eps,
                               const void* bias, const void* resid, int resid_dtype,
                               int epilogue, int flags, b200_stream_t stream) {
+  if (norm_beta != nullptr && norm_w == nullptr) return B200_ERR_ARG;
   if (!x || !w || !y) return B200_ERR_ARG;
   if (K <= 0 || N <= 0 || (K & 255) != 0 || ldw < K) return B200_ERR_SHAPE;
   if ((ldw & 7) != 0 || ((uintptr_t)w & 15) != 0 || ((uintptr_t)x & 15) != 0) return B200_ERR_ALIGN;
@@ -399,7 +426,8 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
 
   GemvArgs a{};
   a.x = x; a.w = (const uint16_t*)w; a.y = y;
-  a.norm_w = (const uint16_t*)norm_w; a.bias = (const uint16_t*)bias; a.resid = resid;
+  a.norm_w = (const uint16_t*)norm_w; a.norm_b = (const uint16_t*)norm_beta;
+  a.bias = (const uint16_t*)bias; a.resid = resid;
   a.K = K; a.N = N; a.ldw = ldw; a.rpc = 0;
   a.x_dtype = x_dtype; a.y_dtype = y_dtype; a.resid_dtype = resid_dtype; a.epilogue = epilogue;
   a.eps = eps;

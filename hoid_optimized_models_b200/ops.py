@@ -66,10 +66,10 @@ def _bf16(t: Optional[Tensor], name: str) -> None:
 @torch.library.custom_op("b200::gemv", mutates_args=("y",))
 def gemv(y: Tensor, x: Tensor, w: Tensor, norm_w: Optional[Tensor] = None, eps: float = 0.0,
          bias: Optional[Tensor] = None, resid: Optional[Tensor] = None,
-         epilogue: int = EPI_NONE) -> None:
-    """y = W x with optional RMSNorm prologue, bias, residual and SwiGLU/GELU epilogue.
-    w is the HuggingFace [N, K] weight; x is [K] or [1, K]."""
-    _bf16(w, "w"); _bf16(norm_w, "norm_w"); _bf16(bias, "bias")
+         epilogue: int = EPI_NONE, norm_b: Optional[Tensor] = None) -> None:
+    """y = W x with optional RMSNorm (norm_w) or LayerNorm (norm_w, norm_b) prologue, bias,
+    residual and SwiGLU/GELU epilogue.  w is the HuggingFace [N, K] weight; x is [K] or [1, K]."""
+    _bf16(w, "w"); _bf16(norm_w, "norm_w"); _bf16(norm_b, "norm_b"); _bf16(bias, "bias")
     N, K = w.shape
     if x.numel() != K:
         raise RuntimeError(f"x has {x.numel()} elements, expected {K}")
@@ -78,8 +78,8 @@ def gemv(y: Tensor, x: Tensor, w: Tensor, norm_w: Optional[Tensor] = None, eps: 
         raise RuntimeError(f"y has {y.numel()} elements, expected {n_out}")
     check(_lib.lib().b200_gemv_bf16(
         _ptr(x), _dt(x), _ptr(w), _ptr(y), _dt(y), K, N, w.stride(0),
-        _ptr(norm_w), eps, _ptr(bias), _ptr(resid), _dt(resid) if resid is not None else 0,
-        epilogue, _flags(), _stream()), "b200_gemv_bf16")
+        _ptr(norm_w), _ptr(norm_b), eps, _ptr(bias), _ptr(resid),
+        _dt(resid) if resid is not None else 0, epilogue, _flags(), _stream()), "b200_gemv_bf16")
 
 
 # ----------------------------------------------------------------------------- fused TP GEMV

@@ -176,7 +176,7 @@ class WhisperDecoder:
         self.ws_cross = ops.flash_decode_workspace(H, H, hd, self.cross_splits, dev)
         self.am_ws = ops.argmax_workspace(dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.launches_per_step = 3 + 13 * cfg.dec_layers + 4
+        self.launches_per_step = 4 + 9 * cfg.dec_layers + 3
 
     @torch.no_grad()
     def set_encoder(self, enc_out: torch.Tensor) -> None:
@@ -194,28 +194,30 @@ class WhisperDecoder:
         x, h = self.x, self.h
         first = True
         for i, L in enumerate(self.layers):
+            # every LayerNorm is the prologue of the GEMV that consumes it; identity cos / sin
+            # tables turn the fused RoPE + cache-append + attention launch into Whisper's
+            # position-free self-attention
             if first:   # residual stream = token + position embedding, fused with the first norm
                 ops.add_layernorm(h, x, self.e_tok, L["ln1"][0], L["ln1"][1], cfg.eps, resid=self.e_pos)
+                ops.gemv(self.qkv, h, L["wqkv"], bias=L["bqkv"])
                 first = False
             else:
-                ops.layernorm(h, x, L["ln1"][0], L["ln1"][1], cfg.eps)
-            ops.gemv(self.qkv, h, L["wqkv"], bias=L["bqkv"])
-            ops.qk_rope_cache(self.q, self.kv[i, 0], self.kv[i, 1], self.qkv, self.cos, self.sin,
-                              self.pos, H, H)
-            ops.flash_decode(self.attn, self.q, self.kv[i, 0], self.kv[i, 1], self.kv_len,
-                             self.ws_self, H, H, self.self_splits, scale)
+                ops.gemv(self.qkv, x, L["wqkv"], bias=L["bqkv"], norm_w=L["ln1"][0],
+                         norm_b=L["ln1"][1], eps=cfg.eps)
+            ops.rope_flash_decode(self.attn, self.kv[i, 0], self.kv[i, 1], self.ws_self, self.qkv,
+                                  self.cos, self.sin, self.kv_len, H, H, self.self_splits, scale)
             ops.gemv(x, self.attn, L["wo"], bias=L["bo"], resid=x)
-            ops.layernorm(h, x, L["ln2"][0], L["ln2"][1], cfg.eps)
-            ops.gemv(self.cq, h, L["wcq"], bias=L["bcq"])
+            ops.gemv(self.cq, x, L["wcq"], bias=L["bcq"], norm_w=L["ln2"][0], norm_b=L["ln2"][1],
+                     eps=cfg.eps)
             ops.flash_decode(self.attn, self.cq, self.cross_k[i], self.cross_v[i], self.enc_len,
                              self.ws_cross, H, H, self.cross_splits, scale,
                              kv_head_stride=hd, kv_row_stride=D)
             ops.gemv(x, self.attn, L["wco"], bias=L["bco"], resid=x)
-            ops.layernorm(h, x, L["ln3"][0], L["ln3"][1], cfg.eps)
-            ops.gemv(self.act, h, L["wf1"], bias=L["bf1"], epilogue=ops.EPI_GELU)
+            ops.gemv(self.act, x, L["wf1"], bias=L["bf1"], epilogue=ops.EPI_GELU,
+                     norm_w=L["ln3"][0], norm_b=L["ln3"][1], eps=cfg.eps)
             ops.gemv(x, self.act, L["wf2"], bias=L["bf2"], resid=x)
-        ops.layernorm(h, x, self.ln_f[0], self.ln_f[1], cfg.eps)
-        ops.gemv(self.logits, h, self.embed_tok)
+        ops.gemv(self.logits, x, self.embed_tok, norm_w=self.ln_f[0], norm_b=self.ln_f[1],
+                 eps=cfg.eps)
         ops.argmax(self.cand, self.logits, self.am_ws)
         ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
 

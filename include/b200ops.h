@@ -72,6 +72,9 @@ int b200_sm_count(void);
  * Optional fusions (pass NULL to disable):
  *   norm_w  : RMSNorm prologue, x <- x * rsqrt(mean(x^2) + eps) * norm_w   (bf16 [K])
  *             (replaces models/llama31-8b/kernels/rmsnorm_prefetch16_k.cu:4-22 at s = 1)
+ *   norm_beta : with norm_w, LayerNorm prologue instead: x <- (x - mean) * rsqrt(var + eps) *
+ *             norm_w + norm_beta, two-pass fp32 statistics (replaces the stand-alone LayerNorm
+ *             launches of models/whisper-large-v3/whisper_decoder_optimized.py:416-447)
  *   bias    : bf16 [N] added to y
  *   resid   : y = resid + W x; may alias y (replaces kernels/add_bf16_vec8_k.cu:10-21)
  *   epilogue: B200_EPI_SWIGLU over interleaved gate/up rows, output length N/2
@@ -80,7 +83,7 @@ int b200_sm_count(void);
  */
 int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y, int y_dtype,
                    int K, int N, int ldw,
-                   const void* norm_w, float eps,
+                   const void* norm_w, const void* norm_beta, float eps,
                    const void* bias,
                    const void* resid, int resid_dtype,
                    int epilogue, int flags, b200_stream_t stream);

@@ -54,9 +54,9 @@ def test_no_gpu_calls_needed_for_queries(lib):
 
 def test_argument_validation_returns_codes(lib):
     # null pointers and bad shapes are rejected on the host before any launch
-    assert lib.b200_gemv_bf16(None, 0, None, None, 0, 256, 8, 256, None, 0.0, None, None, 0, 0, 0, None) == -4
+    assert lib.b200_gemv_bf16(None, 0, None, None, 0, 256, 8, 256, None, None, 0.0, None, None, 0, 0, 0, None) == -4
     one = ctypes.c_void_p(16)
-    assert lib.b200_gemv_bf16(one, 0, one, one, 0, 100, 8, 100, None, 0.0, None, None, 0, 0, 0, None) == -1
+    assert lib.b200_gemv_bf16(one, 0, one, one, 0, 100, 8, 100, None, None, 0.0, None, None, 0, 0, 0, None) == -1
     assert lib.b200_add_rmsnorm(None, one, 0, one, 0, None, 0, one, 1, 12, 1e-5, 0, None) == -1
     assert lib.b200_flash_decode(one, 1, one, 1, one, one, one, one, 32, 5, 128, 128, 128, 4, 1.0, 0, None) == -1
     assert lib.b200_gemm_bf16(one, one, one, 0, 128, 100, 64, 64, 64, 100, None, None, 0, 0, None, 0, None) == -1
