@@ -35,6 +35,113 @@ struct FdArgs {
 // threads per CTA: the register file holds 512 threads at 128 registers (G <= 4)
 constexpr int fd_threads(int G) { return G <= 4 ? 512 : 256; }
 
+// ---- shared tail of both kernels -------------------------------------------------------------
+// In: srec[WARPS][REC] holds one record (acc[G][HD], m[G], l[G]) per warp.  The warps are merged,
+// the CTA's record goes to the workspace, and the CTA that arrives last on the kv head's counter
+// merges the n_splits records.  srec is re-used as scratch by that last step and must hold at
+// least 6 * THREADS floats.
+template <int HD, int G, int THREADS>
+__device__ __forceinline__ void fd_finish(const FdArgs& a, float* srec, float* sw, int kvh,
+                                          int split) {
+  constexpr int WARPS = THREADS / 32;
+  constexpr int REC = G * HD + ((2 * G + 3) & ~3);
+  __shared__ float s_M[G], s_den[G];
+  __shared__ int s_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __syncthreads();
+  // ---- merge the CTA's warps: warp g' computes the weights of head g' ----
+  for (int g = warp; g < G; g += WARPS) {
+    const float mv = lane < WARPS ? srec[lane * REC + G * HD + g] : -INFINITY;
+    const float M = warp_max(mv);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    const float w = lane < WARPS ? exp2f(mv - Mu) : 0.f;
+    const float den = warp_sum(lane < WARPS ? srec[lane * REC + G * HD + G + g] * w : 0.f);
+    if (lane < WARPS) sw[lane * G + g] = w;
+    if (lane == 0) { s_M[g] = M; s_den[g] = den; }
+  }
+  __syncthreads();
+  float* wr = a.recs + (size_t)(kvh * a.n_splits + split) * REC;
+  for (int i = tid; i < G * HD; i += THREADS) {
+    const int g = i / HD;
+    float num = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < WARPS; ++w2) num = fmaf(srec[w2 * REC + i], sw[w2 * G + g], num);
+    wr[i] = num;
+  }
+  if (tid < G) { wr[G * HD + tid] = s_M[tid]; wr[G * HD + G + tid] = s_den[tid]; }
+
+  // ---- publish, and let the last-arriving CTA of this kv head finish the job ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&a.counters[kvh], 1);
+    s_last = (old == a.n_splits - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  // Every thread owns one float4 column of the output and every PARTS-th split: all its loads
+  // are independent (one L2 round trip), the partial results meet in shared memory.
+  constexpr int C4 = G * HD / 4;
+  constexpr int PARTS = (THREADS / C4) >= 8 ? 8 : ((THREADS / C4) >= 1 ? (THREADS / C4) : 1);
+  static_assert(C4 <= THREADS, "one pass over the output columns");
+  float4* sp_num = reinterpret_cast<float4*>(srec);             // [PARTS][C4]
+  float* sp_m = srec + 4 * PARTS * C4;                          // [PARTS][C4]
+  float* sp_d = sp_m + PARTS * C4;
+  const float* rb = a.recs + (size_t)kvh * a.n_splits * REC;
+  const int ns = a.n_splits;
+  if (tid < PARTS * C4) {
+    const int c = tid % C4, part = tid / C4, g = (c * 4) / HD;
+    float m_run = -INFINITY, den = 0.f;
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int sp = part; sp < ns; sp += PARTS) {
+      const float* rec = rb + (size_t)sp * REC;
+      const float mv = __ldcg(rec + G * HD + g);
+      const float lv = __ldcg(rec + G * HD + G + g);
+      const float4 r = __ldcg(reinterpret_cast<const float4*>(rec) + c);
+      const float mn = fmaxf(m_run, mv);
+      const float mu = (mn == -INFINITY) ? 0.f : mn;
+      const float wa = exp2f(m_run - mu), wb = exp2f(mv - mu);
+      num.x = num.x * wa + r.x * wb; num.y = num.y * wa + r.y * wb;
+      num.z = num.z * wa + r.z * wb; num.w = num.w * wa + r.w * wb;
+      den = den * wa + lv * wb;
+      m_run = mn;
+    }
+    sp_num[tid] = num; sp_m[tid] = m_run; sp_d[tid] = den;
+  }
+  __syncthreads();
+  if (tid < C4) {
+    float m_run = sp_m[tid], den = sp_d[tid];
+    float4 num = sp_num[tid];
+#pragma unroll
+    for (int p = 1; p < PARTS; ++p) {
+      const float mv = sp_m[p * C4 + tid], lv = sp_d[p * C4 + tid];
+      const float4 r = sp_num[p * C4 + tid];
+      const float mn = fmaxf(m_run, mv);
+      const float mu = (mn == -INFINITY) ? 0.f : mn;
+      const float wa = exp2f(m_run - mu), wb = exp2f(mv - mu);
+      num.x = num.x * wa + r.x * wb; num.y = num.y * wa + r.y * wb;
+      num.z = num.z * wa + r.z * wb; num.w = num.w * wa + r.w * wb;
+      den = den * wa + lv * wb;
+      m_run = mn;
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    const size_t oi = (size_t)kvh * G * HD + (size_t)tid * 4;
+    if (a.out_dtype == B200_F32) {
+      reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + oi)[0] =
+          make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+    } else {
+      uint2 w2;
+      w2.x = pack_bf16(num.x * inv, num.y * inv);
+      w2.y = pack_bf16(num.z * inv, num.w * inv);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out) + oi) = w2;
+    }
+  }
+  if (tid == 0) a.counters[kvh] = 0;  // ready for the next launch
+}
+
 template <int HD, int G, bool ROPE = false>
 __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
   constexpr int THREADS = fd_threads(G);
@@ -44,9 +151,7 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
   constexpr int REC = G * HD + ((2 * G + 3) & ~3);  // record: acc[G][HD], m[G], l[G], 16-byte padded
   extern __shared__ __align__(16) float fd_smem[];
   float* srec = fd_smem;               // [WARPS][REC]
-  float* sw = srec + WARPS * REC;      // [max(WARPS, n_splits)][G] merge weights
-  __shared__ float s_M[G], s_den[G];
-  __shared__ int s_last;
+  float* sw = srec + WARPS * REC;      // [WARPS][G] merge weights
   __shared__ uint4 s_newk[ROPE ? HD / 8 : 1], s_newv[ROPE ? HD / 8 : 1];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -261,86 +366,16 @@ __global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
       if (dl == 0) { r[G * HD + g] = m[g]; r[G * HD + G + g] = l[g]; }
     }
   }
-  __syncthreads();
-  // ---- merge the CTA's warps: warp g' computes the weights of head g' ----
-  for (int g = warp; g < G; g += WARPS) {
-    const float mv = lane < WARPS ? srec[lane * REC + G * HD + g] : -INFINITY;
-    const float M = warp_max(mv);
-    const float Mu = (M == -INFINITY) ? 0.f : M;
-    const float w = lane < WARPS ? exp2f(mv - Mu) : 0.f;
-    const float den = warp_sum(lane < WARPS ? srec[lane * REC + G * HD + G + g] * w : 0.f);
-    if (lane < WARPS) sw[lane * G + g] = w;
-    if (lane == 0) { s_M[g] = M; s_den[g] = den; }
-  }
-  __syncthreads();
-  float* wr = a.recs + (size_t)(kvh * a.n_splits + split) * REC;
-  for (int i = tid; i < G * HD; i += THREADS) {
-    const int g = i / HD;
-    float num = 0.f;
-#pragma unroll
-    for (int w2 = 0; w2 < WARPS; ++w2) num = fmaf(srec[w2 * REC + i], sw[w2 * G + g], num);
-    wr[i] = num;
-  }
-  if (tid < G) { wr[G * HD + tid] = s_M[tid]; wr[G * HD + G + tid] = s_den[tid]; }
-
-  // ---- publish, and let the last-arriving CTA of this kv head finish the job ----
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(&a.counters[kvh], 1);
-    s_last = (old == a.n_splits - 1);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-
-  const float* rb = a.recs + (size_t)kvh * a.n_splits * REC;
-  const int ns = a.n_splits;
-  for (int g = warp; g < G; g += WARPS) {
-    float M = -INFINITY;
-    for (int sp = lane; sp < ns; sp += 32) M = fmaxf(M, __ldcg(rb + (size_t)sp * REC + G * HD + g));
-    M = warp_max(M);
-    const float Mu = (M == -INFINITY) ? 0.f : M;
-    float den = 0.f;
-    for (int sp = lane; sp < ns; sp += 32) {
-      const float w = exp2f(__ldcg(rb + (size_t)sp * REC + G * HD + g) - Mu);
-      sw[sp * G + g] = w;
-      den = fmaf(__ldcg(rb + (size_t)sp * REC + G * HD + G + g), w, den);
-    }
-    den = warp_sum(den);
-    if (lane == 0) s_den[g] = den;
-  }
-  __syncthreads();
-  for (int i4 = tid; i4 < G * HD / 4; i4 += THREADS) {
-    const int g = (i4 * 4) / HD;
-    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int sp = 0; sp < ns; ++sp) {
-      const float4 r = __ldcg(reinterpret_cast<const float4*>(rb + (size_t)sp * REC) + i4);
-      const float w = sw[sp * G + g];
-      num.x = fmaf(r.x, w, num.x); num.y = fmaf(r.y, w, num.y);
-      num.z = fmaf(r.z, w, num.z); num.w = fmaf(r.w, w, num.w);
-    }
-    const float inv = s_den[g] > 0.f ? 1.f / s_den[g] : 0.f;
-    const size_t oi = (size_t)kvh * G * HD + (size_t)i4 * 4;
-    if (a.out_dtype == B200_F32) {
-      reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + oi)[0] =
-          make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
-    } else {
-      uint2 w2;
-      w2.x = pack_bf16(num.x * inv, num.y * inv);
-      w2.y = pack_bf16(num.z * inv, num.w * inv);
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out) + oi) = w2;
-    }
-  }
-  if (tid == 0) a.counters[kvh] = 0;  // ready for the next launch
+  fd_finish<HD, G, THREADS>(a, srec, sw, kvh, split);
 }
 
 template <int HD, int G>
 static size_t fd_smem_bytes(int n_splits) {
   constexpr int WARPS = fd_threads(G) / 32;
-  const int wrows = n_splits > WARPS ? n_splits : WARPS;
-  return (size_t)(WARPS * (G * HD + ((2 * G + 3) & ~3)) + wrows * G) * 4;
+  (void)n_splits;
+  size_t rec = (size_t)WARPS * (G * HD + ((2 * G + 3) & ~3));
+  if (rec < 6 * (size_t)fd_threads(G)) rec = 6 * (size_t)fd_threads(G);   // combine scratch
+  return (rec + (size_t)WARPS * G) * 4;
 }
 
 template <int HD, int G, bool ROPE = false>
@@ -353,6 +388,330 @@ static cudaError_t fd_launch(const FdArgs& a, cudaStream_t st, bool pdl) {
     attr_set = true;
   }
   return launch(flash_decode_kernel<HD, G, ROPE>, dim3(a.n_splits, a.n_kv), dim3(fd_threads(G)),
+                smem, st, pdl, a);
+}
+
+// ---- tensor-core variant ---------------------------------------------------------------------
+// The SIMT kernel above spends ~185 instructions per KB of cache (a 16-lane shuffle reduction per
+// key and head) and is issue-bound near 4 TB/s.  Here a CTA of eight warps streams 128-key tiles
+// of K and V through a three-stage cp.async ring; each warp owns 16 keys of a tile and runs
+// S = Q K^T and O += P V on mma.sync m16n8k16 (about 20 instructions per KB).  The 16-row A
+// operand carries the group's G <= 8 query heads twice: rows 0..7 hold the bf16 high part of q
+// (and of P), rows 8..15 the bf16 low part, so q and P keep ~16 mantissa bits at no extra MMA and
+// the two halves of an accumulator add up inside one thread.
+constexpr int kFmThreads = 256, kFmWarps = 8, kFmTile = 128, kFmStages = 3;
+
+__device__ __forceinline__ void fm_cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void fm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void fm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fm_ldsm(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void fm_ldsm_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                          uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void fm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// byte offset of 16-byte chunk c of row r in an XOR-swizzled [rows][HD] bf16 tile
+template <int HD>
+__device__ __forceinline__ uint32_t fm_swz(int r, int c) {
+  return (uint32_t)(r * (HD * 2) + ((c ^ (r & 7)) << 4));
+}
+// bf16 high / low split of two fp32 values, packed for an A fragment
+__device__ __forceinline__ void fm_split(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 xh = __float2bfloat16(x), yh = __float2bfloat16(y);
+  hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
+  lo = pack_bf16(x - __bfloat162float(xh), y - __bfloat162float(yh));
+}
+
+template <int HD, int G, bool ROPE>
+__global__ void __launch_bounds__(kFmThreads, 1) flash_decode_mma_kernel(FdArgs a) {
+  constexpr int KS = HD / 16;          // k16 steps over the head dim
+  constexpr int DB = HD / 8;           // n8 blocks over the head dim
+  constexpr int CPR = HD / 8;          // 16-byte chunks per row
+  constexpr int TILE = kFmTile * HD * 2;                 // bytes of one K (or V) tile
+  constexpr int REC = G * HD + ((2 * G + 3) & ~3);
+  extern __shared__ __align__(128) unsigned char fm_smem[];
+  const uint32_t ring = smem_u32(fm_smem);               // [stages][K tile | V tile]
+  float* srec = reinterpret_cast<float*>(fm_smem);       // re-uses the ring after the loop
+  float* sw = reinterpret_cast<float*>(fm_smem + kFmStages * 2 * TILE);   // [WARPS][G]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, tq = lane & 3;                // fragment row (= head) and column pair
+  const int split = blockIdx.x, kvh = blockIdx.y;
+
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int kv_len = a.kv_len[0];
+  const int per = (kv_len + a.n_splits - 1) / a.n_splits;
+  const int k0 = split * per;
+  const int k1 = min(kv_len, k0 + per);
+  const int ntiles = k1 > k0 ? (k1 - k0 + kFmTile - 1) / kFmTile : 0;
+
+  const uint16_t* kb = a.k + (size_t)kvh * a.head_stride;
+  const uint16_t* vb = a.v + (size_t)kvh * a.head_stride;
+  auto load_tile = [&](int t) {
+    const uint32_t sk = ring + (t % kFmStages) * 2 * TILE, sv = sk + TILE;
+    const int row0 = k0 + t * kFmTile;
+#pragma unroll
+    for (int i = tid; i < kFmTile * CPR; i += kFmThreads) {
+      const int r = i / CPR, c = i % CPR;
+      int gr = row0 + r;
+      gr = gr < k1 ? gr : k1 - 1;                        // rows past the slice are masked below
+      const size_t off = (size_t)gr * a.row_stride + c * 8;
+      fm_cp16(sk + fm_swz<HD>(r, c), kb + off);
+      fm_cp16(sv + fm_swz<HD>(r, c), vb + off);
+    }
+  };
+  if (0 < ntiles) load_tile(0);
+  fm_commit();
+  if (1 < ntiles) load_tile(1);
+  fm_commit();
+
+  // ---- q as A fragments: head g in rows g (high part) and g + 8 (low part) ----
+  uint32_t qf[KS][4];
+  int pos_own = -1;
+  uint4 newk = make_uint4(0, 0, 0, 0), newv = make_uint4(0, 0, 0, 0);
+  {
+    float x[KS][4];                                      // dims ks*16 + tq*2 + {0, 1, 8, 9}
+    const bool live = g < G;
+    if (ROPE) {
+      const int pos = kv_len - 1;
+      const bool in_cache = pos >= 0 && pos < a.max_seq;
+      const float* src = a.qkv + (size_t)(kvh * G + (live ? g : 0)) * HD;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const float2 u = *reinterpret_cast<const float2*>(src + ks * 16 + tq * 2);
+        const float2 w = *reinterpret_cast<const float2*>(src + ks * 16 + tq * 2 + 8);
+        x[ks][0] = u.x; x[ks][1] = u.y; x[ks][2] = w.x; x[ks][3] = w.y;
+      }
+      if (a.qn_w != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ss = fmaf(x[ks][e], x[ks][e], ss);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        const float inv = rsqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(a.qn_w + ks * 16 + tq * 2);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(a.qn_w + ks * 16 + tq * 2 + 8);
+          x[ks][0] = x[ks][0] * inv * bf16lo(w0); x[ks][1] = x[ks][1] * inv * bf16hi(w0);
+          x[ks][2] = x[ks][2] * inv * bf16lo(w1); x[ks][3] = x[ks][3] * inv * bf16hi(w1);
+        }
+      }
+      // rotate-half: dim d < HD/2 pairs with d + HD/2, which the same thread holds in step ks + KS/2
+      const size_t ci = (size_t)(in_cache ? pos : 0) * (HD / 2);
+#pragma unroll
+      for (int ks = 0; ks < KS / 2; ++ks) {
+        const float2 c0 = *reinterpret_cast<const float2*>(a.cos_t + ci + ks * 16 + tq * 2);
+        const float2 c1 = *reinterpret_cast<const float2*>(a.cos_t + ci + ks * 16 + tq * 2 + 8);
+        const float2 s0 = *reinterpret_cast<const float2*>(a.sin_t + ci + ks * 16 + tq * 2);
+        const float2 s1 = *reinterpret_cast<const float2*>(a.sin_t + ci + ks * 16 + tq * 2 + 8);
+        const float cs[4] = {c0.x, c0.y, c1.x, c1.y}, sn[4] = {s0.x, s0.y, s1.x, s1.y};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = x[ks][e], hi = x[ks + KS / 2][e];
+          x[ks][e] = lo * cs[e] - hi * sn[e];
+          x[ks + KS / 2][e] = hi * cs[e] + lo * sn[e];
+        }
+      }
+      // the new k / v row: (norm +) RoPE in the 8-dims-per-lane layout, by warp 0 of the CTA whose
+      // slice ends with it
+      if (in_cache && pos >= k0 && pos < k1) {
+        pos_own = pos;
+        if (warp == 0) {
+          constexpr int LPK = HD / 8, HL = LPK / 2;
+          const int dl = lane % LPK;
+          const bool hi = dl >= HL;
+          const float* ks_ = a.qkv + (size_t)(a.n_q + kvh) * HD + dl * 8;
+          const float4 x0 = reinterpret_cast<const float4*>(ks_)[0];
+          const float4 x1 = reinterpret_cast<const float4*>(ks_)[1];
+          float kx[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+          if (a.kn_w != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(kx[e], kx[e], ss);
+#pragma unroll
+            for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+            const float inv = rsqrtf(ss / (float)HD + a.eps);
+            float w[8];
+            unpack8(*reinterpret_cast<const uint4*>(a.kn_w + dl * 8), w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) kx[e] = kx[e] * inv * w[e];
+          }
+          const float* cp = a.cos_t + ci + (size_t)(dl - (hi ? HL : 0)) * 8;
+          const float* sp = a.sin_t + ci + (size_t)(dl - (hi ? HL : 0)) * 8;
+          const float4 c0 = reinterpret_cast<const float4*>(cp)[0], c1 = reinterpret_cast<const float4*>(cp)[1];
+          const float4 s0 = reinterpret_cast<const float4*>(sp)[0], s1 = reinterpret_cast<const float4*>(sp)[1];
+          const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          float kr[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, kx[e], HL);
+            kr[e] = hi ? (kx[e] * cs[e] + other * sn[e]) : (kx[e] * cs[e] - other * sn[e]);
+          }
+          const float4* vp = reinterpret_cast<const float4*>(
+              a.qkv + (size_t)(a.n_q + a.n_kv + kvh) * HD + dl * 8);
+          const float4 v0 = vp[0], v1 = vp[1];
+          newk.x = pack_bf16(kr[0], kr[1]); newk.y = pack_bf16(kr[2], kr[3]);
+          newk.z = pack_bf16(kr[4], kr[5]); newk.w = pack_bf16(kr[6], kr[7]);
+          newv.x = pack_bf16(v0.x, v0.y); newv.y = pack_bf16(v0.z, v0.w);
+          newv.z = pack_bf16(v1.x, v1.y); newv.w = pack_bf16(v1.z, v1.w);
+          if (lane < LPK) {
+            const size_t row = (size_t)kvh * a.head_stride + (size_t)pos * a.row_stride + dl * 8;
+            *reinterpret_cast<uint4*>(const_cast<uint16_t*>(a.k) + row) = newk;
+            *reinterpret_cast<uint4*>(const_cast<uint16_t*>(a.v) + row) = newv;
+          }
+        }
+      }
+    } else {
+      const size_t qi = (size_t)(kvh * G + (live ? g : 0)) * HD;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        if (a.q_dtype == B200_F32) {
+          const float* src = reinterpret_cast<const float*>(a.q) + qi + ks * 16 + tq * 2;
+          const float2 u = *reinterpret_cast<const float2*>(src);
+          const float2 w = *reinterpret_cast<const float2*>(src + 8);
+          x[ks][0] = u.x; x[ks][1] = u.y; x[ks][2] = w.x; x[ks][3] = w.y;
+        } else {
+          const uint16_t* src = reinterpret_cast<const uint16_t*>(a.q) + qi + ks * 16 + tq * 2;
+          const uint32_t u = *reinterpret_cast<const uint32_t*>(src);
+          const uint32_t w = *reinterpret_cast<const uint32_t*>(src + 8);
+          x[ks][0] = bf16lo(u); x[ks][1] = bf16hi(u); x[ks][2] = bf16lo(w); x[ks][3] = bf16hi(w);
+        }
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const float sc = live ? a.scale_log2 : 0.f;        // padding rows carry zeros
+      fm_split(x[ks][0] * sc, x[ks][1] * sc, qf[ks][0], qf[ks][1]);
+      fm_split(x[ks][2] * sc, x[ks][3] * sc, qf[ks][2], qf[ks][3]);
+    }
+  }
+
+  float o[DB][4];
+#pragma unroll
+  for (int d = 0; d < DB; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+  float m = -INFINITY, l = 0.f;
+
+  for (int t = 0; t < ntiles; ++t) {
+    fm_wait<1>();                    // tile t has landed (at most tile t + 1 still in flight)
+    __syncthreads();                 // ... for every thread, and everyone is done with tile t - 1
+    if (t + 2 < ntiles) load_tile(t + 2);
+    fm_commit();
+    const uint32_t sk = ring + (t % kFmStages) * 2 * TILE, sv = sk + TILE;
+    const int row0 = k0 + t * kFmTile;
+    if (ROPE && pos_own >= row0 && pos_own < row0 + kFmTile) {   // CTA-uniform
+      // the cache row this launch appends must not be read back through the async copies
+      if (warp == 0 && lane < HD / 8) {
+        const uint32_t off = fm_swz<HD>(pos_own - row0, lane);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sk + off), "r"(newk.x),
+                     "r"(newk.y), "r"(newk.z), "r"(newk.w) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sv + off), "r"(newv.x),
+                     "r"(newv.y), "r"(newv.z), "r"(newv.w) : "memory");
+      }
+      __syncthreads();
+    }
+    const int key0 = row0 + warp * 16;                   // this warp's 16 keys
+    if (key0 >= k1) continue;                            // warp-uniform
+    // ---- S = Q K^T : 16 rows x 16 keys ----
+    float s[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      const int key = warp * 16 + ((lane >> 4) << 3) + (lane & 7);
+      const int c = ks * 2 + ((lane >> 3) & 1);
+      fm_ldsm(sk + fm_swz<HD>(key, c), b0, b1, b2, b3);
+      fm_mma(s[0], qf[ks], b0, b1);
+      fm_mma(s[1], qf[ks], b2, b3);
+    }
+    // high + low rows of the same head meet in one thread
+    float sv4[4] = {s[0][0] + s[0][2], s[0][1] + s[0][3], s[1][0] + s[1][2], s[1][1] + s[1][3]};
+    if (key0 + 16 > k1) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + (e >> 1) * 8 + tq * 2 + (e & 1);
+        if (key >= k1) sv4[e] = -INFINITY;
+      }
+    }
+    float mt = fmaxf(fmaxf(sv4[0], sv4[1]), fmaxf(sv4[2], sv4[3]));
+    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+    const float mn = fmaxf(m, mt);
+    const float mu = (mn == -INFINITY) ? 0.f : mn;
+    const float corr = exp2f(m - mu);
+    m = mn;
+    float p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) p[e] = exp2f(sv4[e] - mu);
+    l = l * corr + (p[0] + p[1]) + (p[2] + p[3]);
+    uint32_t pf[4];                  // P as the A fragment of one k16 step: rows g / g + 8 = hi / lo
+    fm_split(p[0], p[1], pf[0], pf[1]);
+    fm_split(p[2], p[3], pf[2], pf[3]);
+#pragma unroll
+    for (int d = 0; d < DB; ++d) { o[d][0] *= corr; o[d][1] *= corr; o[d][2] *= corr; o[d][3] *= corr; }
+    // ---- O += P V ----
+#pragma unroll
+    for (int d2 = 0; d2 < DB / 2; ++d2) {
+      uint32_t b0, b1, b2, b3;
+      const int key = warp * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+      const int c = d2 * 2 + (lane >> 4);
+      fm_ldsm_t(sv + fm_swz<HD>(key, c), b0, b1, b2, b3);
+      fm_mma(o[d2 * 2], pf, b0, b1);
+      fm_mma(o[d2 * 2 + 1], pf, b2, b3);
+    }
+  }
+  fm_wait<0>();
+  __syncthreads();                   // the ring is free: it becomes the record area
+
+  // ---- one record per warp ----
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (g < G) {
+    float* r = srec + warp * REC;
+#pragma unroll
+    for (int d = 0; d < DB; ++d)
+      *reinterpret_cast<float2*>(r + g * HD + d * 8 + tq * 2) =
+          make_float2(o[d][0] + o[d][2], o[d][1] + o[d][3]);
+    if (tq == 0) { r[G * HD + g] = m; r[G * HD + G + g] = l; }
+  }
+  fd_finish<HD, G, kFmThreads>(a, srec, sw, kvh, split);
+}
+
+template <int HD, int G>
+static size_t fm_smem_bytes() {
+  return (size_t)kFmStages * 2 * kFmTile * HD * 2 + (size_t)kFmWarps * G * 4;
+}
+
+template <int HD, int G, bool ROPE>
+static cudaError_t fm_launch(const FdArgs& a, cudaStream_t st, bool pdl) {
+  const size_t smem = fm_smem_bytes<HD, G>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(flash_decode_mma_kernel<HD, G, ROPE>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  return launch(flash_decode_mma_kernel<HD, G, ROPE>, dim3(a.n_splits, a.n_kv), dim3(kFmThreads),
                 smem, st, pdl, a);
 }
 
@@ -392,7 +751,9 @@ extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) e = fd_launch<HD_, G_>(a, st, pdl); else
+  const bool simt = g_tuning[B200_TUNE_FLASH_DECODE] == 1;
+#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) \
+    e = simt ? fd_launch<HD_, G_>(a, st, pdl) : fm_launch<HD_, G_, false>(a, st, pdl); else
   FD_CASE(128, 1) FD_CASE(128, 2) FD_CASE(128, 4) FD_CASE(128, 8)
   FD_CASE(64, 1) FD_CASE(64, 2) FD_CASE(64, 4) FD_CASE(64, 8)
   return B200_ERR_SHAPE;
@@ -435,7 +796,9 @@ extern "C" int b200_rope_flash_decode(void* out, int out_dtype, const float* qkv
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) e = fd_launch<HD_, G_, true>(a, st, pdl); else
+  const bool simt = g_tuning[B200_TUNE_FLASH_DECODE] == 1;
+#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) \
+    e = simt ? fd_launch<HD_, G_, true>(a, st, pdl) : fm_launch<HD_, G_, true>(a, st, pdl); else
   FD_CASE(128, 1) FD_CASE(128, 2) FD_CASE(128, 4) FD_CASE(128, 8)
   FD_CASE(64, 1) FD_CASE(64, 2) FD_CASE(64, 4) FD_CASE(64, 8)
   return B200_ERR_SHAPE;
