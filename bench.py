@@ -176,8 +176,8 @@ def run_secondary(args):
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     ops.set_pdl(not args.no_pdl)
-    if args.tp_allreduce == "fused-flags":
-        ops.set_tuning(2, 1)                       # B200_TUNE_TP_PROTOCOL
+    if args.tp_allreduce.startswith("fused-"):     # B200_TUNE_TP_PROTOCOL
+        ops.set_tuning(2, {"flags": 1, "direct": 2, "summed": 3}[args.tp_allreduce[6:]])
     peak, peak_kind = measured_peaks()
     K, W = args.steps, max(args.warmup, 3)
     name = args.workload
@@ -301,7 +301,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--ttft-runs", type=int, default=3)
-    ap.add_argument("--tp-allreduce", default="fused", choices=["fused", "fused-flags", "nccl"],
+    ap.add_argument("--tp-allreduce", default="fused", choices=["fused", "fused-flags", "fused-direct", "fused-summed", "nccl"],
                     help="N>1: all-reduce fused into the GEMVs over peer memory (tagged pairs, or "
                          "data + sequence flags), or NCCL calls")
     ap.add_argument("--workload", default="llama-3.1-8b",
@@ -357,8 +357,8 @@ def main():
     from hoid_optimized_models_b200.decoder import Llama31Optimized
     from hoid_optimized_models_b200.weights import make_decoder_weights
     ops.set_pdl(not args.no_pdl)
-    if args.tp_allreduce == "fused-flags":
-        ops.set_tuning(2, 1)                       # B200_TUNE_TP_PROTOCOL
+    if args.tp_allreduce.startswith("fused-"):     # B200_TUNE_TP_PROTOCOL
+        ops.set_tuning(2, {"flags": 1, "direct": 2, "summed": 3}[args.tp_allreduce[6:]])
 
     weights = make_decoder_weights(cfg, 1234, dev)
     max_seq = args.prompt + W + K + 8

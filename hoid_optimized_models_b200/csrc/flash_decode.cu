@@ -453,14 +453,15 @@ __global__ void __launch_bounds__(kFmThreads, 1) flash_decode_mma_kernel(FdArgs 
   const int split = blockIdx.x, kvh = blockIdx.y;
 
   pdl_launch_dependents();
-  pdl_wait();
 
-  const int kv_len = a.kv_len[0];
-  const int per = (kv_len + a.n_splits - 1) / a.n_splits;
-  const int k0 = split * per;
-  const int k1 = min(kv_len, k0 + per);
-  const int ntiles = k1 > k0 ? (k1 - k0 + kFmTile - 1) / kFmTile : 0;
-
+  int kv_len, k0, k1, ntiles;
+  auto slice = [&](int kvl) {
+    kv_len = kvl;
+    const int per = (kvl + a.n_splits - 1) / a.n_splits;
+    k0 = split * per;
+    k1 = min(kvl, k0 + per);
+    ntiles = k1 > k0 ? (k1 - k0 + kFmTile - 1) / kFmTile : 0;
+  };
   const uint16_t* kb = a.k + (size_t)kvh * a.head_stride;
   const uint16_t* vb = a.v + (size_t)kvh * a.head_stride;
   auto load_tile = [&](int t) {
@@ -476,10 +477,32 @@ __global__ void __launch_bounds__(kFmThreads, 1) flash_decode_mma_kernel(FdArgs 
       fm_cp16(sv + fm_swz<HD>(r, c), vb + off);
     }
   };
-  if (0 < ntiles) load_tile(0);
-  fm_commit();
-  if (1 < ntiles) load_tile(1);
-  fm_commit();
+  auto first_tiles = [&]() {
+    if (0 < ntiles) load_tile(0);
+    fm_commit();
+    if (1 < ntiles) load_tile(1);
+    fm_commit();
+  };
+  const volatile int* kvl_p = a.kv_len;
+  if (ROPE) {
+    // Cache rows of earlier positions never change during a step, so the first tiles are
+    // requested before the wait on the previous kernel, with the length as it reads now; the row
+    // this launch appends is patched in shared memory anyway.  If the length turns out to have
+    // been stale (possible only outside a replayed graph), the copies are simply issued again.
+    slice(kvl_p[0]);
+    first_tiles();
+    pdl_wait();
+    const int now = kvl_p[0];
+    if (now != kv_len) {                                 // CTA-uniform
+      fm_wait<0>();
+      slice(now);
+      first_tiles();
+    }
+  } else {
+    pdl_wait();
+    slice(kvl_p[0]);
+    first_tiles();
+  }
 
   // ---- q as A fragments: head g in rows g (high part) and g + 8 (low part) ----
   uint32_t qf[KS][4];

@@ -34,6 +34,7 @@ constexpr int kGemvWarps = kGemvThreads / 32;
 // Two inbox slots alternate by sequence parity: a rank can be at most one all-reduce ahead of
 // its slowest peer, because the next one needs that peer's contribution.
 constexpr int kTpMaxRanks = 8;
+constexpr int kTpReducers = 8;     // CTAs that sum the ranks' contributions (hierarchical mode)
 constexpr long long kTpWaitTicks = 4000000000LL;   // ~2 s: every wait on a peer is bounded
 struct TpLink {
   float* inbox[kTpMaxRanks];        // inbox of rank p (peer-mapped): [2 slots][world][H] fp32, or
@@ -43,6 +44,8 @@ struct TpLink {
   const int* seq_base;              // device scalar: sequence number of the step's first all-reduce
   int world, rank, H;
   int ll;                           // 1: tagged-pair protocol, 0: data + sequence flags
+  int hier;                         // tagged pairs: a few CTAs reduce, the others read their sums
+  uint4* xr;                        // local staging of the reduced vector: [2 slots][H] pairs
 };
 
 struct GemvArgs {
@@ -71,12 +74,54 @@ struct GemvArgs {
 
 constexpr int kMaxExpertSegs = 256;
 
+// B200_TUNE_TP_PROTOCOL: 0 default (tagged pairs; hierarchical above two ranks), 1 data + flags,
+// 2 tagged pairs read directly by every CTA, 3 tagged pairs through the reducer CTAs
+static void tp_apply_tuning(TpLink& l) {
+  const int t = g_tuning[B200_TUNE_TP_PROTOCOL];
+  if (t == 1) l.ll = 0;
+  else if (t == 2) l.hier = 0;
+  else if (t == 3) l.hier = 1;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
   uint4 v;
   asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
+}
+// Sum over n tagged-pair vectors (stride in uint4) of the float4 at q0: every 8-byte
+// {value, tag} pair arrives atomically, so the data itself is polled (bounded) - no flag, no fence.
+__device__ __forceinline__ float4 ll_reduce(const uint4* q0, int n, int stride, unsigned tag,
+                                            int* status) {
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  long long t0 = 0;
+  for (int r = 0; r < n; ++r) {
+    const uint4* q = q0 + (size_t)r * stride;
+    uint4 e0, e1;
+    int spins = 0;
+    while (true) {
+      e0 = ld_volatile_v4(q);
+      e1 = ld_volatile_v4(q + 1);
+      if (e0.y == tag && e0.w == tag && e1.y == tag && e1.w == tag) break;
+      if ((++spins & 63) == 0) {
+        // an earlier wait already gave up: do not spend the budget again
+        if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) break;
+        if (t0 == 0) t0 = clock64();
+        if (clock64() - t0 > kTpWaitTicks) {
+          if (status != nullptr) atomicExch(status, B200_ERR_TIMEOUT);
+          break;
+        }
+      }
+    }
+    v.x += __uint_as_float(e0.x); v.y += __uint_as_float(e0.z);
+    v.z += __uint_as_float(e1.x); v.w += __uint_as_float(e1.z);
+  }
+  return v;
+}
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ void st_volatile_v2(uint2* p, uint2 v) {
   asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
@@ -170,11 +215,12 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   // stage x (fp32, segment-swizzled: [seg][half][lane] float4) and zero the row partials
   float ss = 0.f, sm = 0.f;
   float4* xs4 = reinterpret_cast<float4*>(xs);
-  unsigned tp_slot = 0;
+  unsigned tp_slot = 0, tp_tag = 0;
   if (TP && a.tp_in >= 0) {
     // wait for every rank's contribution to all-reduce number seq (bounded, like every wait)
     const unsigned seq = (unsigned)(a.tp.seq_base[0] + a.tp_in);
     tp_slot = seq & 1u;
+    tp_tag = seq + 1u;
     if (!a.tp.ll) {
       if (tid < a.tp.world) {
         const volatile unsigned* f = a.tp.flags[a.tp.rank] + tp_slot * a.tp.world + tid;
@@ -195,36 +241,34 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
       __syncthreads();
     }
   }
+  if (TP && a.tp_in >= 0 && a.tp.ll && a.tp.hier) {
+    // A few CTAs sum the ranks' contributions, one slice each, and publish the sums locally as
+    // tagged pairs; every CTA then polls that one vector.  The inbox is read once per GPU instead
+    // of once per CTA (which costs world x 32 KB of L2 traffic per CTA).
+    const int nred = min(kTpReducers, (int)gridDim.x);
+    if ((int)blockIdx.x < nred) {
+      const int n4 = K >> 2, per = (n4 + nred - 1) / nred;
+      const int lo = blockIdx.x * per, hi = min(n4, lo + per);
+      const uint4* box = reinterpret_cast<const uint4*>(a.tp.inbox[a.tp.rank]) +
+                         (size_t)tp_slot * a.tp.world * (K >> 1);
+      uint4* dst = a.tp.xr + (size_t)tp_slot * (K >> 1);
+      for (int i = lo + tid; i < hi; i += kGemvThreads) {
+        const float4 v = ll_reduce(box + 2 * i, a.tp.world, K >> 1, tp_tag, a.status);
+        st_volatile_v4(dst + 2 * i, make_uint4(__float_as_uint(v.x), tp_tag, __float_as_uint(v.y), tp_tag));
+        st_volatile_v4(dst + 2 * i + 1, make_uint4(__float_as_uint(v.z), tp_tag, __float_as_uint(v.w), tp_tag));
+        if (a.x_out != nullptr) reinterpret_cast<float4*>(a.x_out)[i] = v;
+      }
+    }
+  }
   for (int i = tid; i < (K >> 2); i += kGemvThreads) {
     float4 v;
     if (TP && a.tp_in >= 0) {
       if (a.tp.ll) {
-        // every 8-byte {value, tag} pair arrives atomically: poll the data itself, no flag
-        const unsigned tag = (unsigned)(a.tp.seq_base[0] + a.tp_in) + 1u;
-        const uint4* box = reinterpret_cast<const uint4*>(a.tp.inbox[a.tp.rank]) +
-                           (size_t)tp_slot * a.tp.world * (K >> 1) + 2 * i;
-        v = make_float4(0.f, 0.f, 0.f, 0.f);
-        long long t0 = 0;
-        for (int r = 0; r < a.tp.world; ++r) {
-          const uint4* q = box + (size_t)r * (K >> 1);
-          uint4 e0, e1;
-          int spins = 0;
-          while (true) {
-            e0 = ld_volatile_v4(q);
-            e1 = ld_volatile_v4(q + 1);
-            if (e0.y == tag && e0.w == tag && e1.y == tag && e1.w == tag) break;
-            if ((++spins & 63) == 0) {
-              if (a.status != nullptr && *reinterpret_cast<volatile int*>(a.status) != 0) break;
-              if (t0 == 0) t0 = clock64();
-              if (clock64() - t0 > kTpWaitTicks) {
-                if (a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
-                break;
-              }
-            }
-          }
-          v.x += __uint_as_float(e0.x); v.y += __uint_as_float(e0.z);
-          v.z += __uint_as_float(e1.x); v.w += __uint_as_float(e1.z);
-        }
+        const uint4* src = a.tp.hier
+            ? a.tp.xr + (size_t)tp_slot * (K >> 1) + 2 * i
+            : reinterpret_cast<const uint4*>(a.tp.inbox[a.tp.rank]) +
+                  (size_t)tp_slot * a.tp.world * (K >> 1) + 2 * i;
+        v = ll_reduce(src, a.tp.hier ? 1 : a.tp.world, K >> 1, tp_tag, a.status);
       } else {
         const float4* box = reinterpret_cast<const float4*>(a.tp.inbox[a.tp.rank]) +
                             (size_t)tp_slot * a.tp.world * (K >> 2) + i;
@@ -234,7 +278,8 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
           v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
         }
       }
-      if (a.x_out != nullptr && blockIdx.x == 0) reinterpret_cast<float4*>(a.x_out)[i] = v;
+      if (a.x_out != nullptr && blockIdx.x == 0 && !(a.tp.ll && a.tp.hier))
+        reinterpret_cast<float4*>(a.x_out)[i] = v;
     } else if (a.x_dtype == B200_F32) {
       v = reinterpret_cast<const float4*>(a.x)[i];
     } else {
@@ -497,7 +542,7 @@ static int moe_down_impl(const b200::TpLink* link, int tp_out, int* status,
   if (link != nullptr) {
     if (hidden != link->H) return B200_ERR_SHAPE;
     a.tp = *link; a.tp_out = tp_out; a.status = status;
-    if (g_tuning[B200_TUNE_TP_PROTOCOL] == 1) a.tp.ll = 0;
+    tp_apply_tuning(a.tp);
     e = gemv_launch<8, 2, 2, true>(a, false, (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0);
   } else {
     e = gemv_launch<8, 2, 2>(a, false, (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0);
@@ -526,7 +571,7 @@ size_t tp_flag_bytes(int world) { return ((size_t)2 * world * 4 + kTpAlign - 1) 
 /* Bytes of the per-rank communication buffer: [flags | arrival counter + seq_base | inbox]. */
 extern "C" int64_t b200_tp_buffer_bytes(int world, int H) {
   if (world <= 0 || world > kTpMaxRanks || H <= 0) return 0;
-  return (int64_t)(tp_flag_bytes(world) + kTpAlign + (size_t)2 * world * H * 8);
+  return (int64_t)(tp_flag_bytes(world) + kTpAlign + (size_t)2 * world * H * 8 + (size_t)2 * H * 8);
 }
 
 /* cudaMalloc + zero the communication buffer (set-up time only) and return its IPC handle. */
@@ -569,6 +614,8 @@ extern "C" int b200_tp_create(void* const* bufs, int world, int rank, int H) {
   l.local_counter = (int*)own;
   l.seq_base = (const int*)(own + 64);
   l.world = world; l.rank = rank; l.H = H; l.ll = 1;
+  l.hier = world > 2;
+  l.xr = (uint4*)((char*)l.inbox[rank] + (size_t)2 * world * H * 8);
   g_tp[id].local = bufs[rank];
   g_tp[id].used = true;
   return id;
@@ -615,7 +662,7 @@ extern "C" int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, i
   a.expert_lo = 0; a.n_local = 0;
   a.tp = l; a.tp_in = tp_in; a.tp_out = tp_out;
   a.x_out = (float*)x_out; a.status = status;
-  if (g_tuning[B200_TUNE_TP_PROTOCOL] == 1) a.tp.ll = 0;     // data + sequence flags
+  tp_apply_tuning(a.tp);
   cudaError_t e = gemv_launch<8, 2, 0, true>(a, epilogue == B200_EPI_SWIGLU, (cudaStream_t)stream,
                                     (flags & B200_FLAG_PDL) != 0);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;

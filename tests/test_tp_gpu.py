@@ -41,8 +41,10 @@ def _worker(rank, size, port, moe, fused, out):
         from hoid_optimized_models_b200 import ops
         from hoid_optimized_models_b200.decoder import DenseDecoder
         from hoid_optimized_models_b200.weights import make_decoder_weights
-        if fused == "flags":
-            ops.set_tuning(2, 1)                    # B200_TUNE_TP_PROTOCOL: data + sequence flags
+        # B200_TUNE_TP_PROTOCOL: 1 data + sequence flags, 3 tagged pairs summed by a few CTAs
+        # (the default above two ranks)
+        if fused in ("flags", "summed"):
+            ops.set_tuning(2, 1 if fused == "flags" else 3)
         cfg = _cfg(moe)
         w = make_decoder_weights(cfg, 21)
         ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(21)).to(dev)
@@ -66,9 +68,10 @@ def _worker(rank, size, port, moe, fused, out):
         os._exit(0)
 
 
-@pytest.mark.parametrize("moe,fused", [(False, "pairs"), (False, "flags"), (False, ""), (True, "pairs"), (True, "")],
-                         ids=["dense-fused-pairs", "dense-fused-flags", "dense-nccl",
-                              "moe-fused-pairs", "moe-nccl"])
+@pytest.mark.parametrize("moe,fused", [(False, "pairs"), (False, "summed"), (False, "flags"), (False, ""),
+                                       (True, "pairs"), (True, "summed"), (True, "")],
+                         ids=["dense-fused-pairs", "dense-fused-summed", "dense-fused-flags",
+                              "dense-nccl", "moe-fused-pairs", "moe-fused-summed", "moe-nccl"])
 def test_two_ranks_match_one(dev, moe, fused):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
