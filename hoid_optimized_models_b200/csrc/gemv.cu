@@ -74,7 +74,7 @@ struct GemvArgs {
 
 constexpr int kMaxExpertSegs = 256;
 
-// B200_TUNE_TP_PROTOCOL: 0 default (tagged pairs; hierarchical above two ranks), 1 data + flags,
+// B200_TUNE_TP_PROTOCOL: 0 default (tagged pairs summed by a few reducer CTAs), 1 data + flags,
 // 2 tagged pairs read directly by every CTA, 3 tagged pairs through the reducer CTAs
 static void tp_apply_tuning(TpLink& l) {
   const int t = g_tuning[B200_TUNE_TP_PROTOCOL];
@@ -614,7 +614,7 @@ extern "C" int b200_tp_create(void* const* bufs, int world, int rank, int H) {
   l.local_counter = (int*)own;
   l.seq_base = (const int*)(own + 64);
   l.world = world; l.rank = rank; l.H = H; l.ll = 1;
-  l.hier = world > 2;
+  l.hier = 1;
   l.xr = (uint4*)((char*)l.inbox[rank] + (size_t)2 * world * H * 8);
   g_tp[id].local = bufs[rank];
   g_tp[id].used = true;

@@ -129,7 +129,9 @@ class DenseDecoder:
         self.cand = f32(2)
         self.cand_all = f32(tp_size, 2)
         if n_splits is None:
-            n_splits = max(1, min(148 // self.n_kv, (max_seq + 63) // 64))  # ~one CTA per SM
+            # about one CTA per SM, at least one 128-key tile per split, and at most 36 splits:
+            # beyond that the merge of the splits' records costs more than shorter slices save
+            n_splits = max(1, min(148 // self.n_kv, (max_seq + 127) // 128, 36))
         self.n_splits = n_splits
         self.fd_ws = ops.flash_decode_workspace(self.n_q, self.n_kv, hd, n_splits, dev)
         self.am_ws = ops.argmax_workspace(dev)
