@@ -176,6 +176,8 @@ def run_secondary(args):
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     ops.set_pdl(not args.no_pdl)
+    for kv in args.tune:
+        ops.set_tuning(*(int(t) for t in kv.split("=")))
     if args.tp_allreduce.startswith("fused-"):     # B200_TUNE_TP_PROTOCOL
         ops.set_tuning(2, {"flags": 1, "direct": 2, "summed": 3}[args.tp_allreduce[6:]])
     peak, peak_kind = measured_peaks()
@@ -306,6 +308,8 @@ def main():
                          "data + sequence flags), or NCCL calls")
     ap.add_argument("--workload", default="llama-3.1-8b",
                     help="llama-3.1-8b (headline) | qwen3-4b | qwen3-30b-a3b | xlm-roberta-large | whisper-large-v3")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="kernel tuning knob (B200_TUNE_* key number = value), repeatable")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: random KV cache instead of a prefill, decode timing only")
     args = ap.parse_args()
@@ -357,6 +361,8 @@ def main():
     from hoid_optimized_models_b200.decoder import Llama31Optimized
     from hoid_optimized_models_b200.weights import make_decoder_weights
     ops.set_pdl(not args.no_pdl)
+    for kv in args.tune:
+        ops.set_tuning(*(int(t) for t in kv.split("=")))
     if args.tp_allreduce.startswith("fused-"):     # B200_TUNE_TP_PROTOCOL
         ops.set_tuning(2, {"flags": 1, "direct": 2, "summed": 3}[args.tp_allreduce[6:]])
 

@@ -68,6 +68,7 @@ struct GemvArgs {
   // tensor-parallel fusion (see the comment above tp_consume / tp_publish)
   TpLink tp;
   int tp_in, tp_out;         // sequence offsets of the all-reduce to consume / to feed (-1 = none)
+  int norm_in_smem;          // RMSNorm: 1 = normalise the staged vector, 0 = scale the row sums
   float* x_out;              // consumer: CTA 0 stores the reduced vector here (nullable)
   int* status;
 };
@@ -215,6 +216,7 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   // stage x (fp32, segment-swizzled: [seg][half][lane] float4) and zero the row partials
   float ss = 0.f, sm = 0.f;
   float4* xs4 = reinterpret_cast<float4*>(xs);
+  const bool rms_deferred = a.norm_w != nullptr && a.norm_b == nullptr && !a.norm_in_smem;
   unsigned tp_slot = 0, tp_tag = 0;
   if (TP && a.tp_in >= 0) {
     // wait for every rank's contribution to all-reduce number seq (bounded, like every wait)
@@ -288,9 +290,16 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
     }
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     sm += (v.x + v.y) + (v.z + v.w);
+    if (rms_deferred) {
+      // rmsnorm(x) = (x * w) * rsqrt(mean(x^2) + eps): stage x * w now, the scalar multiplies the
+      // row sums in the epilogue, so nothing waits for the sum of squares before the weight loop
+      const uint2 u = reinterpret_cast<const uint2*>(a.norm_w)[i];
+      v.x *= bf16lo(u.x); v.y *= bf16hi(u.x); v.z *= bf16lo(u.y); v.w *= bf16hi(u.y);
+    }
     const int k = i << 2, seg = k >> 8, within = k & 255;
     xs4[seg * 64 + ((within >> 2) & 1) * 32 + (within >> 3)] = v;
   }
+  float out_scale = 1.f;
   for (int i = tid; i < a.rpc * kGemvWarps; i += kGemvThreads) part[i] = 0.f;
   if (a.norm_w != nullptr && a.norm_b != nullptr) {
     // LayerNorm prologue: two-pass statistics over the staged vector, like the stand-alone kernel
@@ -315,6 +324,8 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
       v.w = (v.w - mean) * scale * bf16hi(g.y) + bf16hi(b.y);
       xs4[si] = v;
     }
+  } else if (rms_deferred) {
+    out_scale = rsqrtf(block_sum(ss, red) / (float)K + a.eps);   // its barriers also publish xs
   } else if (a.norm_w != nullptr) {
     const float tot = block_sum(ss, red);
     const float scale = rsqrtf(tot / (float)K + a.eps);
@@ -372,6 +383,7 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
     float v = 0.f;
 #pragma unroll
     for (int i = 0; i < kGemvWarps; ++i) v += part[r * kGemvWarps + i];
+    v *= out_scale;
     if (a.bias != nullptr) v += __uint_as_float((uint32_t)a.bias[r0 + r] << 16);
     return v;
   };
@@ -470,6 +482,7 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   if (K > 32768) return B200_ERR_SHAPE;
 
   GemvArgs a{};
+  a.norm_in_smem = g_tuning[B200_TUNE_GEMV_NORM] == 1;
   a.x = x; a.w = (const uint16_t*)w; a.y = y;
   a.norm_w = (const uint16_t*)norm_w; a.norm_b = (const uint16_t*)norm_beta;
   a.bias = (const uint16_t*)bias; a.resid = resid;
@@ -504,6 +517,7 @@ extern "C" int b200_moe_decode_gate_up(void* act, const void* x, int x_dtype, co
     return B200_ERR_SHAPE;
   if (((uintptr_t)w_gu & 15) != 0 || ((uintptr_t)x & 15) != 0) return B200_ERR_ALIGN;
   GemvArgs a{};
+  a.norm_in_smem = g_tuning[B200_TUNE_GEMV_NORM] == 1;
   a.x = x; a.w = (const uint16_t*)w_gu; a.y = act; a.norm_w = (const uint16_t*)norm_w;
   a.bias = nullptr; a.resid = nullptr;
   a.K = hidden; a.N = 2 * inter; a.ldw = hidden; a.rpc = 0;
@@ -530,6 +544,7 @@ static int moe_down_impl(const b200::TpLink* link, int tp_out, int* status,
   if (top_k * segs > kMaxExpertSegs || (long)top_k * inter > 32768) return B200_ERR_SHAPE;
   if (((uintptr_t)w_down & 15) != 0 || ((uintptr_t)act & 15) != 0) return B200_ERR_ALIGN;
   GemvArgs a{};
+  a.norm_in_smem = g_tuning[B200_TUNE_GEMV_NORM] == 1;
   a.x = act; a.w = (const uint16_t*)w_down; a.y = y; a.norm_w = nullptr; a.bias = nullptr;
   a.resid = resid;
   a.K = top_k * inter; a.N = hidden; a.ldw = inter; a.rpc = 0;
@@ -653,6 +668,7 @@ extern "C" int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, i
     return B200_ERR_SHAPE;
   if (epilogue == B200_EPI_SWIGLU && ((N & 1) != 0 || resid != nullptr)) return B200_ERR_SHAPE;
   GemvArgs a{};
+  a.norm_in_smem = g_tuning[B200_TUNE_GEMV_NORM] == 1;
   a.x = x; a.w = (const uint16_t*)w; a.y = y;
   a.norm_w = (const uint16_t*)norm_w; a.bias = (const uint16_t*)bias; a.resid = resid;
   a.K = K; a.N = N; a.ldw = ldw; a.rpc = 0;

@@ -59,7 +59,8 @@ int b200_version(void);
 enum { B200_TUNE_GEMV = 0, B200_TUNE_GEMM_BN = 1 /* force the GEMM tile width: 256 / 128 / 64 */,
        B200_TUNE_TP_PROTOCOL = 2 /* fused all-reduce: 0 tagged pairs summed by a few CTAs, 1 data +
                                     sequence flags, 2 tagged pairs read directly by every CTA */,
-       B200_TUNE_FLASH_DECODE = 3 /* decode attention: 0 tensor-core kernel, 1 SIMT kernel */ };
+       B200_TUNE_FLASH_DECODE = 3 /* decode attention: 0 tensor-core kernel, 1 SIMT kernel */,
+       B200_TUNE_GEMV_NORM = 4 /* RMSNorm prologue: 0 scale the row sums, 1 normalise x in smem */ };
 int b200_set_tuning(int key, int value);
 /* Number of SMs the library sizes its grids for (148 on B200). */
 int b200_sm_count(void);
