@@ -40,6 +40,7 @@ SIGNATURES = {
     "b200_tp_advance": (_i, [_i, _i, _i, _p]),
     "b200_gemv_bf16_tp": (_i, [_p, _p, _p, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p]),
     "b200_moe_decode_down_tp": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _p, _i, _p]),
+    "b200_moe_router_gemv": (_i, [_p, _p, _p, _p, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p]),
     "b200_add_rmsnorm": (_i, [_p, _p, _i, _p, _i, _p, _i, _p, _i, _i, _f, _i, _p]),
     "b200_add_layernorm": (_i, [_p, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _f, _i, _p]),
     "b200_qk_rope_cache": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,

@@ -11,28 +11,13 @@ namespace b200 {
 // owns experts l, l + 32, ...
 constexpr int kMaxEPL = 8;  // experts per lane -> E <= 256
 
-__global__ void __launch_bounds__(128) moe_router_kernel(int* ids, float* wts, const void* logits,
-                                                         int logits_dtype, int s, int E, int top_k,
-                                                         int round_bf16) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (t >= s) return;
-  const int epl = E >> 5;
-  float v[kMaxEPL];
+// Softmax + top-k of one token's logits by one warp: v[j] is the logit of expert lane + 32 j
+// (-inf beyond E).  Shared by the stand-alone router and the fused router GEMV.
+__device__ __forceinline__ void router_select(const float* v, int epl, int top_k, int round_bf16,
+                                              int lane, int* ids, float* wts) {
   float mx = -INFINITY;
 #pragma unroll
-  for (int j = 0; j < kMaxEPL; ++j) {
-    v[j] = -INFINITY;
-    if (j < epl) {
-      const size_t i = (size_t)t * E + lane + 32 * j;
-      v[j] = logits_dtype == B200_F32
-                 ? reinterpret_cast<const float*>(logits)[i]
-                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[i]);
-      mx = fmaxf(mx, v[j]);
-    }
-  }
+  for (int j = 0; j < kMaxEPL; ++j) mx = fmaxf(mx, v[j]);
   mx = warp_max(mx);
   float p[kMaxEPL];
   float sum = 0.f;
@@ -74,8 +59,88 @@ __global__ void __launch_bounds__(128) moe_router_kernel(int* ids, float* wts, c
   if (lane < top_k) {
     float w = wsum > 0.f ? sel_w / wsum : 0.f;
     if (round_bf16) w = __bfloat162float(__float2bfloat16(w));
-    ids[(size_t)t * top_k + lane] = sel_i;
-    wts[(size_t)t * top_k + lane] = w;
+    ids[lane] = sel_i;
+    wts[lane] = w;
+  }
+}
+
+__global__ void __launch_bounds__(128) moe_router_kernel(int* ids, float* wts, const void* logits,
+                                                         int logits_dtype, int s, int E, int top_k,
+                                                         int round_bf16) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= s) return;
+  const int epl = E >> 5;
+  float v[kMaxEPL];
+#pragma unroll
+  for (int j = 0; j < kMaxEPL; ++j) {
+    v[j] = -INFINITY;
+    if (j < epl) {
+      const size_t i = (size_t)t * E + lane + 32 * j;
+      v[j] = logits_dtype == B200_F32
+                 ? reinterpret_cast<const float*>(logits)[i]
+                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[i]);
+    }
+  }
+  router_select(v, epl, top_k, round_bf16, lane, ids + (size_t)t * top_k, wts + (size_t)t * top_k);
+}
+
+// Decode-time router in one launch: logits = W_router . rmsnorm(x) (one warp per expert row),
+// then the CTA that arrives last runs the selection above on the finished logits.
+constexpr int kRgWarps = 8;
+__global__ void __launch_bounds__(kRgWarps * 32) moe_router_gemv_kernel(
+    int* ids, float* wts, float* logits, int* counter, const float* x, const uint16_t* norm_w,
+    float eps, const uint16_t* w, int E, int H, int top_k, int round_bf16) {
+  extern __shared__ __align__(16) float rg_x[];      // H floats: x * norm_w
+  __shared__ float red[32];
+  __shared__ int s_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  float ss = 0.f;
+  for (int i = tid; i < (H >> 2); i += kRgWarps * 32) {
+    float4 v = reinterpret_cast<const float4*>(x)[i];
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (norm_w != nullptr) {
+      const uint2 u = reinterpret_cast<const uint2*>(norm_w)[i];
+      v.x *= bf16lo(u.x); v.y *= bf16hi(u.x); v.z *= bf16lo(u.y); v.w *= bf16hi(u.y);
+    }
+    reinterpret_cast<float4*>(rg_x)[i] = v;
+  }
+  const float tot = block_sum(ss, red);              // its barriers also publish rg_x
+  const float scale = norm_w != nullptr ? rsqrtf(tot / (float)H + eps) : 1.f;
+  const int row = blockIdx.x * kRgWarps + warp;
+  if (row < E) {
+    const uint16_t* wr = w + (size_t)row * H;
+    float acc = 0.f;
+    for (int c = lane; c < (H >> 3); c += 32) {       // 8 weights per step
+      float f[8];
+      unpack8(ldg_stream(wr + c * 8), f);
+      const float4 a = reinterpret_cast<const float4*>(rg_x)[2 * c];
+      const float4 b = reinterpret_cast<const float4*>(rg_x)[2 * c + 1];
+      acc = fmaf(f[0], a.x, acc); acc = fmaf(f[1], a.y, acc);
+      acc = fmaf(f[2], a.z, acc); acc = fmaf(f[3], a.w, acc);
+      acc = fmaf(f[4], b.x, acc); acc = fmaf(f[5], b.y, acc);
+      acc = fmaf(f[6], b.z, acc); acc = fmaf(f[7], b.w, acc);
+    }
+    acc = warp_sum(acc) * scale;
+    if (lane == 0) logits[row] = acc;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = (atomicAdd(counter, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (warp == 0) {
+    const int epl = E >> 5;
+    float v[kMaxEPL];
+#pragma unroll
+    for (int j = 0; j < kMaxEPL; ++j) v[j] = j < epl ? __ldcg(logits + lane + 32 * j) : -INFINITY;
+    router_select(v, epl, top_k, round_bf16, lane, ids, wts);
+    if (lane == 0) *counter = 0;                     // ready for the next launch
   }
 }
 
@@ -205,6 +270,23 @@ extern "C" int b200_moe_router(int* ids, float* wts, const void* logits, int log
   cudaError_t e = launch(moe_router_kernel, dim3((s + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
                          (flags & B200_FLAG_PDL) != 0, ids, wts, logits, logits_dtype, s, E, top_k,
                          round_bf16);
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+extern "C" int b200_moe_router_gemv(int* ids, float* wts, float* logits, int* counter,
+                                    const float* x, const void* norm_w, float eps,
+                                    const void* w_router, int E, int H, int top_k, int round_bf16,
+                                    int flags, b200_stream_t stream) {
+  if (!ids || !wts || !logits || !counter || !x || !w_router) return B200_ERR_ARG;
+  if (E <= 0 || (E & 31) != 0 || E > 32 * kMaxEPL || top_k <= 0 || top_k > 32 || top_k > E ||
+      H <= 0 || (H & 7) != 0 || H > 12288)
+    return B200_ERR_SHAPE;
+  if (((uintptr_t)x & 15) != 0 || ((uintptr_t)w_router & 15) != 0) return B200_ERR_ALIGN;
+  const int grid = (E + kRgWarps - 1) / kRgWarps;
+  cudaError_t e = launch(moe_router_gemv_kernel, dim3(grid), dim3(kRgWarps * 32), (size_t)H * 4,
+                         (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0, ids, wts, logits,
+                         counter, x, (const uint16_t*)norm_w, eps, (const uint16_t*)w_router, E, H,
+                         top_k, round_bf16);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 

@@ -321,6 +321,24 @@ def moe_router(ids: Tensor, wts: Tensor, logits: Tensor, round_bf16: bool = Fals
                                      1 if round_bf16 else 0, _flags(), _stream()), "b200_moe_router")
 
 
+@torch.library.custom_op("b200::moe_router_gemv", mutates_args=("ids", "wts", "logits", "counter"))
+def moe_router_gemv(ids: Tensor, wts: Tensor, logits: Tensor, counter: Tensor, x: Tensor,
+                    w_router: Tensor, norm_w: Optional[Tensor] = None, eps: float = 0.0,
+                    round_bf16: bool = False) -> None:
+    """Decode-time router in one launch: logits = w_router . rmsnorm(x), then top-k as moe_router.
+    counter is one int32 that is zero before the first call."""
+    _bf16(w_router, "w_router"); _bf16(norm_w, "norm_w")
+    if x.dtype != torch.float32 or logits.dtype != torch.float32:
+        raise TypeError("x and logits must be float32")
+    if ids.dtype != torch.int32 or wts.dtype != torch.float32 or counter.dtype != torch.int32:
+        raise TypeError("ids / counter must be int32 and wts float32")
+    E, H = w_router.shape
+    check(_lib.lib().b200_moe_router_gemv(
+        _ptr(ids), _ptr(wts), _ptr(logits), _ptr(counter), _ptr(x), _ptr(norm_w), eps,
+        _ptr(w_router), E, H, ids.numel(), 1 if round_bf16 else 0, _flags(), _stream()),
+        "b200_moe_router_gemv")
+
+
 def moe_permute_workspace(pairs: int, E: int, device) -> Tensor:
     n = _lib.lib().b200_moe_permute_workspace_bytes(pairs, E)
     return torch.zeros((n + 3) // 4, dtype=torch.int32, device=device)

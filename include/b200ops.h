@@ -301,6 +301,14 @@ int b200_flash_prefill_tc(void* out, const void* q, const void* k, const void* v
  */
 int b200_moe_router(int* ids, float* wts, const void* logits, int logits_dtype, int s, int E,
                     int top_k, int round_bf16, int flags, b200_stream_t stream);
+/* Decode-time router in one launch: logits[E] = W_router[E, H] . rmsnorm(x) * norm_w (fp32 x,
+ * bf16 weights), then the selection of b200_moe_router on those logits by the CTA that arrives
+ * last.  counter: one device int32, zero before the first call (the kernel leaves it zero).
+ * Reference: the router GEMV + moe_router_parallel_topk_k pair of the decode step,
+ * models/qwen3-30b-a3b/qwen3_optimized.py:478-482.  H % 8 == 0, H <= 12288. */
+int b200_moe_router_gemv(int* ids, float* wts, float* logits, int* counter, const float* x,
+                         const void* norm_w, float eps, const void* w_router, int E, int H,
+                         int top_k, int round_bf16, int flags, b200_stream_t stream);
 
 /* a11. Expert-major permutation of the s * top_k (token, slot) pairs: a stable counting sort
  * by expert id, identical to torch.argsort(ids.flatten(), stable=True).

@@ -42,6 +42,38 @@ def test_router_matches_torch_topk(dev, s, E, k):
     assert rel_err(w.cpu()[ok], bf(w_ref2).float()[ok]) < 1e-2
 
 
+@pytest.mark.parametrize("E,H,k,norm", [(128, 2048, 8, True), (128, 2048, 8, False), (32, 4096, 4, True),
+                                          (256, 1024, 2, True)])
+def test_router_gemv_one_launch(dev, E, H, k, norm):
+    """Router GEMV + selection in one launch: logits against an fp32 reference, and the selection
+    bit-exact against the stand-alone router fed with the very logits the kernel produced."""
+    from hoid_optimized_models_b200 import ops
+    from oracle.ref_decoder import rmsnorm, moe_route
+    g = torch.Generator().manual_seed(E + H)
+    x = torch.randn(H, generator=g)
+    w = bf(torch.randn(E, H, generator=g) * 0.05)
+    nw = bf(1 + 0.1 * torch.randn(H, generator=g)) if norm else None
+    xin = rmsnorm(x, nw.float(), 1e-6) if norm else x
+    ref = w.float() @ xin
+    ids = torch.zeros(k, dtype=torch.int32, device=dev)
+    wt = torch.zeros(k, dtype=torch.float32, device=dev)
+    logits = torch.zeros(E, dtype=torch.float32, device=dev)
+    ctr = torch.zeros(1, dtype=torch.int32, device=dev)
+    for _ in range(2):                                   # the counter must come back to zero
+        logits.zero_()
+        ops.moe_router_gemv(ids, wt, logits, ctr, x.to(dev), w.to(dev),
+                            norm_w=nw.to(dev) if norm else None, eps=1e-6)
+        assert rel_err(logits, ref) < 1e-5
+        ids2 = torch.zeros(1, k, dtype=torch.int32, device=dev)
+        wt2 = torch.zeros(1, k, dtype=torch.float32, device=dev)
+        ops.moe_router(ids2, wt2, logits.view(1, E).clone())
+        assert torch.equal(ids.cpu(), ids2.cpu().view(-1))
+        assert torch.equal(wt.cpu(), wt2.cpu().view(-1))
+        assert int(ctr.item()) == 0
+    ids_ref, _ = moe_route(logits.cpu().view(1, E), k)
+    assert torch.equal(ids.cpu().long(), ids_ref.view(-1))
+
+
 def test_router_tie_break_is_lowest_index(dev):
     from hoid_optimized_models_b200 import ops
     logits = torch.zeros(2, 128)
