@@ -25,14 +25,20 @@ constexpr int kGemvWarps = kGemvThreads / 32;
 // ---------------------------------------------------------------------------------------------
 // All-reduce fused into the GEMVs of a tensor-parallel decode step (one process per GPU, peer
 // memory over NVLink, no collective library call):
-//   * a row-parallel GEMV (o_proj, down_proj) does not write y.  Its CTAs store their partial
-//     rows into slot `rank` of EVERY rank's inbox with plain peer stores; the CTA that finishes
-//     last publishes the sequence number with a system-scope release store to every rank;
-//   * the NEXT GEMV on each rank waits (bounded) until all ranks' sequence numbers have arrived,
-//     and stages x = sum over ranks of inbox[rank] in rank order while it would have staged x
-//     anyway.  Every rank adds the same values in the same order, so all ranks stay bit-identical.
+//   * a row-parallel GEMV (o_proj, down_proj, the expert down projection) does not write y.
+//     Each finished row of its partial sum goes into slot `rank` of EVERY rank's inbox as an
+//     8-byte {fp32 value, sequence tag} pair with one 8-byte peer store: the pair arrives
+//     atomically, so the data validates itself and no fence, flag or counter is needed;
+//   * the NEXT GEMV on each rank consumes it while it stages its input vector anyway: a few
+//     reducer CTAs poll (bounded) the ranks' pairs of their slice, add them in rank order and
+//     publish the sum locally as tagged pairs again; all CTAs poll that one vector.  Every rank
+//     adds the same values in the same order, so all ranks stay bit-identical.
 // Two inbox slots alternate by sequence parity: a rank can be at most one all-reduce ahead of
 // its slowest peer, because the next one needs that peer's contribution.
+// Two measured alternatives stay selectable (B200_TUNE_TP_PROTOCOL): every CTA summing the inboxes
+// itself (world x 32 KB of L2 reads per CTA), and plain stores followed by a system fence and one
+// release flag per rank (slower than a collective library: the fence waits out the NVLink round
+// trip).
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpReducers = 8;     // CTAs that sum the ranks' contributions (hierarchical mode)
 constexpr long long kTpWaitTicks = 4000000000LL;   // ~2 s: every wait on a peer is bounded

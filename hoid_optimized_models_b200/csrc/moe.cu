@@ -98,6 +98,17 @@ __global__ void __launch_bounds__(kRgWarps * 32) moe_router_gemv_kernel(
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_launch_dependents();
+  // the router weights do not depend on the previous kernel: the first 4 KB of the warp's row
+  // (all of it for H <= 2048) is requested before the wait, eight loads in flight per lane
+  const int row = blockIdx.x * kRgWarps + warp;
+  const int nchunk = H >> 3;                          // 16-byte chunks per row
+  const uint16_t* wr = w + (size_t)(row < E ? row : 0) * H;
+  uint4 wv[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = j * 32 + lane;
+    wv[j] = c < nchunk ? ldg_stream(wr + c * 8) : make_uint4(0, 0, 0, 0);
+  }
   pdl_wait();
   float ss = 0.f;
   for (int i = tid; i < (H >> 2); i += kRgWarps * 32) {
@@ -111,19 +122,34 @@ __global__ void __launch_bounds__(kRgWarps * 32) moe_router_gemv_kernel(
   }
   const float tot = block_sum(ss, red);              // its barriers also publish rg_x
   const float scale = norm_w != nullptr ? rsqrtf(tot / (float)H + eps) : 1.f;
-  const int row = blockIdx.x * kRgWarps + warp;
   if (row < E) {
-    const uint16_t* wr = w + (size_t)row * H;
     float acc = 0.f;
-    for (int c = lane; c < (H >> 3); c += 32) {       // 8 weights per step
+    auto fma8 = [&](const uint4& wq, int c) {
       float f[8];
-      unpack8(ldg_stream(wr + c * 8), f);
+      unpack8(wq, f);
       const float4 a = reinterpret_cast<const float4*>(rg_x)[2 * c];
       const float4 b = reinterpret_cast<const float4*>(rg_x)[2 * c + 1];
       acc = fmaf(f[0], a.x, acc); acc = fmaf(f[1], a.y, acc);
       acc = fmaf(f[2], a.z, acc); acc = fmaf(f[3], a.w, acc);
       acc = fmaf(f[4], b.x, acc); acc = fmaf(f[5], b.y, acc);
       acc = fmaf(f[6], b.z, acc); acc = fmaf(f[7], b.w, acc);
+    };
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = j * 32 + lane;
+      if (c < nchunk) fma8(wv[j], c);
+    }
+    for (int c0 = 256; c0 < nchunk; c0 += 256) {      // rows longer than 4 KB
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = c0 + j * 32 + lane;
+        wv[j] = c < nchunk ? ldg_stream(wr + c * 8) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = c0 + j * 32 + lane;
+        if (c < nchunk) fma8(wv[j], c);
+      }
     }
     acc = warp_sum(acc) * scale;
     if (lane == 0) logits[row] = acc;

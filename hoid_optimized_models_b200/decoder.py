@@ -144,7 +144,8 @@ class DenseDecoder:
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.fuse_rope = fuse_rope
-        self.launches_per_step = 1 + ((7 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
+        self.launches_per_step = (1 + ((7 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
+                                  + (1 if self.link is not None else 0))   # + sequence advance
 
     # ------------------------------------------------------------------ collectives
     def _all_reduce(self, t: torch.Tensor) -> None:

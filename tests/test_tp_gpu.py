@@ -111,3 +111,70 @@ def test_two_ranks_match_one(dev, moe, fused):
     full = torch.tensor(res[0][2]) if moe else torch.cat([torch.tensor(r[2]) for r in res])
     err = float((full - logits_ref).abs().max() / logits_ref.abs().max())
     assert err < 1e-2, err
+
+
+def _dp_worker(rank, size, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=size, device_id=dev)
+    try:
+        from hoid_optimized_models_b200.encoder import XlmrEncoder
+        from hoid_optimized_models_b200.weights import make_encoder_weights
+        cfg, B, S, ids = _enc_case()
+        eng = XlmrEncoder(cfg, make_encoder_weights(cfg, 31), batch=B, seq=S, device=dev,
+                          dp_rank=rank, dp_size=size, group=dist.group.WORLD)
+        per = B // size
+        emb = eng.embed(ids[rank * per:(rank + 1) * per].to(dev))
+        out.put((rank, emb.float().cpu().tolist()))
+        out.close()
+        out.join_thread()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        os._exit(0)
+
+
+def _enc_case():
+    from hoid_optimized_models_b200.configs import XLMR_LARGE
+    cfg = replace(XLMR_LARGE, name="xlmr-dp-test", layers=2, vocab=4096)
+    B, S = 4, 128
+    ids = torch.randint(3, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(31))
+    return cfg, B, S, ids
+
+
+def test_encoder_data_parallel_matches_one_rank(dev):
+    """Batch split over two ranks + all-gather of the pooled rows against the one-rank encoder."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from hoid_optimized_models_b200.encoder import XlmrEncoder
+    from hoid_optimized_models_b200.weights import make_encoder_weights
+    cfg, B, S, ids = _enc_case()
+    ref = XlmrEncoder(cfg, make_encoder_weights(cfg, 31), batch=B, seq=S, device=dev)
+    emb_ref = ref.embed(ids.to(dev)).float().cpu()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res, waited = [], 0
+    while len(res) < len(procs):
+        try:
+            res.append(out.get(timeout=5))
+        except Exception:                                    # queue.Empty
+            waited += 5
+            if [p.exitcode for p in procs if p.exitcode not in (None, 0)] or waited > 300:
+                for p in procs:
+                    if p.is_alive():
+                        p.kill()
+                pytest.fail(f"rank exit codes {[p.exitcode for p in procs]} after {waited} s")
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, emb in res:                                    # every rank holds the whole batch
+        err = float((torch.tensor(emb) - emb_ref).abs().max())
+        assert err < 1e-3, (rank, err)
