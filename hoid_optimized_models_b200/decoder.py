@@ -125,7 +125,6 @@ class DenseDecoder:
             self.router_logits = f32(cfg.n_experts)
             self.topk_ids = torch.zeros(cfg.top_k, dtype=torch.int32, device=dev)
             self.topk_w = f32(cfg.top_k)
-            self.router_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
         self.logits = f32(self.vocab_local)
         self.cand = f32(2)
         self.cand_all = f32(tp_size, 2)
@@ -144,7 +143,7 @@ class DenseDecoder:
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.fuse_rope = fuse_rope
-        self.launches_per_step = (1 + ((7 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
+        self.launches_per_step = (1 + ((8 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
                                   + (1 if self.link is not None else 0))   # + sequence advance
 
     # ------------------------------------------------------------------ collectives
@@ -194,8 +193,8 @@ class DenseDecoder:
             else:
                 ops.gemv(h, self.attn, self.wo[i], resid=h)
             if self.moe:
-                ops.moe_router_gemv(self.topk_ids, self.topk_w, self.router_logits, self.router_ctr,
-                                    h, self.w_router[i], norm_w=self.ln2[i], eps=cfg.eps)
+                ops.gemv(self.router_logits, h, self.w_router[i], norm_w=self.ln2[i], eps=cfg.eps)
+                ops.moe_router(self.topk_ids, self.topk_w, self.router_logits.view(1, -1))
                 ops.moe_decode_gate_up(self.act, h, self.wgu[i], self.topk_ids, self.topk_w,
                                        norm_w=self.ln2[i], eps=cfg.eps,
                                        expert_lo=self.expert_lo)
@@ -276,8 +275,8 @@ class DenseDecoder:
                     collect.append(h.clone())
             self._attend(i)
             ops.gemv(h, self.attn, self.wo[i], resid=h)
-            ops.moe_router_gemv(self.topk_ids, self.topk_w, self.router_logits, self.router_ctr, h,
-                                self.w_router[i], norm_w=self.ln2[i], eps=cfg.eps)
+            ops.gemv(self.router_logits, h, self.w_router[i], norm_w=self.ln2[i], eps=cfg.eps)
+            ops.moe_router(self.topk_ids, self.topk_w, self.router_logits.view(1, -1))
             ops.moe_decode_gate_up(self.act, h, self.wgu[i], self.topk_ids, self.topk_w,
                                    norm_w=self.ln2[i], eps=cfg.eps, expert_lo=self.expert_lo)
             ops.moe_decode_down_tp_publish(self.act, self.wd[i], self.topk_ids, ctx, i,
