@@ -345,7 +345,7 @@ def main():
     W = max(args.warmup, 3)
     K = args.steps
     config = {"workload": f"{cfg.name} batch-1 greedy decode, {args.prompt}-token prompt + {K + W} steps "
-                          f"(BASELINE config 2)", "prompt_tokens": args.prompt,
+                          f"(the reference's headline configuration)", "prompt_tokens": args.prompt,
               "parallelism": f"tp{world}",
               "tp_allreduce": (args.tp_allreduce if world > 1 else None), "cache_policy": "inputs larger than L2 "
               "(every step streams all weights, 15 GB / TP)"}
@@ -525,8 +525,8 @@ def main():
         "metric": "decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong",
-        # the reference engine's published 185.6 tok/s for this model / prompt on
-        # one B200 (real checkpoint; timing does not depend on weight values)
+        # the reference engine's published 185.6 tok/s for this model / prompt on one B200
+        # (real checkpoint; timing does not depend on weight values)
         "vs_baseline": (tok_s / 185.6) if world == 1 else None,
         "dtype": "bf16", "data": "synthetic",
         "config": config,
@@ -545,7 +545,7 @@ def main():
         "step_roofline": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_gbs,
                           "frac_of_peak": step_gbs / peak, "frac_of_8tbs": step_gbs / 8000.0},
         "published_reference": {"decode_tok_per_s": 185.6, "ttft_ms": 119.53,
-                                "note": "reference engine on 1xB200, real weights (BASELINE.md)"},
+                                "note": "reference engine on 1xB200, real weights (its published table)"},
     }
     if world == 1 and not args.no_cpu_baseline:
         try:

@@ -123,3 +123,49 @@ def test_whisper_restatement_matches_golden_and_hf():
     enc2, lg2 = W.hf_forward(W.hf_model(cfg, w), mel, ids)
     assert float((enc2 - enc).abs().max()) <= 1e-4 * float(enc2.abs().max())
     assert float((lg2 - lg).abs().max()) <= 1e-4 * float(lg2.abs().max())
+
+
+def test_bf16_eager_mode_is_a_depth_dependent_floor():
+    """decoder_forward(act_dtype=bfloat16) restates the reference's bf16 eager numerics: same
+    function as the fp32 run up to rounding, and its distance from fp32 grows with depth (the
+    full-size GPU test measures the CUDA path against this run)."""
+    from dataclasses import replace
+    from hoid_optimized_models_b200.configs import LLAMA31_8B
+    from hoid_optimized_models_b200.weights import make_decoder_weights
+    from oracle.ref_decoder import decoder_forward
+    cfg = replace(LLAMA31_8B, name="floor-test", hidden=512, inter=1536, n_q=4, n_kv=2, layers=6,
+                  vocab=512)
+    w = make_decoder_weights(cfg, 5)
+    ids = torch.randint(0, cfg.vocab, (48,), generator=torch.Generator().manual_seed(5))
+    h32, l32, _ = decoder_forward(cfg, w, ids)
+    h16, l16, _ = decoder_forward(cfg, w, ids, act_dtype=torch.bfloat16)
+    err = [float((a - b).abs().max() / b.abs().max()) for a, b in zip(h16[1:-1], h32[1:-1])]
+    assert all(0 < e < 5e-2 for e in err), err            # bf16 rounding, not a different function
+    assert err[-1] > err[0]                                # and it accumulates over layers
+    cos = torch.nn.functional.cosine_similarity(l16, l32, dim=-1)
+    assert float(cos.min()) > 0.99
+    # the default is untouched fp32
+    h32b, _, _ = decoder_forward(cfg, w, ids, act_dtype=None)
+    assert torch.equal(h32b[3], h32[3])
+
+
+def test_bf16_eager_mode_matches_hf_run_in_bf16():
+    """Pins the floor itself: HuggingFace's eager model run in torch.bfloat16 on the CPU sits at
+    the same distance from the fp32 run as the restatement with act_dtype=bfloat16 (the two round
+    at slightly different places, so they are compared by their distance from fp32, per layer)."""
+    from dataclasses import replace
+    from hoid_optimized_models_b200.configs import LLAMA31_8B
+    from hoid_optimized_models_b200.weights import make_decoder_weights
+    from oracle.ref_decoder import decoder_forward, hf_forward, hf_model
+    cfg = replace(LLAMA31_8B, name="floor-test", hidden=512, inter=1536, n_q=4, n_kv=2, layers=6,
+                  vocab=512)
+    w = make_decoder_weights(cfg, 5)
+    ids = torch.randint(0, cfg.vocab, (48,), generator=torch.Generator().manual_seed(5))
+    h32, _, _ = decoder_forward(cfg, w, ids)
+    h16, _, _ = decoder_forward(cfg, w, ids, act_dtype=torch.bfloat16)
+    hs, _ = hf_forward(hf_model(cfg, w).to(torch.bfloat16), ids)
+    for l in range(1, cfg.layers):
+        ref = h32[l]
+        mine = float((h16[l] - ref).abs().max() / ref.abs().max())
+        hf = float((hs[l].float() - ref).abs().max() / ref.abs().max())
+        assert 0.5 < mine / hf < 2.0, (l, mine, hf)
