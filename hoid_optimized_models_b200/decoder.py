@@ -146,6 +146,18 @@ class DenseDecoder:
         self.launches_per_step = (1 + ((8 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
                                   + (1 if self.link is not None else 0))   # + sequence advance
 
+    @classmethod
+    def from_checkpoint(cls, cfg: DecoderConfig, weights_dir: str, max_seq: int, device="cuda",
+                        **kw) -> "DenseDecoder":
+        """Engine on a HuggingFace safetensors checkpoint (the reference's load_weights +
+        constructor, models/llama31-8b/llama31_optimized.py:294-346): names and shapes are
+        checked against the configuration before anything is packed."""
+        from . import checkpoint
+        w = checkpoint.load_weights(weights_dir, device=device)
+        checkpoint.check_decoder_names(cfg, w)
+        kw.setdefault("free_source_weights", True)
+        return cls(cfg, w, max_seq, device=device, **kw)
+
     # ------------------------------------------------------------------ collectives
     def _all_reduce(self, t: torch.Tensor) -> None:
         if self.tp_size > 1:

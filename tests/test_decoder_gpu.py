@@ -142,3 +142,23 @@ def test_qwen3_arch(dev):
     from hoid_optimized_models_b200.configs import QWEN3_4B, reduced
     cfg = reduced(QWEN3_4B, layers=2, vocab=8192)
     _run(dev, cfg, P=129, seed=1)
+
+
+def test_engine_from_safetensors_checkpoint(dev, tmp_path):
+    """The real-weight path: an engine built from a sharded safetensors directory under the
+    HuggingFace names generates the same tokens as one built from the in-memory weights."""
+    from hoid_optimized_models_b200 import checkpoint
+    from hoid_optimized_models_b200.configs import QWEN3_4B, reduced
+    from hoid_optimized_models_b200.decoder import Qwen3Optimized
+    from hoid_optimized_models_b200.weights import make_decoder_weights
+    cfg = reduced(QWEN3_4B, layers=2, vocab=4096)
+    w = make_decoder_weights(cfg, 7)
+    names = sorted(w)
+    checkpoint.save_file(str(tmp_path / "model-00001-of-00002.safetensors"),
+                         {n: w[n] for n in names[::2]})
+    checkpoint.save_file(str(tmp_path / "model-00002-of-00002.safetensors"),
+                         {n: w[n] for n in names[1::2]})
+    ids = torch.randint(0, cfg.vocab, (40,), generator=torch.Generator().manual_seed(7)).to(dev)
+    a = Qwen3Optimized(cfg, w, max_seq=64, device=dev).generate(ids, 6)
+    b = Qwen3Optimized.from_checkpoint(cfg, str(tmp_path), max_seq=64, device=dev).generate(ids, 6)
+    assert a == b
