@@ -62,6 +62,43 @@ def test_argument_validation_returns_codes(lib):
     assert lib.b200_gemm_bf16(one, one, one, 0, 128, 100, 64, 64, 64, 100, None, None, 0, 0, None, 0, None) == -1
 
 
+def test_validation_of_the_newer_entry_points(lib):
+    """Fused attention, LayerNorm-prologue GEMV, tensor-parallel link and router GEMV reject bad
+    arguments on the host; nothing here reaches a CUDA call."""
+    one, odd = ctypes.c_void_p(16), ctypes.c_void_p(24)
+    # b200_rope_flash_decode: null, group size, alignment of the projection row (every variant
+    # below is refused before the launch: this test must stay harmless on a machine with a GPU)
+    args = [one, 1, one, one, one, one, one, None, None, 1e-6, one, one, 32, 8, 128, 128 * 64, 128,
+            64, 4, 1.0, 0, None]
+    bad = list(args); bad[2] = None
+    assert lib.b200_rope_flash_decode(*bad) == -4
+    bad = list(args); bad[12] = 30
+    assert lib.b200_rope_flash_decode(*bad) == -1
+    bad = list(args); bad[2] = odd
+    assert lib.b200_rope_flash_decode(*bad) == -2
+    bad = list(args); bad[7] = one                            # q norm weight without k norm weight
+    assert lib.b200_rope_flash_decode(*bad) == -4
+    # LayerNorm beta without gamma
+    assert lib.b200_gemv_bf16(one, 0, one, one, 0, 256, 8, 256, None, one, 0.0, None, None, 0, 0, 0,
+                              None) == -4
+    # tensor-parallel link: sizes, and calls on a context that was never created
+    assert lib.b200_tp_buffer_bytes(2, 4096) == 256 + 256 + 2 * 2 * 4096 * 8 + 2 * 4096 * 8
+    assert lib.b200_tp_buffer_bytes(9, 4096) == 0 and lib.b200_tp_buffer_bytes(2, 0) == 0
+    assert lib.b200_tp_create(None, 2, 0, 4096) == -4
+    assert lib.b200_tp_advance(3, 64, 0, None) == -4
+    assert lib.b200_gemv_bf16_tp(one, one, one, 4096, 4096, 4096, None, 0.0, None, None, 0, 3, -1, 0,
+                                 None, None, 0, None) == -4
+    assert lib.b200_moe_decode_down_tp(one, one, one, 8, 768, 2048, 0, 128, None, 3, 0, None, 0,
+                                       None) == -4
+    # router GEMV: expert count must be a multiple of 32, k <= E
+    assert lib.b200_moe_router_gemv(one, one, one, one, one, None, 0.0, one, 100, 2048, 8, 0, 0,
+                                    None) == -1
+    assert lib.b200_moe_router_gemv(one, one, one, None, one, None, 0.0, one, 128, 2048, 8, 0, 0,
+                                    None) == -4
+    # the mixed-dtype RMSNorm keeps its shape rule
+    assert lib.b200_add_rmsnorm(one, one, 0, one, 1, one, 0, one, 1, 12, 1e-5, 0, None) == -1
+
+
 def test_ops_refuse_cpu_tensors():
     """There is no CPU fallback: CPU tensors are an error, not a slow path."""
     from hoid_optimized_models_b200 import ops
