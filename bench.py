@@ -150,6 +150,14 @@ def cpu_reference(cfg, ctx: int, steps: int, warmup: int, sample_layers: int = 4
 
 
 # ------------------------------------------------------------------------------ other configs
+def _no_switch_multicast():
+    """The ranks leave with os._exit while captured graphs still hold communicator kernels (see
+    leave()), i.e. without the communicator teardown.  Memory bound to an NVLink multicast object
+    must not outlive its process that way, so the collective library's in-switch path is left off
+    unless the caller asked for it; the decode exchange does not go through the library anyway."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
+
 def _time_graph(graph, steps, warmup):
     for _ in range(warmup):
         graph.replay()
@@ -190,6 +198,7 @@ def run_secondary(args):
         import torch.distributed as dist
         if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
             del os.environ["NCCL_DEBUG"]
+        _no_switch_multicast()
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
 
@@ -374,6 +383,7 @@ def main():
         import torch.distributed as dist
         if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
             del os.environ["NCCL_DEBUG"]           # keep stdout to the one JSON line
+        _no_switch_multicast()
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
 
