@@ -449,6 +449,193 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core variant of the dense GEMV (B200_TUNE_GEMV = 3; EXPERIMENTAL: its data mapping is
+// checked against an emulation of the mma fragment layout, it has not been timed yet and is not
+// the default).  The SIMT loop above spends 64 instructions per 512 bytes of weights (unpack,
+// dependent FMAs, bookkeeping); here a warp multiplies 16 rows x 64 columns of W per step with
+// four 16-byte loads per lane and four mma.sync.m16n8k16:
+//   * A = W: lane (g, tq) loads 32 contiguous bytes of row g and of row g + 8 (a quad covers one
+//     128-byte line per row).  The dot product does not care in which order k is visited, so the
+//     16 values of a lane are used as they lie: MMA m takes elements 4m .. 4m+3 of both rows;
+//   * B = x: column 0 carries the bf16 high part of x, column 1 the low part (x = hi + lo keeps
+//     ~16 mantissa bits), the other six columns are zero; lane (n, tq) reads the 16 matching
+//     values of column n from shared memory with two 16-byte loads;
+//   * D: column 0 + column 1 of row g / g + 8 meet in lane tq = 0 - no shuffle, no unpack.
+// The eight warps of a CTA split K, every warp walks all 16-row groups of the CTA over its K
+// slice, and the per-warp partial sums are added in warp order exactly as in the SIMT kernel.
+__device__ __forceinline__ void gemv_mma_step(float* c, const uint4& a0, const uint4& a1,
+                                              const uint4& b0, const uint4& b1, const uint4& x0,
+                                              const uint4& x1) {
+  // a0 / a1: elements 0..7 / 8..15 of row g; b0 / b1: the same of row g + 8; x0 / x1: the lane's
+  // 16 values of its B column
+#define B200_GEMV_MMA(A0, A1, A2, A3, B0, B1)                                                   \
+  asm volatile(                                                                                 \
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "      \
+      "{%8,%9}, {%0,%1,%2,%3};"                                                                  \
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])                                          \
+      : "r"(A0), "r"(A1), "r"(A2), "r"(A3), "r"(B0), "r"(B1))
+  B200_GEMV_MMA(a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
+  B200_GEMV_MMA(a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
+  B200_GEMV_MMA(a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
+  B200_GEMV_MMA(a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
+#undef B200_GEMV_MMA
+}
+
+template <int MINB>
+__global__ void __launch_bounds__(kGemvThreads, MINB) gemv_mma_kernel(GemvArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int K = a.K;
+  uint32_t* xh = reinterpret_cast<uint32_t*>(smem_raw);      // K/2 packed bf16 pairs: high parts
+  uint32_t* xl = xh + (K >> 1);                               // K/2 pairs: low parts
+  const int rpc16 = (a.rpc + 15) & ~15;
+  float* part = reinterpret_cast<float*>(xl + (K >> 1));      // [rpc16][kGemvWarps]
+  float* red = part + rpc16 * kGemvWarps;                     // 32
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, tq = lane & 3;
+  const int r0 = blockIdx.x * a.rpc;
+  const int nrows = min(a.N - r0, a.rpc);
+  pdl_launch_dependents();
+  if (nrows <= 0) return;
+
+  // this warp's K slice in units of 64 columns (128 bytes per row)
+  const int units = K >> 6;
+  const int u0 = units * warp / kGemvWarps, u1 = units * (warp + 1) / kGemvWarps;
+  const int nu = u1 - u0;
+  const int ngroups = (nrows + 15) >> 4;
+  const int total = ngroups * nu;                             // steps of this warp
+  const unsigned char* wbase = reinterpret_cast<const unsigned char*>(a.w);
+  const size_t row_bytes = (size_t)a.ldw * 2;
+  auto load_step = [&](uint4* d, int s) {                     // d[0..1] row g, d[2..3] row g + 8
+    const int grp = s / nu, u = u0 + (s - grp * nu);
+    const int ra = min(grp * 16 + g, nrows - 1), rb = min(grp * 16 + g + 8, nrows - 1);
+    const unsigned char* pa = wbase + (size_t)(r0 + ra) * row_bytes + (size_t)u * 128 + tq * 32;
+    const unsigned char* pb = wbase + (size_t)(r0 + rb) * row_bytes + (size_t)u * 128 + tq * 32;
+    d[0] = ldg_stream(pa); d[1] = ldg_stream(pa + 16);
+    d[2] = ldg_stream(pb); d[3] = ldg_stream(pb + 16);
+  };
+  // weights do not depend on the previous kernel: two steps are in flight before the wait
+  uint4 w0[4], w1[4], w2[4];
+  if (0 < total) load_step(w0, 0);
+  if (1 < total) load_step(w1, 1);
+
+  pdl_wait();
+
+  // stage x (* norm weight) as bf16 high / low pairs; the RMSNorm scalar multiplies the row sums
+  float ss = 0.f;
+  for (int i = tid; i < (K >> 2); i += kGemvThreads) {
+    float4 v;
+    if (a.x_dtype == B200_F32) {
+      v = reinterpret_cast<const float4*>(a.x)[i];
+    } else {
+      const uint2 u = reinterpret_cast<const uint2*>(a.x)[i];
+      v = make_float4(bf16lo(u.x), bf16hi(u.x), bf16lo(u.y), bf16hi(u.y));
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (a.norm_w != nullptr) {
+      const uint2 u = reinterpret_cast<const uint2*>(a.norm_w)[i];
+      v.x *= bf16lo(u.x); v.y *= bf16hi(u.x); v.z *= bf16lo(u.y); v.w *= bf16hi(u.y);
+    }
+    const __nv_bfloat16 h0 = __float2bfloat16(v.x), h1 = __float2bfloat16(v.y);
+    const __nv_bfloat16 h2 = __float2bfloat16(v.z), h3 = __float2bfloat16(v.w);
+    uint2 hi, lo;
+    hi.x = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+    hi.y = (uint32_t)__bfloat16_as_ushort(h2) | ((uint32_t)__bfloat16_as_ushort(h3) << 16);
+    lo.x = pack_bf16(v.x - __bfloat162float(h0), v.y - __bfloat162float(h1));
+    lo.y = pack_bf16(v.z - __bfloat162float(h2), v.w - __bfloat162float(h3));
+    reinterpret_cast<uint2*>(xh)[i] = hi;
+    reinterpret_cast<uint2*>(xl)[i] = lo;
+  }
+  for (int i = tid; i < rpc16 * kGemvWarps; i += kGemvThreads) part[i] = 0.f;
+  const float tot = block_sum(ss, red);                       // its barriers also publish xh / xl
+  const float out_scale = a.norm_w != nullptr ? rsqrtf(tot / (float)K + a.eps) : 1.f;
+  __syncthreads();
+
+  const uint32_t* xsel = g == 0 ? xh : xl;                    // B column of this lane (g < 2)
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  auto compute = [&](const uint4* d, int s) {
+    const int grp = s / nu, u = u0 + (s - grp * nu);
+    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+    if (g < 2) {
+      const uint4* xp = reinterpret_cast<const uint4*>(xsel + ((u * 64 + tq * 16) >> 1));
+      x0 = xp[0]; x1 = xp[1];
+    }
+    gemv_mma_step(c, d[0], d[1], d[2], d[3], x0, x1);
+    if (s - grp * nu == nu - 1) {                             // last step of this group: park the sums
+      if (tq == 0) {
+        part[(grp * 16 + g) * kGemvWarps + warp] = c[0] + c[1];
+        part[(grp * 16 + g + 8) * kGemvWarps + warp] = c[2] + c[3];
+      }
+      c[0] = c[1] = c[2] = c[3] = 0.f;
+    }
+  };
+  for (int s = 0; s < total; s += 3) {                        // three register buffers in rotation
+    if (s + 2 < total) load_step(w2, s + 2);
+    compute(w0, s);
+    if (s + 1 < total) {
+      if (s + 3 < total) load_step(w0, s + 3);
+      compute(w1, s + 1);
+    }
+    if (s + 2 < total) {
+      if (s + 4 < total) load_step(w1, s + 4);
+      compute(w2, s + 2);
+    }
+  }
+  __syncthreads();
+
+  // ---- epilogue: fixed-order row sums (as in the SIMT kernel) ----
+  auto row_value = [&](int r) -> float {
+    float v = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGemvWarps; ++i) v += part[r * kGemvWarps + i];
+    v *= out_scale;
+    if (a.bias != nullptr) v += __uint_as_float((uint32_t)a.bias[r0 + r] << 16);
+    return v;
+  };
+  if (a.epilogue == B200_EPI_SWIGLU) {
+    for (int t = tid; t < (nrows >> 1); t += kGemvThreads) {
+      const float gv = row_value(2 * t), uv = row_value(2 * t + 1);
+      const float o = silu_f(gv) * uv;
+      const int oi = (r0 >> 1) + t;
+      if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = o;
+      else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(o);
+    }
+  } else {
+    for (int t = tid; t < nrows; t += kGemvThreads) {
+      float v = row_value(t);
+      if (a.epilogue == B200_EPI_GELU) v = gelu_erf(v);
+      const int oi = r0 + t;
+      if (a.resid != nullptr) {
+        v += (a.resid_dtype == B200_F32)
+                 ? reinterpret_cast<const float*>(a.resid)[oi]
+                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.resid)[oi]);
+      }
+      if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = v;
+      else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(v);
+    }
+  }
+}
+
+template <int MINB>
+static cudaError_t gemv_mma_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pdl) {
+  const int wave = MINB * kNumSMs;
+  int grid = wave;
+  int rpc = (a.N + grid - 1) / grid;
+  while (rpc > 1024) { grid += wave; rpc = (a.N + grid - 1) / grid; }
+  if (swiglu && (rpc & 1)) ++rpc;
+  grid = (a.N + rpc - 1) / rpc;
+  a.rpc = rpc;
+  const size_t smem = (size_t)a.K * 4 + (size_t)((rpc + 15) & ~15) * kGemvWarps * 4 + 128;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemv_mma_kernel<MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    attr_set = true;
+  }
+  return launch(gemv_mma_kernel<MINB>, dim3(grid), dim3(kGemvThreads), smem, st, pdl, a);
+}
+
 template <int U, int MINB, int MODE = 0, bool TP = false>
 static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pdl, int n_slots = 1) {
   // MINB CTAs per SM (shared between the routing slots in MODE 1); grow the grid in whole
@@ -505,6 +692,9 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   switch (g_tuning[B200_TUNE_GEMV]) {
     case 1: e = gemv_launch<4, 4>(a, sw, st, pdl); break;
     case 2: e = gemv_launch<4, 3>(a, sw, st, pdl); break;
+    case 3:   // experimental tensor-core loop; no LayerNorm prologue there
+      e = norm_beta != nullptr ? gemv_launch<8, 2>(a, sw, st, pdl) : gemv_mma_launch<2>(a, sw, st, pdl);
+      break;
     default: e = gemv_launch<8, 2>(a, sw, st, pdl); break;
   }
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;

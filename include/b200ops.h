@@ -55,7 +55,8 @@ enum {
 
 int b200_version(void);
 /* Kernel tuning knobs (process-wide, host side): key B200_TUNE_GEMV selects the GEMV
- * variant (loads per batch / CTAs per SM / row mapping); 0 is the measured best. */
+ * variant (loads per batch / CTAs per SM / row mapping); 0 is the measured best; 3 is an
+ * experimental inner loop on mma.sync (bf16 high / low split of x), not yet timed. */
 enum { B200_TUNE_GEMV = 0, B200_TUNE_GEMM_BN = 1 /* force the GEMM tile width: 256 / 128 / 64 */,
        B200_TUNE_TP_PROTOCOL = 2 /* fused all-reduce: 0 tagged pairs summed by a few CTAs, 1 data +
                                     sequence flags, 2 tagged pairs read directly by every CTA */,

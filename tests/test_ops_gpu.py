@@ -2,6 +2,8 @@
 (oracle/ref_decoder.py helpers where they exist).  Tolerances are stated per test."""
 import math
 
+import os
+
 import pytest
 import torch
 
@@ -70,6 +72,41 @@ def test_gemv_fusions(dev):
     ops.gemv(yb, act, wd.to(dev), epilogue=ops.EPI_GELU)
     ref3 = torch.nn.functional.gelu(wd.float() @ act.float().cpu())
     assert rel_err(yb, ref3) < 1e-2  # bf16 output rounding
+
+
+@pytest.mark.skipif(os.environ.get("B200_EXPERIMENTAL") != "1",
+                    reason="tensor-core GEMV loop: not yet validated on a GPU, opt in with B200_EXPERIMENTAL=1")
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 6144), (14336, 4096), (2048, 128), (256, 7),
+                                 (1280, 51866)])
+def test_gemv_tensor_core_variant(dev, K, N):
+    """B200_TUNE_GEMV = 3 against the fp32 reference and the default kernel, with the RMSNorm
+    prologue, bias / residual and the SwiGLU epilogue."""
+    from hoid_optimized_models_b200 import ops
+    from oracle.ref_decoder import rmsnorm
+    g = torch.Generator().manual_seed(K + N)
+    w = bf(torch.randn(N, K, generator=g) * 0.02).to(dev)
+    x = torch.randn(K, generator=g)
+    nw = bf(1 + 0.02 * torch.randn(K, generator=g))
+    bias = bf(torch.randn(N, generator=g))
+    res = torch.randn(N, generator=g)
+    ref = w.float().cpu() @ rmsnorm(x, nw.float(), 1e-5) + bias.float() + res
+    y0 = torch.empty(N, dtype=torch.float32, device=dev)
+    y1 = torch.empty(N, dtype=torch.float32, device=dev)
+    ops.gemv(y0, x.to(dev), w, norm_w=nw.to(dev), eps=1e-5, bias=bias.to(dev), resid=res.to(dev))
+    try:
+        ops.set_tuning(0, 3)
+        ops.gemv(y1, x.to(dev), w, norm_w=nw.to(dev), eps=1e-5, bias=bias.to(dev), resid=res.to(dev))
+        torch.cuda.synchronize()
+        assert rel_err(y1, ref) < 1e-4 and rel_err(y1, y0.cpu()) < 1e-4
+        if N % 2 == 0:
+            a0 = torch.empty(N // 2, dtype=torch.float32, device=dev)
+            a1 = torch.empty(N // 2, dtype=torch.float32, device=dev)
+            ops.gemv(a1, x.to(dev), w, epilogue=ops.EPI_SWIGLU)
+            ops.set_tuning(0, 0)
+            ops.gemv(a0, x.to(dev), w, epilogue=ops.EPI_SWIGLU)
+            assert rel_err(a1, a0.cpu()) < 1e-4
+    finally:
+        ops.set_tuning(0, 0)
 
 
 def test_gemv_rejects_bad_shapes(dev):
