@@ -89,3 +89,61 @@ def test_attention_rows_carry_high_and_low_parts():
             got = [s[lane, nb, 0] + s[lane, nb, 2], s[lane, nb, 1] + s[lane, nb, 3]]
             want = ref[g, nb * 8 + tq * 2: nb * 8 + tq * 2 + 2]
             assert np.abs(np.array(got) - want).max() < 1e-12
+
+
+def _gemv_visits(K, nrows):
+    """Replays the work split of gemv_mma_kernel for one CTA: which (row, k) every lane of every
+    warp loads in every step, with the kernel's own index arithmetic."""
+    warps = 8
+    units = K >> 6
+    ngroups = (nrows + 15) >> 4
+    seen = np.zeros((nrows, K), dtype=np.int32)
+    parked = np.zeros((ngroups * 16, warps), dtype=np.int32)
+    for warp in range(warps):
+        u0, u1 = units * warp // warps, units * (warp + 1) // warps
+        nu = u1 - u0
+        for s in range(ngroups * nu):
+            grp = s // nu
+            u = u0 + (s - grp * nu)
+            for lane in range(32):
+                g, tq = lane >> 2, lane & 3
+                for half in (0, 8):
+                    row = grp * 16 + g + half
+                    if row < nrows:                       # clamped rows are loaded but never used
+                        k = u * 64 + tq * 16
+                        seen[row, k:k + 16] += 1
+            if s - grp * nu == nu - 1:
+                parked[grp * 16:(grp + 1) * 16, warp] += 1
+    return seen, parked, units
+
+
+def test_gemv_work_split_covers_every_weight_exactly_once():
+    for K in (256, 768, 1280, 4096, 14336):
+        for nrows in (1, 7, 16, 21, 98):
+            seen, parked, units = _gemv_visits(K, nrows)
+            assert (seen == 1).all(), (K, nrows)
+            # a warp parks its sums for a group exactly once iff it owns part of K
+            owns = np.array([units * (w + 1) // 8 > units * w // 8 for w in range(8)])
+            assert (parked[:, owns] == 1).all() and (parked[:, ~owns] == 0).all(), (K, nrows)
+
+
+def test_decode_attention_tiles_cover_every_key_exactly_once():
+    """flash_decode_mma_kernel: splits, 128-key tiles, 16 keys per warp, masks past the slice."""
+    for kv_len in (1, 15, 16, 127, 128, 129, 333, 1500, 8193):
+        for n_splits in (1, 4, 7, 18, 36):
+            seen = np.zeros(kv_len, dtype=np.int32)
+            per = (kv_len + n_splits - 1) // n_splits
+            for split in range(n_splits):
+                k0 = split * per
+                k1 = min(kv_len, k0 + per)
+                ntiles = (k1 - k0 + 127) // 128 if k1 > k0 else 0
+                for t in range(ntiles):
+                    row0 = k0 + t * 128
+                    for warp in range(8):
+                        key0 = row0 + warp * 16
+                        if key0 >= k1:
+                            continue
+                        for e in range(16):
+                            if key0 + e < k1:             # the kernel masks the others to -inf
+                                seen[key0 + e] += 1
+            assert (seen == 1).all(), (kv_len, n_splits)
