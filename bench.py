@@ -218,7 +218,7 @@ def run_secondary(args):
     if name in ("qwen3-4b", "qwen3-30b-a3b"):
         from hoid_optimized_models_b200.decoder import DenseDecoder
         cfg = C.QWEN3_4B if name == "qwen3-4b" else C.QWEN3_30B_A3B
-        P = args.prompt if args.prompt != PROMPT else 1024
+        P = args.prompt or 1024                    # the reference quotes these two at 1k tokens
         w = Wt.make_decoder_weights(cfg, 1234, dev)
         eng = DenseDecoder(cfg, w, max_seq=P + W + K + 8, device=dev, max_new_tokens=W + K + 8,
                            free_source_weights=True, tp_rank=rank, tp_size=world, group=group,
@@ -327,7 +327,8 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--prompt", type=int, default=None,
+                    help=f"prompt tokens (default {PROMPT}; 1024 for the Qwen3 workloads)")
     ap.add_argument("--layers", type=int, default=0, help="debug: reduced depth (invalid as a result)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
@@ -346,6 +347,7 @@ def main():
     if args.workload != "llama-3.1-8b" and args.impl == "b200":
         run_secondary(args)
         return
+    args.prompt = args.prompt or PROMPT
     from hoid_optimized_models_b200.configs import LLAMA31_8B, reduced
     cfg = LLAMA31_8B if not args.layers else reduced(LLAMA31_8B, layers=args.layers)
     rank = int(os.environ.get("RANK", "0"))
