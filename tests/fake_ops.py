@@ -1,9 +1,9 @@
 """TEST INFRASTRUCTURE - a plain-torch CPU stand-in for `hoid_optimized_models_b200.ops`.
 
-The engines (`decoder.py`) are host logic over the op layer: buffer ownership, weight packing,
-launch order, device-side step state, tensor- / expert-parallel sharding and which all-reduce
-feeds which GEMV.  These functions re-state every op the decoder engine calls with the same
-signature and the same in/out semantics on CPU tensors, so that logic runs in the CPU test suite
+The engines (`decoder.py`, `encoder.py`, `whisper.py`) are host logic over the op layer: buffer
+ownership, weight packing, launch order, device-side step state, tensor- / expert- / data-parallel
+sharding and which all-reduce feeds which GEMV.  These functions re-state every op the engines
+call with the same signature and the same in/out semantics on CPU tensors, so that logic runs in the CPU test suite
 (single process and world_size-2 gloo) against the fp32 oracle.  Nothing in the product imports
 this file, and it is no fallback: `hoid_optimized_models_b200.ops` itself refuses CPU tensors.
 """
@@ -97,6 +97,38 @@ def add_rmsnorm(norm_out, resid_out, a, b, w, eps):
     _store(norm_out, _rms(s, w, eps))
 
 
+def _ln_sum(x, bias, resid, rounded: bool):
+    """x (+ bias) (+ resid); with bf16 inputs every addition is rounded to bf16 like the kernel."""
+    r = (lambda t: t.to(torch.bfloat16).float()) if rounded else (lambda t: t)
+    v = x.float()
+    if bias is not None:
+        v = r(v + bias.float())
+    if resid is not None:
+        v = r(v + resid.float().reshape(v.shape))
+    return v
+
+
+def layernorm(norm_out, x, gamma, beta, eps, bias=None, resid=None):
+    v = _ln_sum(x, bias, resid, x.dtype == torch.bfloat16)
+    _store(norm_out, F.layer_norm(v, v.shape[-1:], gamma.float(), beta.float(), eps))
+
+
+def add_layernorm(norm_out, resid_out, x, gamma, beta, eps, bias=None, resid=None):
+    v = _ln_sum(x, bias, resid, x.dtype == torch.bfloat16)
+    _store(resid_out, v)
+    v = resid_out.float().reshape(v.shape)
+    _store(norm_out, F.layer_norm(v, v.shape[-1:], gamma.float(), beta.float(), eps))
+
+
+def cls_pool_l2(out, x, seq_len, eps=1e-12):
+    first = x.float().reshape(-1, seq_len, x.shape[-1])[:, 0]
+    _store(out, first / first.norm(dim=-1, keepdim=True).clamp_min(eps))
+
+
+def silu_mul(out, gate, up):
+    _store(out, F.silu(gate.float()) * up.float())
+
+
 # ----------------------------------------------------------------------------- rope / attention
 def _rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
     half = x.shape[-1] // 2
@@ -124,7 +156,12 @@ def flash_decode_workspace(n_q, n_kv, hd, n_splits, device):
 
 def flash_decode(out, q, kcache, vcache, kv_len, workspace, n_q, n_kv, n_splits, scale,
                  kv_head_stride=-1, kv_row_stride=-1):
-    L, hd = int(kv_len), kcache.shape[-1]
+    L = int(kv_len)
+    hd = q.numel() // n_q
+    if kv_row_stride > 0 and kcache.dim() == 2:
+        # rows of [L, n_kv * hd] projections: head h of row j starts at j * row_stride + h * hd
+        kcache = kcache.reshape(kcache.shape[0], n_kv, hd).permute(1, 0, 2)
+        vcache = vcache.reshape(vcache.shape[0], n_kv, hd).permute(1, 0, 2)
     g = n_q // n_kv
     qq = q.float().reshape(n_q, hd)
     kk = kcache[:, :L].float().repeat_interleave(g, 0)
