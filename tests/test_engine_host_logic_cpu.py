@@ -133,3 +133,21 @@ def test_two_gloo_ranks_match_one(kind, fused):
     # dense: the vocabulary is sharded over the ranks; MoE: every rank holds all logits
     full = torch.tensor(res[0][2]) if kind == "moe" else torch.cat([torch.tensor(r[2]) for r in res])
     assert float((full - logits_ref).abs().max() / logits_ref.abs().max()) < 2e-2
+
+
+def test_engine_from_checkpoint_on_cpu(tmp_path):
+    """The real-weight path end to end: sharded safetensors directory -> from_checkpoint ->
+    the same tokens as the engine built from the in-memory weights."""
+    import hoid_optimized_models_b200.decoder as D
+    from hoid_optimized_models_b200 import checkpoint
+    from hoid_optimized_models_b200.weights import make_decoder_weights
+    D.ops = fake_ops
+    cfg = _cfg("qwen3")
+    w = make_decoder_weights(cfg, 3)
+    names = sorted(w)
+    checkpoint.save_file(str(tmp_path / "model-00001-of-00002.safetensors"), {n: w[n] for n in names[::2]})
+    checkpoint.save_file(str(tmp_path / "model-00002-of-00002.safetensors"), {n: w[n] for n in names[1::2]})
+    ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(3))
+    a = _generate(_engine(cfg, dict(w)), ids)
+    eng = D.Qwen3Optimized.from_checkpoint(cfg, str(tmp_path), max_seq=P + N_NEW + 2, device="cpu")
+    assert _generate(eng, ids) == a
