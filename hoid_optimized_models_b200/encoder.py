@@ -64,6 +64,17 @@ class XlmrEncoder:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_forward = 3 + 7 * cfg.layers + 1
 
+    @classmethod
+    def from_checkpoint(cls, cfg: EncoderConfig, weights_dir: str, batch: int, seq: int,
+                        device="cuda", strip_prefix: str = "", **kw) -> "XlmrEncoder":
+        """Engine on a HuggingFace safetensors checkpoint of an `XLMRobertaModel` (the tensors
+        models/bge-m3/bge_optimized.py:294-313 reads from the stock model); `strip_prefix` removes
+        a wrapper prefix such as "roberta." from the stored names."""
+        from . import checkpoint
+        w = checkpoint.load_weights(weights_dir, device=device, keep=lambda n: True,
+                                    strip_prefix=strip_prefix)
+        return cls(cfg, w, batch, seq, device=device, **kw)
+
     def load_inputs(self, input_ids: torch.Tensor) -> None:
         """input_ids: this rank's [batch / dp, seq] token ids."""
         self.ids.copy_(input_ids.reshape(-1).to(torch.int32))

@@ -34,6 +34,15 @@ def _conv_as_gemm_weight(w: torch.Tensor) -> torch.Tensor:
     return w.permute(0, 2, 1).reshape(w.shape[0], -1).contiguous()
 
 
+def load_checkpoint(weights_dir: str, device="cuda") -> Dict[str, torch.Tensor]:
+    """The `model.*` tensors of a HuggingFace `WhisperForConditionalGeneration` safetensors
+    checkpoint (the names models/whisper-large-v3/whisper_decoder_optimized.py:189-228 reads), as
+    both engines below take them."""
+    from . import checkpoint
+    return checkpoint.load_weights(weights_dir, device=device,
+                                   keep=lambda n: n.startswith("model."))
+
+
 class WhisperEncoder:
     def __init__(self, cfg: WhisperConfig, weights: Dict[str, torch.Tensor], device="cuda"):
         self.cfg, self.device = cfg, torch.device(device)

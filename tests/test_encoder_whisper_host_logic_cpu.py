@@ -125,3 +125,31 @@ def test_whisper_matches_oracle_on_cpu():
     for j, (a, b) in enumerate(zip(toks, ref_toks)):
         k = len(prefix) - 1 + j
         assert a == b or float(top2[k, 0] - top2[k, 1]) < 2e-2, (j, toks, ref_toks)
+
+
+def test_encoder_and_whisper_from_checkpoints_on_cpu(tmp_path):
+    """Safetensors directories (one with a wrapper prefix on the stored names) -> engines with the
+    same outputs as the engines built from the in-memory weights."""
+    from hoid_optimized_models_b200 import checkpoint
+    from hoid_optimized_models_b200.encoder import XlmrEncoder
+    import hoid_optimized_models_b200.whisper as Wh
+    from hoid_optimized_models_b200.configs import WHISPER_LARGE_V3
+    from hoid_optimized_models_b200.weights import make_whisper_weights
+    cfg, w, B, S, ids = _enc_case()
+    (tmp_path / "enc").mkdir()
+    checkpoint.save_file(str(tmp_path / "enc" / "model.safetensors"), {"roberta." + n: t for n, t in w.items()})
+    a = XlmrEncoder(cfg, w, batch=B, seq=S, device="cpu").embed(ids).clone()
+    b = XlmrEncoder.from_checkpoint(cfg, str(tmp_path / "enc"), B, S, device="cpu",
+                                    strip_prefix="roberta.").embed(ids)
+    assert torch.equal(a, b)
+
+    wc = replace(WHISPER_LARGE_V3, name="host-whisper", d_model=128, heads=4, ffn=256, n_mels=16,
+                 n_frames=120, n_ctx=60, enc_layers=1, dec_layers=1, vocab=300, max_target=32)
+    ww = make_whisper_weights(wc, 6)
+    (tmp_path / "whisper").mkdir()
+    checkpoint.save_file(str(tmp_path / "whisper" / "model.safetensors"), {**ww, "proj_out.weight": ww["model.decoder.embed_tokens.weight"]})
+    got = Wh.load_checkpoint(str(tmp_path / "whisper"), device="cpu")
+    assert set(got) == set(ww) and all(torch.equal(got[n], ww[n]) for n in ww)
+    mel = torch.randn(wc.n_mels, wc.n_frames, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    e1, e2 = Wh.WhisperEncoder(wc, ww, device="cpu"), Wh.WhisperEncoder(wc, got, device="cpu")
+    assert torch.equal(e1.encode(mel), e2.encode(mel))
