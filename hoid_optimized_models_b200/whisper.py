@@ -20,7 +20,7 @@ Decoder step (fp32 activations, weights streamed once per token):
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -135,7 +135,12 @@ class WhisperEncoder:
 
 class WhisperDecoder:
     def __init__(self, cfg: WhisperConfig, weights: Dict[str, torch.Tensor], device="cuda",
-                 max_new_tokens: int = 448):
+                 max_new_tokens: int = 448, suppress_tokens: Optional[Sequence[int]] = None,
+                 begin_suppress_tokens: Optional[Sequence[int]] = None):
+        """suppress_tokens / begin_suppress_tokens: token ids whose logit is forced to -inf at
+        every step / at the first generated token only (the `mask` and `begin_mask` the reference
+        adds to the logits before its argmax, models/whisper-large-v3/best_hoid.py:88-104).  The
+        mask rides as the bias of the logits GEMV, so the on-device greedy selection sees it."""
         self.cfg, self.device = cfg, torch.device(device)
         dev, D, H, hd = self.device, cfg.d_model, cfg.heads, cfg.head_dim
         g = lambda n: weights["model.decoder." + n].to(dev)
@@ -179,6 +184,16 @@ class WhisperDecoder:
         self.act = f32(cfg.ffn)
         self.logits = f32(cfg.vocab)
         self.cand = f32(2)
+        self.logit_bias = self._steady_bias = self._begin_bias = None
+        if suppress_tokens or begin_suppress_tokens:
+            def mask(ids):
+                m = torch.zeros(cfg.vocab, dtype=torch.bfloat16, device=dev)
+                if ids:
+                    m[torch.tensor(sorted(set(ids)), dtype=torch.long, device=dev)] = float("-inf")
+                return m
+            self._steady_bias = mask(list(suppress_tokens or []))
+            self._begin_bias = mask(list(suppress_tokens or []) + list(begin_suppress_tokens or []))
+            self.logit_bias = self._steady_bias.clone()      # the buffer the captured graph reads
         self.self_splits = max(1, min(148 // H, (T + 63) // 64))
         self.cross_splits = max(1, min(148 // H, (S + 63) // 64))
         self.ws_self = ops.flash_decode_workspace(H, H, hd, self.self_splits, dev)
@@ -226,7 +241,7 @@ class WhisperDecoder:
                      norm_w=L["ln3"][0], norm_b=L["ln3"][1], eps=cfg.eps)
             ops.gemv(x, self.act, L["wf2"], bias=L["bf2"], resid=x)
         ops.gemv(self.logits, x, self.embed_tok, norm_w=self.ln_f[0], norm_b=self.ln_f[1],
-                 eps=cfg.eps)
+                 eps=cfg.eps, bias=self.logit_bias)
         ops.argmax(self.cand, self.logits, self.am_ws)
         ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
 
@@ -263,11 +278,15 @@ class WhisperDecoder:
         greedily.  Returns the generated tokens."""
         for p, t in enumerate(prefix):
             self.set_step(t, p, 0)
+            if self.logit_bias is not None and p == len(prefix) - 1:
+                self.logit_bias.copy_(self._begin_bias)      # this step yields the first new token
             self._run()
             if collect_logits is not None:
                 collect_logits.append(self.logits.float().cpu().clone())
         # the step for the last prefix token has already produced the first new token
         out = [int(self.tok.item())]
+        if self.logit_bias is not None:
+            self.logit_bias.copy_(self._steady_bias)
         pos = len(prefix)
         self.state.copy_(torch.tensor([pos, pos + 1, 0, 0], dtype=torch.int32))
         for _ in range(n_new - 1):

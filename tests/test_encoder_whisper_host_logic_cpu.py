@@ -153,3 +153,35 @@ def test_encoder_and_whisper_from_checkpoints_on_cpu(tmp_path):
     mel = torch.randn(wc.n_mels, wc.n_frames, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
     e1, e2 = Wh.WhisperEncoder(wc, ww, device="cpu"), Wh.WhisperEncoder(wc, got, device="cpu")
     assert torch.equal(e1.encode(mel), e2.encode(mel))
+
+
+def test_whisper_suppression_masks_ride_in_the_logits_bias():
+    """suppress_tokens hold at every step, begin_suppress_tokens at the first generated token only;
+    without either the decoder is unchanged."""
+    from hoid_optimized_models_b200.configs import WHISPER_LARGE_V3
+    from hoid_optimized_models_b200.weights import make_whisper_weights
+    from hoid_optimized_models_b200.whisper import WhisperDecoder
+    cfg = replace(WHISPER_LARGE_V3, name="host-whisper", d_model=128, heads=4, ffn=256, n_mels=16,
+                  n_frames=120, n_ctx=60, enc_layers=1, dec_layers=2, vocab=300, max_target=32)
+    w = make_whisper_weights(cfg, 6)
+    enc_out = (torch.randn(cfg.n_ctx, cfg.d_model, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16)
+    prefix, n_new = [7, 100, 33], 6
+
+    def run(**kw):
+        dec = WhisperDecoder(cfg, w, device="cpu", **kw)
+        dec.set_encoder(enc_out)
+        logits = []
+        return dec.generate(prefix, n_new, collect_logits=logits), torch.stack(logits)
+
+    base, lg0 = run()
+    banned_first = base[0]
+    others = [t for t in base[1:] if t != banned_first]
+    banned_always = others[0] if others else (banned_first + 1) % cfg.vocab
+    toks, lg = run(suppress_tokens=[banned_always], begin_suppress_tokens=[banned_first])
+    assert toks[0] != banned_first and banned_always not in toks
+    first = len(prefix) - 1                         # row of the first generated token
+    assert torch.isinf(lg[first, banned_first]) and torch.isinf(lg[first:, banned_always]).all()
+    assert not torch.isinf(lg[first + 1:, banned_first]).any()      # begin mask: first token only
+    keep = torch.ones(cfg.vocab, dtype=torch.bool)
+    keep[[banned_first, banned_always]] = False
+    assert torch.allclose(lg[first][keep], lg0[first][keep])        # everything else untouched
