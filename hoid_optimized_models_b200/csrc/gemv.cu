@@ -774,7 +774,8 @@ extern "C" int b200_moe_decode_down(void* y, int y_dtype, const void* act, const
 // Tensor-parallel link: peer-mapped inboxes set up once per process.
 namespace {
 struct TpContext { b200::TpLink link; void* local; bool used; };
-TpContext g_tp[4];
+constexpr int kTpMaxContexts = 16;   // links per process (an engine holds one for its lifetime)
+TpContext g_tp[kTpMaxContexts];
 constexpr size_t kTpAlign = 256;
 size_t tp_flag_bytes(int world) { return ((size_t)2 * world * 4 + kTpAlign - 1) & ~(kTpAlign - 1); }
 }  // namespace
@@ -813,7 +814,7 @@ extern "C" int b200_tp_create(void* const* bufs, int world, int rank, int H) {
   if (!bufs || world <= 0 || world > kTpMaxRanks || rank < 0 || rank >= world || H <= 0 || (H & 3))
     return B200_ERR_ARG;
   int id = -1;
-  for (int i = 0; i < 4; ++i) if (!g_tp[i].used) { id = i; break; }
+  for (int i = 0; i < kTpMaxContexts; ++i) if (!g_tp[i].used) { id = i; break; }
   if (id < 0) return B200_ERR_ARG;
   TpLink& l = g_tp[id].link;
   for (int p = 0; p < world; ++p) {
@@ -840,7 +841,7 @@ __global__ void tp_advance_kernel(int* seq_base, int inc) {
 
 /* seq_base += inc (number of fused all-reduces issued since the last advance): once per step. */
 extern "C" int b200_tp_advance(int ctx, int inc, int flags, b200_stream_t stream) {
-  if (ctx < 0 || ctx >= 4 || !g_tp[ctx].used) return B200_ERR_ARG;
+  if (ctx < 0 || ctx >= kTpMaxContexts || !g_tp[ctx].used) return B200_ERR_ARG;
   cudaError_t e = launch(tp_advance_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream,
                          (flags & B200_FLAG_PDL) != 0, (int*)g_tp[ctx].link.seq_base, inc);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
@@ -855,7 +856,7 @@ extern "C" int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, i
                                  const void* norm_w, float eps, const void* bias,
                                  const void* resid, int epilogue, int ctx, int tp_in, int tp_out,
                                  void* x_out, int* status, int flags, b200_stream_t stream) {
-  if (ctx < 0 || ctx >= 4 || !g_tp[ctx].used) return B200_ERR_ARG;
+  if (ctx < 0 || ctx >= kTpMaxContexts || !g_tp[ctx].used) return B200_ERR_ARG;
   if (!w || (tp_in < 0 && !x) || (tp_out < 0 && !y)) return B200_ERR_ARG;
   if (K <= 0 || N <= 0 || (K & 255) != 0 || ldw < K || K > 32768) return B200_ERR_SHAPE;
   if ((ldw & 7) != 0 || ((uintptr_t)w & 15) != 0) return B200_ERR_ALIGN;
@@ -887,7 +888,7 @@ extern "C" int b200_moe_decode_down_tp(const void* act, const void* w_down, cons
                                        int top_k, int inter, int hidden, int expert_lo,
                                        int n_local, const void* resid, int ctx, int tp_out,
                                        int* status, int flags, b200_stream_t stream) {
-  if (ctx < 0 || ctx >= 4 || !g_tp[ctx].used || tp_out < 0) return B200_ERR_ARG;
+  if (ctx < 0 || ctx >= kTpMaxContexts || !g_tp[ctx].used || tp_out < 0) return B200_ERR_ARG;
   return moe_down_impl(&g_tp[ctx].link, tp_out, status, nullptr, B200_F32, act, w_down, ids, top_k,
                        inter, hidden, expert_lo, n_local, resid, B200_F32, flags, stream);
 }

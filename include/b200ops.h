@@ -98,7 +98,8 @@ int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y, int y_dty
  * models/llama31-8b/llama31_optimized.py:407,414) is fused into the GEMVs on both sides of it.
  * Set-up (once per process, may allocate): every rank allocates b200_tp_buffer_bytes() with
  * b200_tp_alloc, exchanges the 64-byte IPC handles, maps its peers with b200_tp_open and
- * registers the table with b200_tp_create (returns a context id >= 0).
+ * registers the table with b200_tp_create (returns a context id >= 0; at most 16 links per
+ * process, each lives until the process exits).
  * Per step: b200_gemv_bf16_tp with tp_out >= 0 pushes this rank's partial y into every rank's
  * inbox over NVLink, as 8-byte {value, sequence tag} pairs that arrive atomically (or, with
  * tuning key B200_TUNE_TP_PROTOCOL = 1, as plain stores followed by one system-scope release
