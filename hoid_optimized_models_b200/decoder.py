@@ -141,6 +141,7 @@ class DenseDecoder:
             from .comm import PeerLink
             self.link = PeerLink(group, tp_rank, tp_size, H)
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}
+        self._prefill_graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.fuse_rope = fuse_rope
         self.launches_per_step = (1 + ((8 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
@@ -386,16 +387,41 @@ class DenseDecoder:
 
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, collect: Optional[list] = None,
-                collect_router: Optional[list] = None) -> int:
+                collect_router: Optional[list] = None, graph: bool = False) -> int:
         """Runs the prompt, fills the KV cache and returns the first generated token.
         `collect` receives a copy of the residual stream after every layer, `collect_router`
-        the expert ids [P, top_k] every MoE layer chose."""
-        cfg = self.cfg
+        the expert ids [P, top_k] every MoE layer chose.
+        graph=True (off by default; not yet exercised on a GPU) replays a CUDA graph captured
+        for this prompt length instead of launching the ~9 kernels per layer from the host,
+        which is what bounds the time to first token of short prompts."""
         P = ids.numel()
         if P + 1 > self.max_seq:
             raise ValueError("prompt too long for this cache")
         e = self._prefill_buffers(P)
         e["ids"].copy_(ids.to(torch.int32))
+        if graph and collect is None and collect_router is None:
+            g = self._prefill_graphs.get(P)
+            if g is None:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    self._prefill_launches(e, P, None, None)      # warm-up outside the capture
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._prefill_launches(e, P, None, None)
+                self._prefill_graphs[P] = g
+            g.replay()
+        else:
+            self._prefill_launches(e, P, collect, collect_router)
+        self.last_prefill_hidden = e["x"]
+        return int(self.tok.item())
+
+    def _prefill_launches(self, e: Dict[str, torch.Tensor], P: int, collect: Optional[list],
+                          collect_router: Optional[list]) -> None:
+        """Every launch of one prefill over the buffers `e` (no host synchronisation inside)."""
+        cfg = self.cfg
         tp = self.att_tp > 1
         ep = self.moe and self.tp_size > 1
         hd = cfg.head_dim
@@ -446,8 +472,6 @@ class DenseDecoder:
             ops.greedy_select(self.tok, self.cand_all)
         else:
             ops.greedy_select(self.tok, self.cand)
-        self.last_prefill_hidden = x
-        return int(self.tok.item())
 
     # ------------------------------------------------------------------ generation
     @torch.no_grad()
