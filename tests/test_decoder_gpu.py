@@ -144,6 +144,9 @@ def test_qwen3_arch(dev):
     _run(dev, cfg, P=129, seed=1)
 
 
+@pytest.mark.skipif(__import__("os").environ.get("B200_EXPERIMENTAL") != "1",
+                    reason="written after the GPU budget was spent: first run is opt-in (B200_EXPERIMENTAL=1); "
+                           "the same path is covered on the CPU in tests/test_engine_host_logic_cpu.py")
 def test_engine_from_safetensors_checkpoint(dev, tmp_path):
     """The real-weight path: an engine built from a sharded safetensors directory under the
     HuggingFace names generates the same tokens as one built from the in-memory weights."""

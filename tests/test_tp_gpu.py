@@ -146,6 +146,9 @@ def _enc_case():
     return cfg, B, S, ids
 
 
+@pytest.mark.skipif(os.environ.get("B200_EXPERIMENTAL") != "1",
+                    reason="written after the GPU budget was spent: first run is opt-in (B200_EXPERIMENTAL=1); "
+                           "the same logic runs on two gloo ranks in tests/test_encoder_whisper_host_logic_cpu.py")
 def test_encoder_data_parallel_matches_one_rank(dev):
     """Batch split over two ranks + all-gather of the pooled rows against the one-rank encoder."""
     if torch.cuda.device_count() < 2:
