@@ -43,6 +43,20 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def ncu_traffic(kernel: str, layers: int):
+    """DRAM bytes per launch of `kernel` from profiles/ncu_traffic.json (written beside the ncu
+    summaries from the captures they describe).  An entry measured on a reduced-depth model
+    carries its depth, and the traffic of the layer phases scales with the number of layers."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            e = json.load(f)[kernel]
+        per = float(e["dram_bytes_per_launch"])
+        return per * layers / e["layers"] if e.get("layers") else per
+    except (OSError, KeyError, ValueError, TypeError):
+        return None
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
 
@@ -154,8 +168,9 @@ def _no_switch_multicast():
     """The ranks leave with os._exit while captured graphs still hold communicator kernels (see
     leave()), i.e. without the communicator teardown.  Memory bound to an NVLink multicast object
     must not outlive its process that way, so the collective library's in-switch path is left off
-    unless the caller asked for it; the decode exchange does not go through the library anyway."""
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    whatever the caller's environment says; the decode exchange does not go through the library
+    anyway."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
 
 
 def _time_graph(graph, steps, warmup):
@@ -186,8 +201,6 @@ def run_secondary(args):
     ops.set_pdl(not args.no_pdl)
     for kv in args.tune:
         ops.set_tuning(*(int(t) for t in kv.split("=")))
-    if args.tp_allreduce.startswith("fused-"):     # B200_TUNE_TP_PROTOCOL
-        ops.set_tuning(2, {"flags": 1, "direct": 2, "summed": 3}[args.tp_allreduce[6:]])
     peak, peak_kind = measured_peaks()
     K, W = args.steps, max(args.warmup, 3)
     name = args.workload
@@ -222,7 +235,8 @@ def run_secondary(args):
         w = Wt.make_decoder_weights(cfg, 1234, dev)
         eng = DenseDecoder(cfg, w, max_seq=P + W + K + 8, device=dev, max_new_tokens=W + K + 8,
                            free_source_weights=True, tp_rank=rank, tp_size=world, group=group,
-                           fused_allreduce=args.tp_allreduce != "nccl")
+                           fused_allreduce=args.tp_allreduce != "nccl",
+                           fused_layers=not args.per_phase_launches)
         del w
         torch.cuda.empty_cache()
         ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(1)).to(dev)
@@ -333,9 +347,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--ttft-runs", type=int, default=3)
-    ap.add_argument("--tp-allreduce", default="fused", choices=["fused", "fused-flags", "fused-direct", "fused-summed", "nccl"],
-                    help="N>1: all-reduce fused into the GEMVs over peer memory (tagged pairs, or "
-                         "data + sequence flags), or NCCL calls")
+    ap.add_argument("--tp-allreduce", default="fused", choices=["fused", "nccl"],
+                    help="N>1: all-reduce fused into the decode kernels over peer memory, or NCCL calls")
+    ap.add_argument("--per-phase-launches", action="store_true",
+                    help="one launch per phase instead of the persistent all-layers kernel (A/B)")
     ap.add_argument("--workload", default="llama-3.1-8b",
                     help="llama-3.1-8b (headline) | qwen3-4b | qwen3-30b-a3b | xlm-roberta-large | whisper-large-v3")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
@@ -364,7 +379,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        base = cpu_reference(cfg, args.prompt, max(2, min(K, 8)), min(W, 2))
+        base = cpu_reference(cfg, args.prompt, K, W)       # exactly K timed steps after W warm ones
         line = {"impl": "reference", "metric": "decode_tok_per_s", "value": base["value"],
                 "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
                 "ms_per_step": base["ms_per_step"], "higher_is_better": True, "scaling": "strong",
@@ -395,14 +410,13 @@ def main():
     ops.set_pdl(not args.no_pdl)
     for kv in args.tune:
         ops.set_tuning(*(int(t) for t in kv.split("=")))
-    if args.tp_allreduce.startswith("fused-"):     # B200_TUNE_TP_PROTOCOL
-        ops.set_tuning(2, {"flags": 1, "direct": 2, "summed": 3}[args.tp_allreduce[6:]])
 
     weights = make_decoder_weights(cfg, 1234, dev)
     max_seq = args.prompt + W + K + 8
     eng = Llama31Optimized(cfg, weights, max_seq=max_seq, device=dev, tp_rank=rank, tp_size=world,
                            group=group, max_new_tokens=W + K + 8, free_source_weights=True,
-                           fused_allreduce=args.tp_allreduce != "nccl")
+                           fused_allreduce=args.tp_allreduce != "nccl",
+                           fused_layers=not args.per_phase_launches)
     del weights
     torch.cuda.empty_cache()
     ids = torch.randint(0, cfg.vocab, (args.prompt,), generator=torch.Generator().manual_seed(2))
@@ -474,47 +488,68 @@ def main():
             os._exit(0)
         return
 
-    # ---- end to end through the public step API: H2D token + state, replay, D2H token ----
-    tok_host = torch.zeros(1, dtype=torch.int32).pin_memory()
-    state_host = torch.zeros(4, dtype=torch.int32).pin_memory()
-    out_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    # ---- end to end through the public host-driven step (DenseDecoder.step_host): per step the
+    # token + step state go up from pinned host memory, the graph replays, the token comes back ----
     pos = args.prompt + W + K
-    eng.set_step(first, pos, 0)
-    tok = first
     KE = max(8, min(K, 32))
+    tok = first
     barrier()
     t0 = time.perf_counter()
     for j in range(KE):
-        tok_host[0] = tok
-        state_host[0], state_host[1], state_host[2] = pos - KE + j, pos - KE + j + 1, 0
-        eng.tok.copy_(tok_host, non_blocking=True)
-        eng.state.copy_(state_host, non_blocking=True)
-        eng.graph.replay()
-        out_host.copy_(eng.tok, non_blocking=True)
-        torch.cuda.synchronize()
-        tok = int(out_host[0])
+        tok = eng.step_host(tok, pos - KE + j)
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / KE
 
-    # ---- roofline of the dominant kernel (gate|up GEMV, half of all bytes), timed live ----
+    # ---- roofline of the dominant kernel, timed live with CUDA events on the launching stream.
+    # With the persistent kernel that is decode_layers_kernel (every layer's weights + the KV
+    # cache, all but the lm_head of the step's bytes); on the per-phase path the gate|up GEMV. ----
     peak, peak_kind = measured_peaks()
-    x = torch.randn(cfg.hidden, dtype=torch.float32, device=dev)
-    for i in range(cfg.layers):
-        ops.gemv(eng.act, x, eng.wgu[i], norm_w=eng.ln2[i], eps=cfg.eps, epilogue=ops.EPI_SWIGLU)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 4
-    e0.record()
-    for _ in range(reps):
-        for i in range(cfg.layers):
-            ops.gemv(eng.act, x, eng.wgu[i], norm_w=eng.ln2[i], eps=cfg.eps, epilogue=ops.EPI_SWIGLU)
-    e1.record()
-    torch.cuda.synchronize()
-    gemv_ms = e0.elapsed_time(e1) / (reps * cfg.layers)
-    gemv_bytes = eng.wgu[0].numel() * 2 + cfg.hidden * 4 + cfg.hidden * 2 + eng.inter * 4
-    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9
     ctx_mid = args.prompt + W + K // 2
     step_bytes = cfg.decode_bytes_per_token(ctx_mid) / world
     step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
+    ops.check_status(dev)
+    reps = 16
+    if eng.plan is not None:
+        kernel_name = "decode_layers_kernel (all layers of the step: q|k|v, attention, o, gate|up, down)"
+        head_bytes = 2 * (cfg.vocab * cfg.hidden + cfg.hidden) / world
+        kernel_bytes = step_bytes - head_bytes
+        eng.set_step(first, ctx_mid - 1, 0)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        barrier()
+        for it in range(3 + reps):
+            ops.embed_gather(eng.h, eng.embed, eng.tok)
+            if it >= 3:
+                ev[it - 3][0].record()
+            ops.decode_layers(eng.plan, eng.cos, eng.sin, eng.kv_len, eng.fd_ws, eng.n_q, eng.n_kv,
+                              eng.n_splits, eng.scale, cfg.eps)
+            if it >= 3:
+                ev[it - 3][1].record()
+            if eng.link is not None:      # finish the step's exchange so that the sequence advances
+                ops.gemv_tp_consume(eng.logits, eng.lm_head, eng.link.ctx, 2 * cfg.layers - 1,
+                                    x_out=eng.h, norm_w=eng.final_norm_w, eps=cfg.eps)
+                ops.tp_advance(eng.link.ctx, 2 * cfg.layers)
+        torch.cuda.synchronize()
+        kernel_ms = max_over_ranks(statistics.median(a.elapsed_time(b) for a, b in ev))
+        launches_timed = 1
+    else:
+        kernel_name = "gemv_kernel (gate|up + SwiGLU, N=28672/tp K=4096)"
+        x = torch.randn(cfg.hidden, dtype=torch.float32, device=dev)
+        for i in range(cfg.layers):
+            ops.gemv(eng.act, x, eng.wgu[i], norm_w=eng.ln2[i], eps=cfg.eps, epilogue=ops.EPI_SWIGLU)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(4):
+            for i in range(cfg.layers):
+                ops.gemv(eng.act, x, eng.wgu[i], norm_w=eng.ln2[i], eps=cfg.eps, epilogue=ops.EPI_SWIGLU)
+        e1.record()
+        torch.cuda.synchronize()
+        kernel_ms = max_over_ranks(e0.elapsed_time(e1) / (4 * cfg.layers))
+        kernel_bytes = eng.wgu[0].numel() * 2 + cfg.hidden * 4 + cfg.hidden * 2 + eng.inter * 4
+        launches_timed = 1
+    ops.check_status(dev)
+    achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
+    traffic = ncu_traffic("decode_layers_kernel" if eng.plan is not None else "gemv_kernel_gate_up",
+                          cfg.layers) if world == 1 else None
 
     def leave():
         """Multi-rank exit: the captured graph holds NCCL kernels, so drop it, meet the other
@@ -547,13 +582,13 @@ def main():
                 "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "steps": KE},
         "gpu_launches": eng.launches_per_step * K,
         "clocks": clk,
-        "roofline": {"bound": "hbm", "kernel": "gemv_kernel (gate|up + SwiGLU, N=28672/tp K=4096)",
+        "roofline": {"bound": "hbm", "kernel": kernel_name,
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}",
-                     # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the ncu
-                     # capture summarised in profiles/gemv_kernel_gate_up_llama8b.md
-                     "traffic": (234_945_000 + 3_219_712) if world == 1 else None,
-                     "bytes_per_launch": gemv_bytes, "ms_per_launch": gemv_ms},
+                     # dram__bytes_read.sum + dram__bytes_write.sum per launch, read from the
+                     # figures file kept beside the ncu summary under profiles/
+                     "traffic": traffic,
+                     "bytes_per_launch": kernel_bytes, "ms_per_launch": kernel_ms},
         "step_roofline": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_gbs,
                           "frac_of_peak": step_gbs / peak, "frac_of_8tbs": step_gbs / 8000.0},
         "published_reference": {"decode_tok_per_s": 185.6, "ttft_ms": 119.53,

@@ -23,6 +23,7 @@ ERRORS = {
     -5: "B200_ERR_TIMEOUT (bounded device-side wait expired)",
     -6: "B200_ERR_DRIVER (driver entry point unavailable)",
     -7: "B200_ERR_SCRATCH (request exceeds the library's fixed scratch array)",
+    -8: "B200_ERR_NUMERIC (non-finite input where an index is derived from it)",
 }
 
 _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_int64
@@ -40,7 +41,11 @@ SIGNATURES = {
     "b200_tp_advance": (_i, [_i, _i, _i, _p]),
     "b200_gemv_bf16_tp": (_i, [_p, _p, _p, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p]),
     "b200_moe_decode_down_tp": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _p, _i, _p]),
-    "b200_moe_router_gemv": (_i, [_p, _p, _p, _p, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p]),
+    "b200_decode_layers_plan_bytes": (_l, [_i]),
+    "b200_decode_layers_sync_bytes": (_i, []),
+    "b200_decode_layers_plan": (_i, [_p, _i] + [_p] * 10 + [_p] * 4 + [_i] * 5),
+    "b200_decode_layers": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _l, _l, _i, _i, _f,
+                                _f, _i, _p, _i, _p]),
     "b200_add_rmsnorm": (_i, [_p, _p, _i, _p, _i, _p, _i, _p, _i, _i, _f, _i, _p]),
     "b200_add_layernorm": (_i, [_p, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _f, _i, _p]),
     "b200_qk_rope_cache": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
@@ -53,10 +58,9 @@ SIGNATURES = {
     "b200_flash_decode_static": (_i, [_p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _l, _l, _i, _f, _i, _p]),
     "b200_gemm_bf16": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _i, _p]),
     "b200_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),
-    "b200_flash_prefill": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_i, _f, _i, _p]),
-    "b200_moe_router": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_moe_router": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p]),
     "b200_moe_permute_workspace_bytes": (_l, [_i, _i]),
-    "b200_moe_permute": (_i, [_p, _p, _p, _p, _i, _i, _p, _i, _p]),
+    "b200_moe_permute": (_i, [_p, _p, _p, _p, _i, _i, _p, _p, _i, _p]),
     "b200_moe_gather_rows": (_i, [_p, _p, _p, _i, _i, _i, _i, _p]),
     "b200_moe_combine": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "b200_moe_decode_gate_up": (_i, [_p, _p, _i, _p, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),

@@ -15,6 +15,7 @@
 namespace b200 {
 
 constexpr int kNumSMs = 148;
+constexpr int kMaxDevices = 64;   // per-device host-side caches are indexed by cudaGetDevice()
 
 // Tuning knobs set through b200_set_tuning (defined in misc.cu).
 extern int g_tuning[16];
@@ -98,6 +99,21 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   // fixed order: every thread adds the warp partials in index order
   for (int i = 0; i < nw; ++i) t += red[i];
   return t;
+}
+
+// Opt a kernel in to `bytes` of dynamic shared memory, once per device: the attribute belongs to
+// the (function, device) pair, so a process that drives several GPUs must set it on each.
+// `done` is a per-call-site array of kMaxDevices flags.
+template <typename... KArgs>
+inline cudaError_t opt_in_smem(void (*kernel)(KArgs...), int bytes, bool* done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[dev] = true;
+  return e;
 }
 
 // Launch helper that optionally attaches the programmatic-stream-serialization

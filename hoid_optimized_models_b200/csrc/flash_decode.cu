@@ -4,437 +4,21 @@
 // contiguous slice of the context and serves all G = n_q / n_kv query heads of the
 // group from a single pass over K and V, so each cache byte is read from HBM once.
 //
-// A key row (HD bf16) is spread over HD/8 lanes, 16 bytes each: a warp-wide 128-bit
-// load covers 32/(HD/8) adjacent keys = 512 contiguous bytes, and a 16-warp CTA
-// keeps 64 KB of loads in flight.  Every lane group runs its own online softmax
-// (m, l, acc in registers); the groups of a warp are merged with shuffles, the
-// warps of a CTA through shared memory, and the CTA publishes ONE record
-// [acc(G x HD), m(G), l(G)] to the workspace.  The CTA that arrives last on the
-// per-kv-head counter merges the n_splits records (a handful of coalesced float4
-// loads per thread) in fixed split order and writes the output.  No CTA ever
-// waits on another.
+// A CTA of eight warps streams 128-key tiles of K and V through a three-stage cp.async ring;
+// each warp owns 16 keys of a tile and runs S = Q K^T and O += P V on mma.sync m16n8k16 (about
+// 20 instructions per KB of cache; a SIMT kernel with one shuffle reduction per key and head
+// needed ~185 and was issue-bound near 4 TB/s).  The 16-row A operand carries the group's
+// G <= 8 query heads twice: rows 0..7 hold the bf16 high part of q (and of P), rows 8..15 the
+// bf16 low part, so q and P keep ~16 mantissa bits at no extra MMA and the two halves of an
+// accumulator add up inside one thread.  The warps' records are merged through shared memory,
+// the CTA publishes ONE record [acc(G x HD), m(G), l(G)] to the workspace, and the CTA that
+// arrives last on the per-kv-head counter merges the n_splits records (a handful of coalesced
+// float4 loads per thread) in fixed split order and writes the output.  No CTA ever waits on
+// another.
 #include "common.cuh"
+#include "flash_decode_core.cuh"
 
 namespace b200 {
-
-constexpr int kFdU = 2;  // keys per lane group per iteration (two iterations in flight)
-
-struct FdArgs {
-  void* out; const void* q; const uint16_t* k; const uint16_t* v; const int* kv_len;
-  int* counters; float* recs;
-  int n_q, n_kv, n_splits, out_dtype, q_dtype;
-  long head_stride, row_stride;  // elements
-  float scale_log2;
-  // ROPE variant: q / k / v of the new position come straight from the packed fp32 projection
-  // row; the kernel applies (QK-RMSNorm +) RoPE itself and appends the row to the cache
-  const float* qkv; const float* cos_t; const float* sin_t;
-  const uint16_t* qn_w; const uint16_t* kn_w;
-  float eps; int max_seq;
-};
-
-// threads per CTA: the register file holds 512 threads at 128 registers (G <= 4)
-constexpr int fd_threads(int G) { return G <= 4 ? 512 : 256; }
-
-// ---- shared tail of both kernels -------------------------------------------------------------
-// In: srec[WARPS][REC] holds one record (acc[G][HD], m[G], l[G]) per warp.  The warps are merged,
-// the CTA's record goes to the workspace, and the CTA that arrives last on the kv head's counter
-// merges the n_splits records.  srec is re-used as scratch by that last step and must hold at
-// least 6 * THREADS floats.
-template <int HD, int G, int THREADS>
-__device__ __forceinline__ void fd_finish(const FdArgs& a, float* srec, float* sw, int kvh,
-                                          int split) {
-  constexpr int WARPS = THREADS / 32;
-  constexpr int REC = G * HD + ((2 * G + 3) & ~3);
-  __shared__ float s_M[G], s_den[G];
-  __shared__ int s_last;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  __syncthreads();
-  // ---- merge the CTA's warps: warp g' computes the weights of head g' ----
-  for (int g = warp; g < G; g += WARPS) {
-    const float mv = lane < WARPS ? srec[lane * REC + G * HD + g] : -INFINITY;
-    const float M = warp_max(mv);
-    const float Mu = (M == -INFINITY) ? 0.f : M;
-    const float w = lane < WARPS ? exp2f(mv - Mu) : 0.f;
-    const float den = warp_sum(lane < WARPS ? srec[lane * REC + G * HD + G + g] * w : 0.f);
-    if (lane < WARPS) sw[lane * G + g] = w;
-    if (lane == 0) { s_M[g] = M; s_den[g] = den; }
-  }
-  __syncthreads();
-  float* wr = a.recs + (size_t)(kvh * a.n_splits + split) * REC;
-  for (int i = tid; i < G * HD; i += THREADS) {
-    const int g = i / HD;
-    float num = 0.f;
-#pragma unroll
-    for (int w2 = 0; w2 < WARPS; ++w2) num = fmaf(srec[w2 * REC + i], sw[w2 * G + g], num);
-    wr[i] = num;
-  }
-  if (tid < G) { wr[G * HD + tid] = s_M[tid]; wr[G * HD + G + tid] = s_den[tid]; }
-
-  // ---- publish, and let the last-arriving CTA of this kv head finish the job ----
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(&a.counters[kvh], 1);
-    s_last = (old == a.n_splits - 1);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-
-  // Every thread owns one float4 column of the output and every PARTS-th split: all its loads
-  // are independent (one L2 round trip), the partial results meet in shared memory.
-  constexpr int C4 = G * HD / 4;
-  constexpr int PARTS = (THREADS / C4) >= 8 ? 8 : ((THREADS / C4) >= 1 ? (THREADS / C4) : 1);
-  static_assert(C4 <= THREADS, "one pass over the output columns");
-  float4* sp_num = reinterpret_cast<float4*>(srec);             // [PARTS][C4]
-  float* sp_m = srec + 4 * PARTS * C4;                          // [PARTS][C4]
-  float* sp_d = sp_m + PARTS * C4;
-  const float* rb = a.recs + (size_t)kvh * a.n_splits * REC;
-  const int ns = a.n_splits;
-  if (tid < PARTS * C4) {
-    const int c = tid % C4, part = tid / C4, g = (c * 4) / HD;
-    float m_run = -INFINITY, den = 0.f;
-    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int sp = part; sp < ns; sp += PARTS) {
-      const float* rec = rb + (size_t)sp * REC;
-      const float mv = __ldcg(rec + G * HD + g);
-      const float lv = __ldcg(rec + G * HD + G + g);
-      const float4 r = __ldcg(reinterpret_cast<const float4*>(rec) + c);
-      const float mn = fmaxf(m_run, mv);
-      const float mu = (mn == -INFINITY) ? 0.f : mn;
-      const float wa = exp2f(m_run - mu), wb = exp2f(mv - mu);
-      num.x = num.x * wa + r.x * wb; num.y = num.y * wa + r.y * wb;
-      num.z = num.z * wa + r.z * wb; num.w = num.w * wa + r.w * wb;
-      den = den * wa + lv * wb;
-      m_run = mn;
-    }
-    sp_num[tid] = num; sp_m[tid] = m_run; sp_d[tid] = den;
-  }
-  __syncthreads();
-  if (tid < C4) {
-    float m_run = sp_m[tid], den = sp_d[tid];
-    float4 num = sp_num[tid];
-#pragma unroll
-    for (int p = 1; p < PARTS; ++p) {
-      const float mv = sp_m[p * C4 + tid], lv = sp_d[p * C4 + tid];
-      const float4 r = sp_num[p * C4 + tid];
-      const float mn = fmaxf(m_run, mv);
-      const float mu = (mn == -INFINITY) ? 0.f : mn;
-      const float wa = exp2f(m_run - mu), wb = exp2f(mv - mu);
-      num.x = num.x * wa + r.x * wb; num.y = num.y * wa + r.y * wb;
-      num.z = num.z * wa + r.z * wb; num.w = num.w * wa + r.w * wb;
-      den = den * wa + lv * wb;
-      m_run = mn;
-    }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    const size_t oi = (size_t)kvh * G * HD + (size_t)tid * 4;
-    if (a.out_dtype == B200_F32) {
-      reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + oi)[0] =
-          make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
-    } else {
-      uint2 w2;
-      w2.x = pack_bf16(num.x * inv, num.y * inv);
-      w2.y = pack_bf16(num.z * inv, num.w * inv);
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out) + oi) = w2;
-    }
-  }
-  if (tid == 0) a.counters[kvh] = 0;  // ready for the next launch
-}
-
-template <int HD, int G, bool ROPE = false>
-__global__ void __launch_bounds__(fd_threads(G)) flash_decode_kernel(FdArgs a) {
-  constexpr int THREADS = fd_threads(G);
-  constexpr int WARPS = THREADS / 32;
-  constexpr int LPK = HD / 8;          // lanes per key
-  constexpr int KPW = 32 / LPK;        // keys per warp-wide load
-  constexpr int REC = G * HD + ((2 * G + 3) & ~3);  // record: acc[G][HD], m[G], l[G], 16-byte padded
-  extern __shared__ __align__(16) float fd_smem[];
-  float* srec = fd_smem;               // [WARPS][REC]
-  float* sw = srec + WARPS * REC;      // [WARPS][G] merge weights
-  __shared__ uint4 s_newk[ROPE ? HD / 8 : 1], s_newv[ROPE ? HD / 8 : 1];
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int sub = lane / LPK, dl = lane % LPK;
-  const int split = blockIdx.x, kvh = blockIdx.y;
-
-  pdl_launch_dependents();
-  pdl_wait();
-
-  const int kv_len = a.kv_len[0];
-  const int per = (kv_len + a.n_splits - 1) / a.n_splits;
-  const int k0 = split * per;
-  const int k1 = min(kv_len, k0 + per);
-
-  // q for the group's heads, pre-multiplied by scale * log2(e)
-  float q[G][8];
-  int pos_own = -1;                    // ROPE: the new position if this CTA's slice holds it
-  if (ROPE) {
-    // rotate-half RoPE on a head spread over LPK lanes: lane dl holds dims [8 dl, 8 dl + 8), its
-    // partner dl ^ (LPK / 2) the matching dims of the other half
-    constexpr int HL = LPK / 2;
-    const bool hi = dl >= HL;
-    const int pos = kv_len - 1;
-    const bool in_cache = pos >= 0 && pos < a.max_seq;
-    const size_t ci = (size_t)(in_cache ? pos : 0) * (HD / 2) + (size_t)(dl - (hi ? HL : 0)) * 8;
-    float cs[8], sn[8];
-    {
-      const float4* c4 = reinterpret_cast<const float4*>(a.cos_t + ci);
-      const float4* s4 = reinterpret_cast<const float4*>(a.sin_t + ci);
-      const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
-      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w;
-      cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w;
-      sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-    }
-    auto rope_head = [&](const float* src, const uint16_t* nw, float* o) {
-      const float4* p = reinterpret_cast<const float4*>(src + dl * 8);
-      const float4 x0 = p[0], x1 = p[1];
-      float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-      if (nw != nullptr) {
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
-#pragma unroll
-        for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
-        const float inv = rsqrtf(ss / (float)HD + a.eps);
-        float w[8];
-        unpack8(*reinterpret_cast<const uint4*>(nw + dl * 8), w);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * w[e];
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float other = __shfl_xor_sync(0xffffffffu, x[e], HL);
-        o[e] = hi ? (x[e] * cs[e] + other * sn[e]) : (x[e] * cs[e] - other * sn[e]);
-      }
-    };
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      rope_head(a.qkv + (size_t)(kvh * G + g) * HD, a.qn_w, q[g]);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) q[g][e] *= a.scale_log2;
-    }
-    if (in_cache && pos >= k0 && pos < k1) {     // CTA-uniform: this slice ends with the new row
-      float kf[8];
-      rope_head(a.qkv + (size_t)(a.n_q + kvh) * HD, a.kn_w, kf);
-      const float4* vp = reinterpret_cast<const float4*>(
-          a.qkv + (size_t)(a.n_q + a.n_kv + kvh) * HD + dl * 8);
-      const float4 v0 = vp[0], v1 = vp[1];
-      uint4 kp, vq;
-      kp.x = pack_bf16(kf[0], kf[1]); kp.y = pack_bf16(kf[2], kf[3]);
-      kp.z = pack_bf16(kf[4], kf[5]); kp.w = pack_bf16(kf[6], kf[7]);
-      vq.x = pack_bf16(v0.x, v0.y); vq.y = pack_bf16(v0.z, v0.w);
-      vq.z = pack_bf16(v1.x, v1.y); vq.w = pack_bf16(v1.z, v1.w);
-      if (warp == 0 && sub == 0) {
-        // the row is handed to the loop through shared memory: the streaming loads below are
-        // non-coherent and must not read what this launch writes
-        s_newk[dl] = kp; s_newv[dl] = vq;
-        const size_t row = (size_t)kvh * a.head_stride + (size_t)pos * a.row_stride + dl * 8;
-        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(a.k) + row) = kp;
-        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(a.v) + row) = vq;
-      }
-      pos_own = pos;
-      __syncthreads();
-    }
-  } else {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const size_t qi = ((size_t)(kvh * G + g) * HD) + dl * 8;
-      if (a.q_dtype == B200_F32) {
-        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.q) + qi);
-        float4 x = p[0], y = p[1];
-        q[g][0] = x.x; q[g][1] = x.y; q[g][2] = x.z; q[g][3] = x.w;
-        q[g][4] = y.x; q[g][5] = y.y; q[g][6] = y.z; q[g][7] = y.w;
-      } else {
-        unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.q) + qi), q[g]);
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) q[g][e] *= a.scale_log2;
-    }
-  }
-
-  float m[G], l[G], acc[G][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
-  }
-
-  const uint16_t* kb = a.k + (size_t)kvh * a.head_stride + dl * 8;
-  const uint16_t* vb = a.v + (size_t)kvh * a.head_stride + dl * 8;
-
-  // key handled by this lane group in unroll slot u of iteration `it`:
-  //   k0 + ((it * U + u) * WARPS + warp) * KPW + sub
-  // The loads of iteration it + 1 are issued before the arithmetic of iteration it.
-  constexpr int STRIDE = kFdU * WARPS * KPW;
-  uint4 kw[kFdU], vw[kFdU];
-  auto issue = [&](uint4* kd, uint4* vd, int base) {
-#pragma unroll
-    for (int u = 0; u < kFdU; ++u) {
-      const int key = base + u * WARPS * KPW + sub;
-      kd[u] = make_uint4(0, 0, 0, 0);
-      vd[u] = make_uint4(0, 0, 0, 0);
-      if (ROPE && key == pos_own) {
-        kd[u] = s_newk[dl];
-        vd[u] = s_newv[dl];
-      } else if (key < k1) {
-        kd[u] = ldg_stream(kb + (size_t)key * a.row_stride);
-        vd[u] = ldg_stream(vb + (size_t)key * a.row_stride);
-      }
-    }
-  };
-  const int base0 = k0 + warp * KPW;
-  if (base0 < k1) issue(kw, vw, base0);
-  for (int base = base0; base < k1; base += STRIDE) {
-    uint4 kn[kFdU], vn[kFdU];
-    if (base + STRIDE < k1) issue(kn, vn, base + STRIDE);
-    float s[kFdU][G];
-#pragma unroll
-    for (int u = 0; u < kFdU; ++u) {
-      const bool ok = base + u * WARPS * KPW + sub < k1;
-      float kf[8];
-      unpack8(kw[u], kf);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float d = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) d = fmaf(q[g][e], kf[e], d);
-#pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        s[u][g] = ok ? d : -INFINITY;
-      }
-    }
-    float p[kFdU][G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float mt = s[0][g];
-#pragma unroll
-      for (int u = 1; u < kFdU; ++u) mt = fmaxf(mt, s[u][g]);
-      const float mn = fmaxf(m[g], mt);
-      const float mu = (mn == -INFINITY) ? 0.f : mn;
-      const float corr = exp2f(m[g] - mu);
-      float ps = 0.f;
-#pragma unroll
-      for (int u = 0; u < kFdU; ++u) { p[u][g] = exp2f(s[u][g] - mu); ps += p[u][g]; }
-      l[g] = l[g] * corr + ps;
-      m[g] = mn;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
-    }
-#pragma unroll
-    for (int u = 0; u < kFdU; ++u) {
-      float vf[8];
-      unpack8(vw[u], vf);
-#pragma unroll
-      for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(p[u][g], vf[e], acc[g][e]);
-    }
-#pragma unroll
-    for (int u = 0; u < kFdU; ++u) { kw[u] = kn[u]; vw[u] = vn[u]; }
-  }
-
-  // ---- merge the lane groups of the warp with shuffles (lanes dl keep the same dims) ----
-#pragma unroll
-  for (int off = LPK; off < 32; off <<= 1) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
-      const float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
-      const float mn = fmaxf(m[g], mo);
-      const float mu = (mn == -INFINITY) ? 0.f : mn;
-      const float wa = exp2f(m[g] - mu), wb = exp2f(mo - mu);
-      l[g] = l[g] * wa + lo * wb;
-      m[g] = mn;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], off);
-        acc[g][e] = acc[g][e] * wa + ao * wb;
-      }
-    }
-  }
-  // ---- one record per warp into shared memory ----
-  if (sub == 0) {
-    float* r = srec + warp * REC;
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float4* dst = reinterpret_cast<float4*>(r + g * HD + dl * 8);
-      dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-      dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
-      if (dl == 0) { r[G * HD + g] = m[g]; r[G * HD + G + g] = l[g]; }
-    }
-  }
-  fd_finish<HD, G, THREADS>(a, srec, sw, kvh, split);
-}
-
-template <int HD, int G>
-static size_t fd_smem_bytes(int n_splits) {
-  constexpr int WARPS = fd_threads(G) / 32;
-  (void)n_splits;
-  size_t rec = (size_t)WARPS * (G * HD + ((2 * G + 3) & ~3));
-  if (rec < 6 * (size_t)fd_threads(G)) rec = 6 * (size_t)fd_threads(G);   // combine scratch
-  return (rec + (size_t)WARPS * G) * 4;
-}
-
-template <int HD, int G, bool ROPE = false>
-static cudaError_t fd_launch(const FdArgs& a, cudaStream_t st, bool pdl) {
-  const size_t smem = fd_smem_bytes<HD, G>(a.n_splits);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(flash_decode_kernel<HD, G, ROPE>,
-                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    attr_set = true;
-  }
-  return launch(flash_decode_kernel<HD, G, ROPE>, dim3(a.n_splits, a.n_kv), dim3(fd_threads(G)),
-                smem, st, pdl, a);
-}
-
-// ---- tensor-core variant ---------------------------------------------------------------------
-// The SIMT kernel above spends ~185 instructions per KB of cache (a 16-lane shuffle reduction per
-// key and head) and is issue-bound near 4 TB/s.  Here a CTA of eight warps streams 128-key tiles
-// of K and V through a three-stage cp.async ring; each warp owns 16 keys of a tile and runs
-// S = Q K^T and O += P V on mma.sync m16n8k16 (about 20 instructions per KB).  The 16-row A
-// operand carries the group's G <= 8 query heads twice: rows 0..7 hold the bf16 high part of q
-// (and of P), rows 8..15 the bf16 low part, so q and P keep ~16 mantissa bits at no extra MMA and
-// the two halves of an accumulator add up inside one thread.
-constexpr int kFmThreads = 256, kFmWarps = 8, kFmTile = 128, kFmStages = 3;
-
-__device__ __forceinline__ void fm_cp16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void fm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void fm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void fm_ldsm(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
-                                        uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void fm_ldsm_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
-                                          uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void fm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// byte offset of 16-byte chunk c of row r in an XOR-swizzled [rows][HD] bf16 tile
-template <int HD>
-__device__ __forceinline__ uint32_t fm_swz(int r, int c) {
-  return (uint32_t)(r * (HD * 2) + ((c ^ (r & 7)) << 4));
-}
-// bf16 high / low split of two fp32 values, packed for an A fragment
-__device__ __forceinline__ void fm_split(float x, float y, uint32_t& hi, uint32_t& lo) {
-  const __nv_bfloat16 xh = __float2bfloat16(x), yh = __float2bfloat16(y);
-  hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
-  lo = pack_bf16(x - __bfloat162float(xh), y - __bfloat162float(yh));
-}
 
 template <int HD, int G, bool ROPE>
 __global__ void __launch_bounds__(kFmThreads, 1) flash_decode_mma_kernel(FdArgs a) {
@@ -728,12 +312,9 @@ static size_t fm_smem_bytes() {
 template <int HD, int G, bool ROPE>
 static cudaError_t fm_launch(const FdArgs& a, cudaStream_t st, bool pdl) {
   const size_t smem = fm_smem_bytes<HD, G>();
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(flash_decode_mma_kernel<HD, G, ROPE>,
-                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDevices] = {false};
+  const cudaError_t ea = opt_in_smem(flash_decode_mma_kernel<HD, G, ROPE>, (int)smem, attr_set);
+  if (ea != cudaSuccess) return ea;
   return launch(flash_decode_mma_kernel<HD, G, ROPE>, dim3(a.n_splits, a.n_kv), dim3(kFmThreads),
                 smem, st, pdl, a);
 }
@@ -743,6 +324,22 @@ static size_t fd_counter_bytes(int n_kv) { return ((size_t)n_kv * 4 + 255) & ~(s
 }  // namespace b200
 
 using namespace b200;
+
+// Argument checks of b200_flash_decode, shared with the variant that brings its own scratch (which
+// must refuse a bad call before it enqueues anything).
+static int fd_check_args(const void* out, const void* q, const void* kcache, const void* vcache,
+                         const int* kv_len_dev, const void* workspace, int n_q, int n_kv, int hd,
+                         int64_t kv_head_stride, int64_t kv_row_stride, int n_splits) {
+  if (!out || !q || !kcache || !vcache || !kv_len_dev || !workspace) return B200_ERR_ARG;
+  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_splits <= 0 || n_splits > 1024)
+    return B200_ERR_SHAPE;
+  const int G = n_q / n_kv;
+  if ((hd != 64 && hd != 128) || (G != 1 && G != 2 && G != 4 && G != 8)) return B200_ERR_SHAPE;
+  if ((kv_row_stride & 7) != 0 || (kv_head_stride & 7) != 0 || ((uintptr_t)kcache & 15) != 0 ||
+      ((uintptr_t)vcache & 15) != 0 || ((uintptr_t)q & 15) != 0 || ((uintptr_t)workspace & 15) != 0)
+    return B200_ERR_ALIGN;
+  return B200_OK;
+}
 
 extern "C" int64_t b200_flash_decode_workspace_bytes(int n_q, int n_kv, int hd, int n_splits) {
   if (n_q <= 0 || n_kv <= 0 || n_splits <= 0) return 0;
@@ -756,12 +353,9 @@ extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_
                                  void* workspace, int n_q, int n_kv, int hd,
                                  int64_t kv_head_stride, int64_t kv_row_stride,
                                  int n_splits, float scale, int flags, b200_stream_t stream) {
-  if (!out || !q || !kcache || !vcache || !kv_len_dev || !workspace) return B200_ERR_ARG;
-  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_splits <= 0 || n_splits > 1024)
-    return B200_ERR_SHAPE;
-  if ((kv_row_stride & 7) != 0 || (kv_head_stride & 7) != 0 || ((uintptr_t)kcache & 15) != 0 ||
-      ((uintptr_t)vcache & 15) != 0 || ((uintptr_t)q & 15) != 0 || ((uintptr_t)workspace & 15) != 0)
-    return B200_ERR_ALIGN;
+  const int bad = fd_check_args(out, q, kcache, vcache, kv_len_dev, workspace, n_q, n_kv, hd,
+                                kv_head_stride, kv_row_stride, n_splits);
+  if (bad != B200_OK) return bad;
   FdArgs a{};
   a.out = out; a.q = q; a.k = (const uint16_t*)kcache; a.v = (const uint16_t*)vcache;
   a.kv_len = kv_len_dev;
@@ -774,9 +368,7 @@ extern "C" int b200_flash_decode(void* out, int out_dtype, const void* q, int q_
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  const bool simt = g_tuning[B200_TUNE_FLASH_DECODE] == 1;
-#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) \
-    e = simt ? fd_launch<HD_, G_>(a, st, pdl) : fm_launch<HD_, G_, false>(a, st, pdl); else
+#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) e = fm_launch<HD_, G_, false>(a, st, pdl); else
   FD_CASE(128, 1) FD_CASE(128, 2) FD_CASE(128, 4) FD_CASE(128, 8)
   FD_CASE(64, 1) FD_CASE(64, 2) FD_CASE(64, 4) FD_CASE(64, 8)
   return B200_ERR_SHAPE;
@@ -819,9 +411,7 @@ extern "C" int b200_rope_flash_decode(void* out, int out_dtype, const float* qkv
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  const bool simt = g_tuning[B200_TUNE_FLASH_DECODE] == 1;
-#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) \
-    e = simt ? fd_launch<HD_, G_, true>(a, st, pdl) : fm_launch<HD_, G_, true>(a, st, pdl); else
+#define FD_CASE(HD_, G_) if (hd == HD_ && G == G_) e = fm_launch<HD_, G_, true>(a, st, pdl); else
   FD_CASE(128, 1) FD_CASE(128, 2) FD_CASE(128, 4) FD_CASE(128, 8)
   FD_CASE(64, 1) FD_CASE(64, 2) FD_CASE(64, 4) FD_CASE(64, 8)
   return B200_ERR_SHAPE;
@@ -844,12 +434,11 @@ static __device__ __align__(256) unsigned char g_fd_static_scratch[kFdStaticByte
 
 // In host code `g_fd_static_scratch` is only a stand-in for the symbol, never a device
 // address; the real address is looked up once per device (with that device current).
-constexpr int kFdMaxDevices = 64;
-static void* g_fd_static_ptr[kFdMaxDevices] = {nullptr};
+static void* g_fd_static_ptr[kMaxDevices] = {nullptr};
 
 static int fd_static_address(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kFdMaxDevices) return B200_ERR_ARG;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_ERR_ARG;
   if (g_fd_static_ptr[dev] == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_fd_static_scratch) != cudaSuccess || p == nullptr)
@@ -875,6 +464,10 @@ extern "C" int b200_flash_decode_static(void* out, int out_dtype, const void* q,
   void* scratch = nullptr;
   const int rc = fd_static_address(&scratch);   // first call on a device resolves the symbol
   if (rc != B200_OK) return rc;
+  // every check b200_flash_decode makes, before anything is enqueued on the caller's stream
+  const int bad = fd_check_args(out, q, kcache, vcache, kv_len_dev, scratch, n_q, n_kv, hd,
+                                kv_head_stride, kv_row_stride, n_splits);
+  if (bad != B200_OK) return bad;
   // The array keeps whatever the previous call left; the arrival counters must start at zero.
   if (cudaMemsetAsync(scratch, 0, fd_counter_bytes(n_kv), (cudaStream_t)stream) != cudaSuccess)
     return B200_ERR_LAUNCH;

@@ -373,13 +373,8 @@ static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
   // tiles (Q, 2 x K, 2 x V, P) + 11 barriers + TMEM slot / flags + exchange values and sequence numbers
   constexpr size_t smem = (size_t)(HD / 64) * kAtomBytes * 5 + 2 * kAtomBytes + 88 + 16 +
                           (size_t)2 * kFaParts * 128 * 4 + (size_t)kFaParts * 128 * 2;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(flash_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDevices] = {false};
+  if (opt_in_smem(flash_prefill_tc_kernel<HD>, (int)smem, attr_set) != cudaSuccess) return B200_ERR_LAUNCH;
   cudaError_t e = launch(flash_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, st, pdl, mq, mk, mv, a);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }

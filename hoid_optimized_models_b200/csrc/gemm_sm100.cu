@@ -410,13 +410,8 @@ static int gemm_launch_bn(const CUtensorMap& mx, const void* w, uint64_t wrows, 
   long tiles = (long)max_tiles_m * nt;
   int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
   if (grid < 1) grid = 1;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDevices] = {false};
+  if (opt_in_smem(gemm_kernel<BN>, (int)smem, attr_set) != cudaSuccess) return B200_ERR_LAUNCH;
   cudaError_t e = launch(gemm_kernel<BN>, dim3(grid), dim3(kGemmThreads), smem, stream, pdl, mx, mw,
                          my, mr, a);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;

@@ -16,43 +16,12 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "tp_link.cuh"
 
 namespace b200 {
 
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
-
-// ---------------------------------------------------------------------------------------------
-// All-reduce fused into the GEMVs of a tensor-parallel decode step (one process per GPU, peer
-// memory over NVLink, no collective library call):
-//   * a row-parallel GEMV (o_proj, down_proj, the expert down projection) does not write y.
-//     Each finished row of its partial sum goes into slot `rank` of EVERY rank's inbox as an
-//     8-byte {fp32 value, sequence tag} pair with one 8-byte peer store: the pair arrives
-//     atomically, so the data validates itself and no fence, flag or counter is needed;
-//   * the NEXT GEMV on each rank consumes it while it stages its input vector anyway: a few
-//     reducer CTAs poll (bounded) the ranks' pairs of their slice, add them in rank order and
-//     publish the sum locally as tagged pairs again; all CTAs poll that one vector.  Every rank
-//     adds the same values in the same order, so all ranks stay bit-identical.
-// Two inbox slots alternate by sequence parity: a rank can be at most one all-reduce ahead of
-// its slowest peer, because the next one needs that peer's contribution.
-// Two measured alternatives stay selectable (B200_TUNE_TP_PROTOCOL): every CTA summing the inboxes
-// itself (world x 32 KB of L2 reads per CTA), and plain stores followed by a system fence and one
-// release flag per rank (slower than a collective library: the fence waits out the NVLink round
-// trip).
-constexpr int kTpMaxRanks = 8;
-constexpr int kTpReducers = 8;     // CTAs that sum the ranks' contributions (hierarchical mode)
-constexpr long long kTpWaitTicks = 4000000000LL;   // ~2 s: every wait on a peer is bounded
-struct TpLink {
-  float* inbox[kTpMaxRanks];        // inbox of rank p (peer-mapped): [2 slots][world][H] fp32, or
-                                    // [2 slots][world][H] {fp32 value, u32 tag} pairs (ll)
-  unsigned* flags[kTpMaxRanks];     // flags of rank p: [2 slots][world] published sequence numbers
-  int* local_counter;               // CTA arrival counter of the publishing kernel (this rank)
-  const int* seq_base;              // device scalar: sequence number of the step's first all-reduce
-  int world, rank, H;
-  int ll;                           // 1: tagged-pair protocol, 0: data + sequence flags
-  int hier;                         // tagged pairs: a few CTAs reduce, the others read their sums
-  uint4* xr;                        // local staging of the reduced vector: [2 slots][H] pairs
-};
 
 struct GemvArgs {
   const void* x;
@@ -80,59 +49,6 @@ struct GemvArgs {
 };
 
 constexpr int kMaxExpertSegs = 256;
-
-// B200_TUNE_TP_PROTOCOL: 0 default (tagged pairs summed by a few reducer CTAs), 1 data + flags,
-// 2 tagged pairs read directly by every CTA, 3 tagged pairs through the reducer CTAs
-static void tp_apply_tuning(TpLink& l) {
-  const int t = g_tuning[B200_TUNE_TP_PROTOCOL];
-  if (t == 1) l.ll = 0;
-  else if (t == 2) l.hier = 0;
-  else if (t == 3) l.hier = 1;
-}
-
-__device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
-__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-// Sum over n tagged-pair vectors (stride in uint4) of the float4 at q0: every 8-byte
-// {value, tag} pair arrives atomically, so the data itself is polled (bounded) - no flag, no fence.
-__device__ __forceinline__ float4 ll_reduce(const uint4* q0, int n, int stride, unsigned tag,
-                                            int* status) {
-  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  long long t0 = 0;
-  for (int r = 0; r < n; ++r) {
-    const uint4* q = q0 + (size_t)r * stride;
-    uint4 e0, e1;
-    int spins = 0;
-    while (true) {
-      e0 = ld_volatile_v4(q);
-      e1 = ld_volatile_v4(q + 1);
-      if (e0.y == tag && e0.w == tag && e1.y == tag && e1.w == tag) break;
-      if ((++spins & 63) == 0) {
-        // an earlier wait already gave up: do not spend the budget again
-        if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) break;
-        if (t0 == 0) t0 = clock64();
-        if (clock64() - t0 > kTpWaitTicks) {
-          if (status != nullptr) atomicExch(status, B200_ERR_TIMEOUT);
-          break;
-        }
-      }
-    }
-    v.x += __uint_as_float(e0.x); v.y += __uint_as_float(e0.z);
-    v.z += __uint_as_float(e1.x); v.w += __uint_as_float(e1.z);
-  }
-  return v;
-}
-__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void st_volatile_v2(uint2* p, uint2 v) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
-}
 
 // U    : 16-byte loads per lane per batch (two batches are in flight)
 // MINB : CTAs per SM the register budget is sized for
@@ -225,69 +141,18 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
   const bool rms_deferred = a.norm_w != nullptr && a.norm_b == nullptr && !a.norm_in_smem;
   unsigned tp_slot = 0, tp_tag = 0;
   if (TP && a.tp_in >= 0) {
-    // wait for every rank's contribution to all-reduce number seq (bounded, like every wait)
+    // all-reduce number seq: a few CTAs sum the ranks' contributions, one slice each, and publish
+    // the sums locally as tagged pairs; every CTA then polls that one vector (every wait bounded).
+    // The inbox is read once per GPU instead of once per CTA.
     const unsigned seq = (unsigned)(a.tp.seq_base[0] + a.tp_in);
     tp_slot = seq & 1u;
     tp_tag = seq + 1u;
-    if (!a.tp.ll) {
-      if (tid < a.tp.world) {
-        const volatile unsigned* f = a.tp.flags[a.tp.rank] + tp_slot * a.tp.world + tid;
-        const long long t0 = clock64();
-        int spins = 0;
-        while (*f != seq + 1u) {
-          if ((++spins & 63) == 0) {
-            // an earlier wait already gave up: do not spend the budget again
-            if (a.status != nullptr && *reinterpret_cast<volatile int*>(a.status) != 0) break;
-            if (clock64() - t0 > kTpWaitTicks) {
-              if (a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
-              break;
-            }
-          }
-        }
-        __threadfence_system();
-      }
-      __syncthreads();
-    }
-  }
-  if (TP && a.tp_in >= 0 && a.tp.ll && a.tp.hier) {
-    // A few CTAs sum the ranks' contributions, one slice each, and publish the sums locally as
-    // tagged pairs; every CTA then polls that one vector.  The inbox is read once per GPU instead
-    // of once per CTA (which costs world x 32 KB of L2 traffic per CTA).
-    const int nred = min(kTpReducers, (int)gridDim.x);
-    if ((int)blockIdx.x < nred) {
-      const int n4 = K >> 2, per = (n4 + nred - 1) / nred;
-      const int lo = blockIdx.x * per, hi = min(n4, lo + per);
-      const uint4* box = reinterpret_cast<const uint4*>(a.tp.inbox[a.tp.rank]) +
-                         (size_t)tp_slot * a.tp.world * (K >> 1);
-      uint4* dst = a.tp.xr + (size_t)tp_slot * (K >> 1);
-      for (int i = lo + tid; i < hi; i += kGemvThreads) {
-        const float4 v = ll_reduce(box + 2 * i, a.tp.world, K >> 1, tp_tag, a.status);
-        st_volatile_v4(dst + 2 * i, make_uint4(__float_as_uint(v.x), tp_tag, __float_as_uint(v.y), tp_tag));
-        st_volatile_v4(dst + 2 * i + 1, make_uint4(__float_as_uint(v.z), tp_tag, __float_as_uint(v.w), tp_tag));
-        if (a.x_out != nullptr) reinterpret_cast<float4*>(a.x_out)[i] = v;
-      }
-    }
+    tp_reduce_slice<kGemvThreads>(a.tp, tp_slot, tp_tag, a.x_out, a.status);
   }
   for (int i = tid; i < (K >> 2); i += kGemvThreads) {
     float4 v;
     if (TP && a.tp_in >= 0) {
-      if (a.tp.ll) {
-        const uint4* src = a.tp.hier
-            ? a.tp.xr + (size_t)tp_slot * (K >> 1) + 2 * i
-            : reinterpret_cast<const uint4*>(a.tp.inbox[a.tp.rank]) +
-                  (size_t)tp_slot * a.tp.world * (K >> 1) + 2 * i;
-        v = ll_reduce(src, a.tp.hier ? 1 : a.tp.world, K >> 1, tp_tag, a.status);
-      } else {
-        const float4* box = reinterpret_cast<const float4*>(a.tp.inbox[a.tp.rank]) +
-                            (size_t)tp_slot * a.tp.world * (K >> 2) + i;
-        v = __ldcg(box);                                     // peers wrote this: bypass L1
-        for (int r = 1; r < a.tp.world; ++r) {
-          const float4 o = __ldcg(box + (size_t)r * (K >> 2));
-          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-        }
-      }
-      if (a.x_out != nullptr && blockIdx.x == 0 && !(a.tp.ll && a.tp.hier))
-        reinterpret_cast<float4*>(a.x_out)[i] = v;
+      v = tp_read_reduced(a.tp, tp_slot, tp_tag, i, a.status);
     } else if (a.x_dtype == B200_F32) {
       v = reinterpret_cast<const float4*>(a.x)[i];
     } else {
@@ -414,226 +279,11 @@ __global__ void __launch_bounds__(kGemvThreads, MINB) gemv_kernel(GemvArgs a) {
       }
       if (TP && a.tp_out >= 0) {
         // partial row (+ residual on the lead rank) into slot `rank` of every rank's inbox
-        const unsigned seq = (unsigned)(a.tp.seq_base[0] + a.tp_out);
-        const size_t off = ((size_t)(seq & 1u) * a.tp.world + a.tp.rank) * a.tp.H + oi;
-        if (a.tp.ll) {
-          for (int p = 0; p < a.tp.world; ++p)
-            st_volatile_v2(reinterpret_cast<uint2*>(a.tp.inbox[p]) + off,
-                           make_uint2(__float_as_uint(v), seq + 1u));
-        } else {
-          for (int p = 0; p < a.tp.world; ++p) a.tp.inbox[p][off] = v;
-        }
+        tp_publish(a.tp, (unsigned)(a.tp.seq_base[0] + a.tp_out), oi, v);
       } else if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = v;
       else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(v);
     }
   }
-  if (TP && a.tp_out >= 0 && !a.tp.ll) {
-    // The CTA that arrives last knows every partial row of this rank has been stored.  One
-    // system fence per CTA, by the thread that signals: the barrier orders the other threads'
-    // stores before it, and the fence is cumulative.  (A fence in every warp serialises per SM
-    // on the NVLink round trip.)
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence_system();
-      const int old = atomicAdd(a.tp.local_counter, 1);
-      if (old == (int)gridDim.x - 1) {
-        *a.tp.local_counter = 0;
-        __threadfence_system();
-        const unsigned seq = (unsigned)(a.tp.seq_base[0] + a.tp_out);
-        for (int p = 0; p < a.tp.world; ++p) {
-          unsigned* f = a.tp.flags[p] + (seq & 1u) * a.tp.world + a.tp.rank;
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq + 1u) : "memory");
-        }
-      }
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Tensor-core variant of the dense GEMV (B200_TUNE_GEMV = 3; EXPERIMENTAL: its data mapping is
-// checked against an emulation of the mma fragment layout, it has not been timed yet and is not
-// the default).  The SIMT loop above spends 64 instructions per 512 bytes of weights (unpack,
-// dependent FMAs, bookkeeping); here a warp multiplies 16 rows x 64 columns of W per step with
-// four 16-byte loads per lane and four mma.sync.m16n8k16:
-//   * A = W: lane (g, tq) loads 32 contiguous bytes of row g and of row g + 8 (a quad covers one
-//     128-byte line per row).  The dot product does not care in which order k is visited, so the
-//     16 values of a lane are used as they lie: MMA m takes elements 4m .. 4m+3 of both rows;
-//   * B = x: column 0 carries the bf16 high part of x, column 1 the low part (x = hi + lo keeps
-//     ~16 mantissa bits), the other six columns are zero; lane (n, tq) reads the 16 matching
-//     values of column n from shared memory with two 16-byte loads;
-//   * D: column 0 + column 1 of row g / g + 8 meet in lane tq = 0 - no shuffle, no unpack.
-// The eight warps of a CTA split K, every warp walks all 16-row groups of the CTA over its K
-// slice, and the per-warp partial sums are added in warp order exactly as in the SIMT kernel.
-__device__ __forceinline__ void gemv_mma_step(float* c, const uint4& a0, const uint4& a1,
-                                              const uint4& b0, const uint4& b1, const uint4& x0,
-                                              const uint4& x1) {
-  // a0 / a1: elements 0..7 / 8..15 of row g; b0 / b1: the same of row g + 8; x0 / x1: the lane's
-  // 16 values of its B column
-#define B200_GEMV_MMA(A0, A1, A2, A3, B0, B1)                                                   \
-  asm volatile(                                                                                 \
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "      \
-      "{%8,%9}, {%0,%1,%2,%3};"                                                                  \
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])                                          \
-      : "r"(A0), "r"(A1), "r"(A2), "r"(A3), "r"(B0), "r"(B1))
-  B200_GEMV_MMA(a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
-  B200_GEMV_MMA(a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
-  B200_GEMV_MMA(a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
-  B200_GEMV_MMA(a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
-#undef B200_GEMV_MMA
-}
-
-template <int MINB>
-__global__ void __launch_bounds__(kGemvThreads, MINB) gemv_mma_kernel(GemvArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int K = a.K;
-  uint32_t* xh = reinterpret_cast<uint32_t*>(smem_raw);      // K/2 packed bf16 pairs: high parts
-  uint32_t* xl = xh + (K >> 1);                               // K/2 pairs: low parts
-  const int rpc16 = (a.rpc + 15) & ~15;
-  float* part = reinterpret_cast<float*>(xl + (K >> 1));      // [rpc16][kGemvWarps]
-  float* red = part + rpc16 * kGemvWarps;                     // 32
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane >> 2, tq = lane & 3;
-  const int r0 = blockIdx.x * a.rpc;
-  const int nrows = min(a.N - r0, a.rpc);
-  pdl_launch_dependents();
-  if (nrows <= 0) return;
-
-  // this warp's K slice in units of 64 columns (128 bytes per row)
-  const int units = K >> 6;
-  const int u0 = units * warp / kGemvWarps, u1 = units * (warp + 1) / kGemvWarps;
-  const int nu = u1 - u0;
-  const int ngroups = (nrows + 15) >> 4;
-  const int total = ngroups * nu;                             // steps of this warp
-  const unsigned char* wbase = reinterpret_cast<const unsigned char*>(a.w);
-  const size_t row_bytes = (size_t)a.ldw * 2;
-  auto load_step = [&](uint4* d, int s) {                     // d[0..1] row g, d[2..3] row g + 8
-    const int grp = s / nu, u = u0 + (s - grp * nu);
-    const int ra = min(grp * 16 + g, nrows - 1), rb = min(grp * 16 + g + 8, nrows - 1);
-    const unsigned char* pa = wbase + (size_t)(r0 + ra) * row_bytes + (size_t)u * 128 + tq * 32;
-    const unsigned char* pb = wbase + (size_t)(r0 + rb) * row_bytes + (size_t)u * 128 + tq * 32;
-    d[0] = ldg_stream(pa); d[1] = ldg_stream(pa + 16);
-    d[2] = ldg_stream(pb); d[3] = ldg_stream(pb + 16);
-  };
-  // weights do not depend on the previous kernel: two steps are in flight before the wait
-  uint4 w0[4], w1[4], w2[4];
-  if (0 < total) load_step(w0, 0);
-  if (1 < total) load_step(w1, 1);
-
-  pdl_wait();
-
-  // stage x (* norm weight) as bf16 high / low pairs; the RMSNorm scalar multiplies the row sums
-  float ss = 0.f;
-  for (int i = tid; i < (K >> 2); i += kGemvThreads) {
-    float4 v;
-    if (a.x_dtype == B200_F32) {
-      v = reinterpret_cast<const float4*>(a.x)[i];
-    } else {
-      const uint2 u = reinterpret_cast<const uint2*>(a.x)[i];
-      v = make_float4(bf16lo(u.x), bf16hi(u.x), bf16lo(u.y), bf16hi(u.y));
-    }
-    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    if (a.norm_w != nullptr) {
-      const uint2 u = reinterpret_cast<const uint2*>(a.norm_w)[i];
-      v.x *= bf16lo(u.x); v.y *= bf16hi(u.x); v.z *= bf16lo(u.y); v.w *= bf16hi(u.y);
-    }
-    const __nv_bfloat16 h0 = __float2bfloat16(v.x), h1 = __float2bfloat16(v.y);
-    const __nv_bfloat16 h2 = __float2bfloat16(v.z), h3 = __float2bfloat16(v.w);
-    uint2 hi, lo;
-    hi.x = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
-    hi.y = (uint32_t)__bfloat16_as_ushort(h2) | ((uint32_t)__bfloat16_as_ushort(h3) << 16);
-    lo.x = pack_bf16(v.x - __bfloat162float(h0), v.y - __bfloat162float(h1));
-    lo.y = pack_bf16(v.z - __bfloat162float(h2), v.w - __bfloat162float(h3));
-    reinterpret_cast<uint2*>(xh)[i] = hi;
-    reinterpret_cast<uint2*>(xl)[i] = lo;
-  }
-  for (int i = tid; i < rpc16 * kGemvWarps; i += kGemvThreads) part[i] = 0.f;
-  const float tot = block_sum(ss, red);                       // its barriers also publish xh / xl
-  const float out_scale = a.norm_w != nullptr ? rsqrtf(tot / (float)K + a.eps) : 1.f;
-  __syncthreads();
-
-  const uint32_t* xsel = g == 0 ? xh : xl;                    // B column of this lane (g < 2)
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
-  auto compute = [&](const uint4* d, int s) {
-    const int grp = s / nu, u = u0 + (s - grp * nu);
-    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
-    if (g < 2) {
-      const uint4* xp = reinterpret_cast<const uint4*>(xsel + ((u * 64 + tq * 16) >> 1));
-      x0 = xp[0]; x1 = xp[1];
-    }
-    gemv_mma_step(c, d[0], d[1], d[2], d[3], x0, x1);
-    if (s - grp * nu == nu - 1) {                             // last step of this group: park the sums
-      if (tq == 0) {
-        part[(grp * 16 + g) * kGemvWarps + warp] = c[0] + c[1];
-        part[(grp * 16 + g + 8) * kGemvWarps + warp] = c[2] + c[3];
-      }
-      c[0] = c[1] = c[2] = c[3] = 0.f;
-    }
-  };
-  for (int s = 0; s < total; s += 3) {                        // three register buffers in rotation
-    if (s + 2 < total) load_step(w2, s + 2);
-    compute(w0, s);
-    if (s + 1 < total) {
-      if (s + 3 < total) load_step(w0, s + 3);
-      compute(w1, s + 1);
-    }
-    if (s + 2 < total) {
-      if (s + 4 < total) load_step(w1, s + 4);
-      compute(w2, s + 2);
-    }
-  }
-  __syncthreads();
-
-  // ---- epilogue: fixed-order row sums (as in the SIMT kernel) ----
-  auto row_value = [&](int r) -> float {
-    float v = 0.f;
-#pragma unroll
-    for (int i = 0; i < kGemvWarps; ++i) v += part[r * kGemvWarps + i];
-    v *= out_scale;
-    if (a.bias != nullptr) v += __uint_as_float((uint32_t)a.bias[r0 + r] << 16);
-    return v;
-  };
-  if (a.epilogue == B200_EPI_SWIGLU) {
-    for (int t = tid; t < (nrows >> 1); t += kGemvThreads) {
-      const float gv = row_value(2 * t), uv = row_value(2 * t + 1);
-      const float o = silu_f(gv) * uv;
-      const int oi = (r0 >> 1) + t;
-      if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = o;
-      else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(o);
-    }
-  } else {
-    for (int t = tid; t < nrows; t += kGemvThreads) {
-      float v = row_value(t);
-      if (a.epilogue == B200_EPI_GELU) v = gelu_erf(v);
-      const int oi = r0 + t;
-      if (a.resid != nullptr) {
-        v += (a.resid_dtype == B200_F32)
-                 ? reinterpret_cast<const float*>(a.resid)[oi]
-                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.resid)[oi]);
-      }
-      if (a.y_dtype == B200_F32) reinterpret_cast<float*>(a.y)[oi] = v;
-      else reinterpret_cast<__nv_bfloat16*>(a.y)[oi] = __float2bfloat16(v);
-    }
-  }
-}
-
-template <int MINB>
-static cudaError_t gemv_mma_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pdl) {
-  const int wave = MINB * kNumSMs;
-  int grid = wave;
-  int rpc = (a.N + grid - 1) / grid;
-  while (rpc > 1024) { grid += wave; rpc = (a.N + grid - 1) / grid; }
-  if (swiglu && (rpc & 1)) ++rpc;
-  grid = (a.N + rpc - 1) / rpc;
-  a.rpc = rpc;
-  const size_t smem = (size_t)a.K * 4 + (size_t)((rpc + 15) & ~15) * kGemvWarps * 4 + 128;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemv_mma_kernel<MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         200 * 1024);
-    attr_set = true;
-  }
-  return launch(gemv_mma_kernel<MINB>, dim3(grid), dim3(kGemvThreads), smem, st, pdl, a);
 }
 
 template <int U, int MINB, int MODE = 0, bool TP = false>
@@ -648,12 +298,9 @@ static cudaError_t gemv_launch(GemvArgs a, bool swiglu, cudaStream_t st, bool pd
   grid = (a.N + rpc - 1) / rpc;
   a.rpc = rpc;
   const size_t smem = (size_t)a.K * 4 + (size_t)rpc * kGemvWarps * 4 + 128;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemv_kernel<U, MINB, MODE, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         200 * 1024);
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDevices] = {false};
+  const cudaError_t ea = opt_in_smem(gemv_kernel<U, MINB, MODE, TP>, 200 * 1024, attr_set);
+  if (ea != cudaSuccess) return ea;
   return launch(gemv_kernel<U, MINB, MODE, TP>, dim3(grid, n_slots), dim3(kGemvThreads), smem, st, pdl, a);
 }
 
@@ -692,9 +339,6 @@ extern "C" int b200_gemv_bf16(const void* x, int x_dtype, const void* w, void* y
   switch (g_tuning[B200_TUNE_GEMV]) {
     case 1: e = gemv_launch<4, 4>(a, sw, st, pdl); break;
     case 2: e = gemv_launch<4, 3>(a, sw, st, pdl); break;
-    case 3:   // experimental tensor-core loop; no LayerNorm prologue there
-      e = norm_beta != nullptr ? gemv_launch<8, 2>(a, sw, st, pdl) : gemv_mma_launch<2>(a, sw, st, pdl);
-      break;
     default: e = gemv_launch<8, 2>(a, sw, st, pdl); break;
   }
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
@@ -753,7 +397,7 @@ static int moe_down_impl(const b200::TpLink* link, int tp_out, int* status,
   if (link != nullptr) {
     if (hidden != link->H) return B200_ERR_SHAPE;
     a.tp = *link; a.tp_out = tp_out; a.status = status;
-    tp_apply_tuning(a.tp);
+    a.tp.wait_ticks = wait_ticks_from_tuning();
     e = gemv_launch<8, 2, 2, true>(a, false, (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0);
   } else {
     e = gemv_launch<8, 2, 2>(a, false, (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0);
@@ -776,14 +420,13 @@ namespace {
 struct TpContext { b200::TpLink link; void* local; bool used; };
 constexpr int kTpMaxContexts = 16;   // links per process (an engine holds one for its lifetime)
 TpContext g_tp[kTpMaxContexts];
-constexpr size_t kTpAlign = 256;
-size_t tp_flag_bytes(int world) { return ((size_t)2 * world * 4 + kTpAlign - 1) & ~(kTpAlign - 1); }
+constexpr size_t kTpAlign = 256;   // the buffer starts with one aligned block of scalars (seq_base)
 }  // namespace
 
-/* Bytes of the per-rank communication buffer: [flags | arrival counter + seq_base | inbox]. */
+/* Bytes of the per-rank communication buffer: [scalars | inbox pairs | reduced-vector pairs]. */
 extern "C" int64_t b200_tp_buffer_bytes(int world, int H) {
   if (world <= 0 || world > kTpMaxRanks || H <= 0) return 0;
-  return (int64_t)(tp_flag_bytes(world) + kTpAlign + (size_t)2 * world * H * 8 + (size_t)2 * H * 8);
+  return (int64_t)(kTpAlign + (size_t)2 * world * H * 8 + (size_t)2 * H * 8);
 }
 
 /* cudaMalloc + zero the communication buffer (set-up time only) and return its IPC handle. */
@@ -819,19 +462,22 @@ extern "C" int b200_tp_create(void* const* bufs, int world, int rank, int H) {
   TpLink& l = g_tp[id].link;
   for (int p = 0; p < world; ++p) {
     if (!bufs[p]) return B200_ERR_ARG;
-    l.flags[p] = (unsigned*)bufs[p];
-    l.inbox[p] = (float*)((char*)bufs[p] + tp_flag_bytes(world) + kTpAlign);
+    l.inbox[p] = (float*)((char*)bufs[p] + kTpAlign);
   }
-  char* own = (char*)bufs[rank] + tp_flag_bytes(world);
-  l.local_counter = (int*)own;
-  l.seq_base = (const int*)(own + 64);
-  l.world = world; l.rank = rank; l.H = H; l.ll = 1;
-  l.hier = 1;
+  l.seq_base = (const int*)((char*)bufs[rank] + 64);
+  l.world = world; l.rank = rank; l.H = H;
   l.xr = (uint4*)((char*)l.inbox[rank] + (size_t)2 * world * H * 8);
+  l.wait_ticks = kDefaultWaitTicks;
   g_tp[id].local = bufs[rank];
   g_tp[id].used = true;
   return id;
 }
+
+namespace b200 {
+const TpLink* tp_link_get(int ctx) {
+  return (ctx >= 0 && ctx < kTpMaxContexts && g_tp[ctx].used) ? &g_tp[ctx].link : nullptr;
+}
+}  // namespace b200
 
 __global__ void tp_advance_kernel(int* seq_base, int inc) {
   b200::pdl_launch_dependents();
@@ -875,7 +521,7 @@ extern "C" int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, i
   a.expert_lo = 0; a.n_local = 0;
   a.tp = l; a.tp_in = tp_in; a.tp_out = tp_out;
   a.x_out = (float*)x_out; a.status = status;
-  tp_apply_tuning(a.tp);
+  a.tp.wait_ticks = wait_ticks_from_tuning();
   cudaError_t e = gemv_launch<8, 2, 0, true>(a, epilogue == B200_EPI_SWIGLU, (cudaStream_t)stream,
                                     (flags & B200_FLAG_PDL) != 0);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;

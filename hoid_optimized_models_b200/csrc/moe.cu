@@ -12,9 +12,11 @@ namespace b200 {
 constexpr int kMaxEPL = 8;  // experts per lane -> E <= 256
 
 // Softmax + top-k of one token's logits by one warp: v[j] is the logit of expert lane + 32 j
-// (-inf beyond E).  Shared by the stand-alone router and the fused router GEMV.
+// (-inf beyond E).  A non-finite logit (NaN, +inf) would turn every probability into NaN and no
+// comparison below would ever hold; such probabilities are replaced by zero, so the ids written
+// are always valid expert numbers, and the caller's status word (nullable) gets B200_ERR_NUMERIC.
 __device__ __forceinline__ void router_select(const float* v, int epl, int top_k, int round_bf16,
-                                              int lane, int* ids, float* wts) {
+                                              int lane, int* ids, float* wts, int* status) {
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < kMaxEPL; ++j) mx = fmaxf(mx, v[j]);
@@ -28,8 +30,14 @@ __device__ __forceinline__ void router_select(const float* v, int epl, int top_k
   }
   sum = warp_sum(sum);
   const float inv = 1.f / sum;
+  bool bad = false;
 #pragma unroll
-  for (int j = 0; j < kMaxEPL; ++j) p[j] *= inv;   // softmax probabilities
+  for (int j = 0; j < kMaxEPL; ++j) {
+    p[j] *= inv;                                   // softmax probabilities
+    if (!(p[j] >= 0.f && p[j] <= 1.f)) { p[j] = 0.f; bad = true; }
+  }
+  if (__any_sync(0xffffffffu, bad) && lane == 0 && status != nullptr)
+    atomicExch(status, B200_ERR_NUMERIC);
 
   float sel_w = 0.f;   // lane k keeps the k-th selection
   int sel_i = 0;
@@ -66,7 +74,7 @@ __device__ __forceinline__ void router_select(const float* v, int epl, int top_k
 
 __global__ void __launch_bounds__(128) moe_router_kernel(int* ids, float* wts, const void* logits,
                                                          int logits_dtype, int s, int E, int top_k,
-                                                         int round_bf16) {
+                                                         int round_bf16, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -84,90 +92,8 @@ __global__ void __launch_bounds__(128) moe_router_kernel(int* ids, float* wts, c
                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[i]);
     }
   }
-  router_select(v, epl, top_k, round_bf16, lane, ids + (size_t)t * top_k, wts + (size_t)t * top_k);
-}
-
-// Decode-time router in one launch: logits = W_router . rmsnorm(x) (one warp per expert row),
-// then the CTA that arrives last runs the selection above on the finished logits.
-constexpr int kRgWarps = 8;
-__global__ void __launch_bounds__(kRgWarps * 32) moe_router_gemv_kernel(
-    int* ids, float* wts, float* logits, int* counter, const float* x, const uint16_t* norm_w,
-    float eps, const uint16_t* w, int E, int H, int top_k, int round_bf16) {
-  extern __shared__ __align__(16) float rg_x[];      // H floats: x * norm_w
-  __shared__ float red[32];
-  __shared__ int s_last;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  pdl_launch_dependents();
-  // the router weights do not depend on the previous kernel: the first 4 KB of the warp's row
-  // (all of it for H <= 2048) is requested before the wait, eight loads in flight per lane
-  const int row = blockIdx.x * kRgWarps + warp;
-  const int nchunk = H >> 3;                          // 16-byte chunks per row
-  const uint16_t* wr = w + (size_t)(row < E ? row : 0) * H;
-  uint4 wv[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int c = j * 32 + lane;
-    wv[j] = c < nchunk ? ldg_stream(wr + c * 8) : make_uint4(0, 0, 0, 0);
-  }
-  pdl_wait();
-  float ss = 0.f;
-  for (int i = tid; i < (H >> 2); i += kRgWarps * 32) {
-    float4 v = reinterpret_cast<const float4*>(x)[i];
-    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    if (norm_w != nullptr) {
-      const uint2 u = reinterpret_cast<const uint2*>(norm_w)[i];
-      v.x *= bf16lo(u.x); v.y *= bf16hi(u.x); v.z *= bf16lo(u.y); v.w *= bf16hi(u.y);
-    }
-    reinterpret_cast<float4*>(rg_x)[i] = v;
-  }
-  const float tot = block_sum(ss, red);              // its barriers also publish rg_x
-  const float scale = norm_w != nullptr ? rsqrtf(tot / (float)H + eps) : 1.f;
-  if (row < E) {
-    float acc = 0.f;
-    auto fma8 = [&](const uint4& wq, int c) {
-      float f[8];
-      unpack8(wq, f);
-      const float4 a = reinterpret_cast<const float4*>(rg_x)[2 * c];
-      const float4 b = reinterpret_cast<const float4*>(rg_x)[2 * c + 1];
-      acc = fmaf(f[0], a.x, acc); acc = fmaf(f[1], a.y, acc);
-      acc = fmaf(f[2], a.z, acc); acc = fmaf(f[3], a.w, acc);
-      acc = fmaf(f[4], b.x, acc); acc = fmaf(f[5], b.y, acc);
-      acc = fmaf(f[6], b.z, acc); acc = fmaf(f[7], b.w, acc);
-    };
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = j * 32 + lane;
-      if (c < nchunk) fma8(wv[j], c);
-    }
-    for (int c0 = 256; c0 < nchunk; c0 += 256) {      // rows longer than 4 KB
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int c = c0 + j * 32 + lane;
-        wv[j] = c < nchunk ? ldg_stream(wr + c * 8) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int c = c0 + j * 32 + lane;
-        if (c < nchunk) fma8(wv[j], c);
-      }
-    }
-    acc = warp_sum(acc) * scale;
-    if (lane == 0) logits[row] = acc;
-  }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) s_last = (atomicAdd(counter, 1) == (int)gridDim.x - 1);
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  if (warp == 0) {
-    const int epl = E >> 5;
-    float v[kMaxEPL];
-#pragma unroll
-    for (int j = 0; j < kMaxEPL; ++j) v[j] = j < epl ? __ldcg(logits + lane + 32 * j) : -INFINITY;
-    router_select(v, epl, top_k, round_bf16, lane, ids, wts);
-    if (lane == 0) *counter = 0;                     // ready for the next launch
-  }
+  router_select(v, epl, top_k, round_bf16, lane, ids + (size_t)t * top_k, wts + (size_t)t * top_k,
+                status);
 }
 
 // ---------------------------------------------------------------------------
@@ -179,7 +105,16 @@ __global__ void __launch_bounds__(kRgWarps * 32) moe_router_gemv_kernel(
 //           expert e, which keeps equal keys in their original order.
 constexpr int kSortBlock = 1024;  // entries per block
 
-__global__ void __launch_bounds__(256) moe_hist_kernel(int* hist, const int* ids, int pairs, int E) {
+// An id outside [0, E) (a caller error) must not index shared memory: it is sorted as expert 0,
+// consistently in both passes, and the status word (nullable) receives B200_ERR_ARG.
+__device__ __forceinline__ int moe_checked_id(int id, int E, int* status) {
+  if ((unsigned)id < (unsigned)E) return id;
+  if (status != nullptr) atomicExch(status, B200_ERR_ARG);
+  return 0;
+}
+
+__global__ void __launch_bounds__(256) moe_hist_kernel(int* hist, const int* ids, int pairs, int E,
+                                                       int* status) {
   extern __shared__ int sh[];
   pdl_launch_dependents();
   pdl_wait();
@@ -187,7 +122,7 @@ __global__ void __launch_bounds__(256) moe_hist_kernel(int* hist, const int* ids
   __syncthreads();
   const int base = blockIdx.x * kSortBlock;
   for (int i = threadIdx.x; i < kSortBlock && base + i < pairs; i += blockDim.x)
-    atomicAdd(&sh[ids[base + i]], 1);
+    atomicAdd(&sh[moe_checked_id(ids[base + i], E, status)], 1);
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) hist[blockIdx.x * E + e] = sh[e];
 }
@@ -223,7 +158,7 @@ __global__ void __launch_bounds__(256) moe_place_kernel(int* order, int* inv, co
   pdl_wait();
   const int base = blockIdx.x * kSortBlock;
   const int n = min(kSortBlock, pairs - base);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = ids[base + i];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = moe_checked_id(ids[base + i], E, nullptr);
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int pos = hist[blockIdx.x * E + e];
@@ -288,31 +223,15 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(uint4* out, const uint
 using namespace b200;
 
 extern "C" int b200_moe_router(int* ids, float* wts, const void* logits, int logits_dtype, int s,
-                               int E, int top_k, int round_bf16, int flags, b200_stream_t stream) {
+                               int E, int top_k, int round_bf16, int* status, int flags,
+                               b200_stream_t stream) {
   if (!ids || !wts || !logits) return B200_ERR_ARG;
   if (s <= 0 || E <= 0 || (E & 31) != 0 || E > 32 * kMaxEPL || top_k <= 0 || top_k > 32 ||
       top_k > E)
     return B200_ERR_SHAPE;
   cudaError_t e = launch(moe_router_kernel, dim3((s + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
                          (flags & B200_FLAG_PDL) != 0, ids, wts, logits, logits_dtype, s, E, top_k,
-                         round_bf16);
-  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
-}
-
-extern "C" int b200_moe_router_gemv(int* ids, float* wts, float* logits, int* counter,
-                                    const float* x, const void* norm_w, float eps,
-                                    const void* w_router, int E, int H, int top_k, int round_bf16,
-                                    int flags, b200_stream_t stream) {
-  if (!ids || !wts || !logits || !counter || !x || !w_router) return B200_ERR_ARG;
-  if (E <= 0 || (E & 31) != 0 || E > 32 * kMaxEPL || top_k <= 0 || top_k > 32 || top_k > E ||
-      H <= 0 || (H & 7) != 0 || H > 12288)
-    return B200_ERR_SHAPE;
-  if (((uintptr_t)x & 15) != 0 || ((uintptr_t)w_router & 15) != 0) return B200_ERR_ALIGN;
-  const int grid = (E + kRgWarps - 1) / kRgWarps;
-  cudaError_t e = launch(moe_router_gemv_kernel, dim3(grid), dim3(kRgWarps * 32), (size_t)H * 4,
-                         (cudaStream_t)stream, (flags & B200_FLAG_PDL) != 0, ids, wts, logits,
-                         counter, x, (const uint16_t*)norm_w, eps, (const uint16_t*)w_router, E, H,
-                         top_k, round_bf16);
+                         round_bf16, status);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
@@ -322,7 +241,8 @@ extern "C" int64_t b200_moe_permute_workspace_bytes(int pairs, int E) {
 }
 
 extern "C" int b200_moe_permute(int* order, int* inv, int* offsets, const int* ids, int pairs,
-                                int E, void* workspace, int flags, b200_stream_t stream) {
+                                int E, void* workspace, int* status, int flags,
+                                b200_stream_t stream) {
   if (!order || !offsets || !ids || !workspace) return B200_ERR_ARG;
   if (pairs <= 0 || E <= 0 || E > 4096) return B200_ERR_SHAPE;
   const int nblocks = (pairs + kSortBlock - 1) / kSortBlock;
@@ -330,7 +250,7 @@ extern "C" int b200_moe_permute(int* order, int* inv, int* offsets, const int* i
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   int* hist = (int*)workspace;
   if (launch(moe_hist_kernel, dim3(nblocks), dim3(256), (size_t)E * 4, st, pdl, hist, ids, pairs,
-             E) != cudaSuccess)
+             E, status) != cudaSuccess)
     return B200_ERR_LAUNCH;
   if (launch(moe_scan_kernel, dim3(1), dim3(256), (size_t)(E + 1) * 4, st, pdl, hist, offsets,
              nblocks, E) != cudaSuccess)

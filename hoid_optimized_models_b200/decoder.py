@@ -5,12 +5,16 @@ Mirrors the reference engines' interface — `capture()`, `step(tok, pos)`,
 (models/llama31-8b/llama31_optimized.py:317-520, models/qwen3-4b/qwen3_optimized.py:312-517)
 — but with a different dataflow:
 
-decode (5 launches per layer, fp32 activations, one CUDA graph for the whole step)
-    gemv[rmsnorm prologue, packed q|k|v] -> rope_flash_decode (QK-norm + RoPE + cache append in
-    the attention prologue, LSE combine fused)
-    -> gemv[o_proj, + residual] -> gemv[rmsnorm prologue, gate|up interleaved, SwiGLU epilogue]
-    -> gemv[down_proj, + residual];  lm_head gemv (fp32 logits) -> argmax -> greedy_select,
-    which feeds the next step's token and position on the device.
+decode (fp32 activations, one CUDA graph for the whole step)
+    per layer: gemv[rmsnorm prologue, packed q|k|v] -> rope_flash_decode (QK-norm + RoPE + cache
+    append in the attention prologue, LSE combine fused) -> gemv[o_proj, + residual] ->
+    gemv[rmsnorm prologue, gate|up interleaved, SwiGLU epilogue] -> gemv[down_proj, + residual];
+    then lm_head gemv (fp32 logits) -> argmax -> greedy_select, which feeds the next step's token
+    and position on the device.  Dense models run all layers as ONE persistent launch
+    (ops.decode_layers: the same five phases, resident CTAs, weights streaming across the phase
+    boundaries, the tensor-parallel exchange inside the kernel): 5 launches per step instead of
+    5 per layer.  The launch-per-phase path stays for the MoE model, for the NCCL all-reduce
+    variant and for looking at per-layer hidden states (`collect`).
 
 prefill (bf16 activations and residual stream, the reference's own precision; an fp32 stream
 was measured to change the distance from an fp32 model by under 10% at the Llama widths, where
@@ -42,7 +46,7 @@ class DenseDecoder:
                  device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None,
                  n_splits: Optional[int] = None, max_new_tokens: int = 1024,
                  free_source_weights: bool = False, fused_allreduce: bool = True,
-                 fuse_rope: bool = True):
+                 fuse_rope: bool = True, fused_layers: bool = True):
         self.moe = cfg.n_experts > 0   # expert parallelism: attention replicated, experts sharded
         tpart.check_divisible(cfg, tp_size)
         self.cfg, self.device, self.max_seq = cfg, torch.device(device), max_seq
@@ -144,8 +148,27 @@ class DenseDecoder:
         self._prefill_graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.fuse_rope = fuse_rope
-        self.launches_per_step = (1 + ((8 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
-                                  + (1 if self.link is not None else 0))   # + sequence advance
+        # all layers of a dense model's step as one persistent launch
+        self.plan = None
+        if (fused_layers and fuse_rope and not self.moe and (tp_size == 1 or self.link is not None)
+                and self._fused_layers_supported()):
+            self.plan = ops.decode_layers_plan(
+                self.wqkv, self.wo, self.wgu, self.wd, self.ln1, self.ln2, self.kv, self.qn, self.kn,
+                self.h, self.qkv, self.attn, self.act,
+                tp_ctx=self.link.ctx if self.link is not None else -1)
+        if self.plan is not None:
+            self.launches_per_step = 5 + (1 if self.link is not None else 0)
+        else:
+            self.launches_per_step = (1 + ((8 if self.moe else 6) - int(fuse_rope)) * cfg.layers + 3
+                                      + (1 if self.link is not None else 0))   # + sequence advance
+
+    def _fused_layers_supported(self) -> bool:
+        """Shapes the persistent kernel takes (include/b200ops.h, b200_decode_layers)."""
+        H, sms = self.cfg.hidden, 148
+        dims_ok = all(d % 256 == 0 and d <= 16384 for d in (H, self.q_size, self.inter))
+        rows = max(-(-(self.q_size + 2 * self.kv_size) // sms), -(-H // sms), -(-2 * self.inter // sms) + 1)
+        return (dims_ok and rows <= 256 and self.n_kv * self.n_splits <= sms
+                and self.cfg.head_dim in (64, 128) and self.n_q // self.n_kv in (1, 2, 4, 8))
 
     @classmethod
     def from_checkpoint(cls, cfg: DecoderConfig, weights_dir: str, max_seq: int, device="cuda",
@@ -190,6 +213,9 @@ class DenseDecoder:
         lead = self.tp_rank == 0
         ops.embed_gather(self.h, self.embed, self.tok)
         h, h2 = self.h, self.h2
+        if self.plan is not None and collect is None:
+            self._step_fused_layers()
+            return
         if self.link is not None:
             if self.moe:
                 self._step_fused_ep(collect)
@@ -240,6 +266,27 @@ class DenseDecoder:
                                                      group=self.group)
             ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand_all)
         else:
+            ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
+
+    def _step_fused_layers(self) -> None:
+        """All layers in one persistent launch, then the head.  Under tensor parallelism the
+        kernel leaves the last all-reduce (2 * layers - 1) to the lm_head GEMV, which reduces it
+        while staging its input, exactly as in _step_fused_tp."""
+        cfg, L = self.cfg, self.cfg.layers
+        ops.decode_layers(self.plan, self.cos, self.sin, self.kv_len, self.fd_ws, self.n_q,
+                          self.n_kv, self.n_splits, self.scale, cfg.eps)
+        if self.link is not None:
+            ctx = self.link.ctx
+            ops.gemv_tp_consume(self.logits, self.lm_head, ctx, 2 * L - 1, x_out=self.h,
+                                norm_w=self.final_norm_w, eps=cfg.eps)
+            ops.tp_advance(ctx, 2 * L)
+            ops.argmax(self.cand, self.logits, self.am_ws, idx_base=self.tp_rank * self.vocab_local)
+            torch.distributed.all_gather_into_tensor(self.cand_all, self.cand.view(1, 2),
+                                                     group=self.group)
+            ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand_all)
+        else:
+            ops.gemv(self.logits, self.h, self.lm_head, norm_w=self.final_norm_w, eps=cfg.eps)
+            ops.argmax(self.cand, self.logits, self.am_ws, idx_base=0)
             ops.greedy_advance(self.tok, self.state, self.tok_log, self.cand)
 
     def _step_fused_tp(self, collect: Optional[list] = None) -> None:
@@ -322,7 +369,27 @@ class DenseDecoder:
         self.state.copy_(saved[0]); self.tok.copy_(saved[1]); self.tok_log.copy_(saved[2])
         self.kv[:, :, :, :warmup + 1].copy_(saved[3])
 
+    def check_status(self) -> None:
+        """Raises if a kernel reported through the status word since the last check (a bounded
+        wait that ran out, a non-finite router logit).  Synchronises; under tensor / expert
+        parallelism the ranks agree on the worst code first, so that all of them stop together
+        instead of diverging."""
+        word = ops.status_word(self.device)
+        if self.tp_size > 1:
+            worst = word.clone()
+            torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MIN, group=self.group)
+            if int(worst.item()) != 0:
+                word.copy_(worst)
+        try:
+            ops.check_status(self.device)
+        except Exception:
+            if self.plan is not None:
+                ops.reset_decode_plan(self.plan)     # its barrier word may hold a partial count
+            raise
+
     def set_step(self, tok: int, pos: int, generated: int = 0) -> None:
+        if pos < 0 or pos + 1 > self.max_seq:
+            raise ValueError(f"position {pos} does not fit the cache of {self.max_seq} rows")
         self.tok.fill_(tok)
         self.state.copy_(torch.tensor([pos, pos + 1, generated, 0], dtype=torch.int32),
                          non_blocking=False)
@@ -335,6 +402,30 @@ class DenseDecoder:
         else:
             self.step_static()
         return self.logits
+
+    def step_host(self, tok: int, pos: int) -> int:
+        """One host-driven decode step, the way a serving loop that samples on the host uses the
+        engine: the token and the step state go up from pinned host memory (20 bytes), the step
+        runs (graph replay once captured), the selected token comes back (4 bytes) and the call
+        returns it after synchronising."""
+        if pos < 0 or pos + 1 > self.max_seq:
+            raise ValueError(f"position {pos} does not fit the cache of {self.max_seq} rows")
+        if not hasattr(self, "_pin"):
+            self._pin = (torch.zeros(1, dtype=torch.int32).pin_memory(),
+                         torch.zeros(4, dtype=torch.int32).pin_memory(),
+                         torch.zeros(1, dtype=torch.int32).pin_memory())
+        tok_h, state_h, out_h = self._pin
+        tok_h[0] = tok
+        state_h[0], state_h[1], state_h[2], state_h[3] = pos, pos + 1, 0, 0
+        self.tok.copy_(tok_h, non_blocking=True)
+        self.state.copy_(state_h, non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step_static()
+        out_h.copy_(self.tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return int(out_h[0])
 
     # ------------------------------------------------------------------ prefill
     def _prefill_buffers(self, P: int) -> Dict[str, torch.Tensor]:
@@ -416,7 +507,9 @@ class DenseDecoder:
         else:
             self._prefill_launches(e, P, collect, collect_router)
         self.last_prefill_hidden = e["x"]
-        return int(self.tok.item())
+        first = int(self.tok.item())
+        self.check_status()
+        return first
 
     def _prefill_launches(self, e: Dict[str, torch.Tensor], P: int, collect: Optional[list],
                           collect_router: Optional[list]) -> None:
@@ -482,6 +575,11 @@ class DenseDecoder:
         P = ids.numel()
         if n_new > self.tok_log.numel() + 1:
             raise ValueError("n_new exceeds max_new_tokens")
+        if P + n_new - 1 > self.max_seq:
+            # the kernels guard the cache write but attend to kv_len rows: past max_seq that
+            # would read beyond the cache
+            raise ValueError(f"{P} prompt + {n_new - 1} decode positions exceed the cache of "
+                             f"{self.max_seq} rows")
         first = self.prefill(ids)
         out = [first]
         self.set_step(first, P, 0)
@@ -494,6 +592,7 @@ class DenseDecoder:
                 out.append(int(self.tok.item()))
         if not sync_every_step:
             out.extend(self.tok_log[:n_new - 1].tolist())
+        self.check_status()
         return out
 
 

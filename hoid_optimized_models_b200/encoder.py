@@ -129,8 +129,8 @@ class XlmrEncoder:
             self.forward_static()
         if self.dp_size > 1:
             torch.distributed.all_gather_into_tensor(self.pooled_all, self.pooled, group=self.group)
-            return self.pooled_all
-        return self.pooled
+        ops.check_status(self.device)        # a bounded wait inside a tensor-core kernel ran out
+        return self.pooled_all if self.dp_size > 1 else self.pooled
 
 
 class OptimizedBgeM3(XlmrEncoder):

@@ -121,6 +121,68 @@ def tp_advance(ctx: int, inc: int) -> None:
     check(_lib.lib().b200_tp_advance(ctx, inc, _flags(), _stream()), "b200_tp_advance")
 
 
+# ----------------------------------------------------------------------------- whole-step kernel
+class DecodePlan:
+    """Phase table of b200_decode_layers on the device, its synchronisation word, and references
+    to every tensor the table points at (so that none of them is freed while the plan lives)."""
+
+    def __init__(self, table: Tensor, sync: Tensor, n_layers: int, tp_ctx: int, keep: tuple):
+        self.table, self.sync, self.n_layers, self.tp_ctx, self.keep = table, sync, n_layers, tp_ctx, keep
+
+
+def decode_layers_plan(wqkv, wo, wgu, wd, ln1, ln2, kv: Tensor, qn, kn, h: Tensor, qkv: Tensor,
+                       attn: Tensor, act: Tensor, tp_ctx: int = -1) -> DecodePlan:
+    """Set-up of the persistent decode kernel: per-layer weight lists (packed q|k|v, o_proj,
+    interleaved gate|up, down; RMSNorm weights; QK-norm weights or lists of None), the KV cache
+    [layers, 2, n_kv, max_seq, hd] and the fp32 activation vectors of the step."""
+    import ctypes as C
+    L = len(wqkv)
+    for t in (*wqkv, *wo, *wgu, *wd, *ln1, *ln2):
+        _bf16(t, "weights")
+    for t in (h, qkv, attn, act):
+        if t.dtype != torch.float32:
+            raise TypeError("decode activations must be float32")
+    _bf16(kv, "kv")
+
+    def arr(ts):
+        return (C.c_void_p * L)(*[_ptr(t) for t in ts])
+
+    has_qk = qn[0] is not None
+    lib = _lib.lib()
+    dev = h.device
+    table = torch.zeros(lib.b200_decode_layers_plan_bytes(L), dtype=torch.uint8, device=dev)
+    sync = torch.zeros(lib.b200_decode_layers_sync_bytes() // 4, dtype=torch.int32, device=dev)
+    H = h.numel()
+    q_size = attn.numel()
+    kv_size = (qkv.numel() - q_size) // 2
+    check(lib.b200_decode_layers_plan(
+        _ptr(table), L, arr(wqkv), arr(wo), arr(wgu), arr(wd), arr(ln1), arr(ln2),
+        arr([kv[i, 0] for i in range(L)]), arr([kv[i, 1] for i in range(L)]),
+        arr(qn) if has_qk else None, arr(kn) if has_qk else None,
+        _ptr(h), _ptr(qkv), _ptr(attn), _ptr(act), H, q_size, kv_size, act.numel(), tp_ctx),
+        "b200_decode_layers_plan")
+    return DecodePlan(table, sync, L, tp_ctx, (wqkv, wo, wgu, wd, ln1, ln2, kv, qn, kn, h, qkv, attn, act))
+
+
+def decode_layers(plan: DecodePlan, cos: Tensor, sin: Tensor, kv_len: Tensor, workspace: Tensor,
+                  n_q: int, n_kv: int, n_splits: int, scale: float, eps: float) -> None:
+    """Every layer of one decode step in one launch: h (the embedded token) -> h after the last
+    layer, the new position's k / v rows appended to the cache.  With a tensor-parallel plan the
+    last all-reduce (number 2 * layers - 1) is left for `gemv_tp_consume` to reduce."""
+    wqkv, kv, qkv, attn = plan.keep[0], plan.keep[6], plan.keep[10], plan.keep[11]
+    hd = kv.shape[-1]
+    check(_lib.lib().b200_decode_layers(
+        _ptr(plan.table), plan.n_layers, _ptr(qkv), _ptr(attn), _ptr(cos), _ptr(sin), _ptr(kv_len),
+        _ptr(workspace), _ptr(plan.sync), n_q, n_kv, hd, kv.stride(-3), kv.stride(-2),
+        kv.shape[-2], n_splits, scale, eps, plan.tp_ctx, status_word(attn.device).data_ptr(),
+        _flags(), _stream()), "b200_decode_layers")
+
+
+def reset_decode_plan(plan: DecodePlan) -> None:
+    """After a B200_ERR_TIMEOUT: the grid barrier word may hold a partial count."""
+    plan.sync.zero_()
+
+
 # ----------------------------------------------------------------------------- norms
 def _rmsnorm_call(resid_out, norm_out, a, b, w, eps):
     _bf16(w, "w")
@@ -257,7 +319,8 @@ _STATUS = {}
 
 
 def status_word(device) -> Tensor:
-    """Device int32 that tensor-core kernels set to B200_ERR_TIMEOUT if a bounded wait expires."""
+    """Device int32 the kernels report through: B200_ERR_TIMEOUT when a bounded wait expired,
+    B200_ERR_NUMERIC / B200_ERR_ARG when the router or the expert sort met a bad input."""
     key = torch.device(device).index or 0
     if key not in _STATUS:
         _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
@@ -265,11 +328,12 @@ def status_word(device) -> Tensor:
 
 
 def check_status(device) -> None:
-    """Synchronising check of the status word (tests and debugging only)."""
+    """Synchronising check of the status word: the engines call it wherever they synchronise with
+    the device anyway (after a prefill, when the generated tokens are read back)."""
     v = int(status_word(device).item())
     if v != 0:
         status_word(device).zero_()
-        check(v, "tensor-core kernel (device status)")
+        check(v, "device status word")
 
 
 @torch.library.custom_op("b200::gemm", mutates_args=("y",))
@@ -318,28 +382,8 @@ def moe_router(ids: Tensor, wts: Tensor, logits: Tensor, round_bf16: bool = Fals
     s, E = logits.shape[-2] if logits.dim() > 1 else 1, logits.shape[-1]
     k = ids.numel() // s
     check(_lib.lib().b200_moe_router(_ptr(ids), _ptr(wts), _ptr(logits), _dt(logits), s, E, k,
-                                     1 if round_bf16 else 0, _flags(), _stream()), "b200_moe_router")
-
-
-@torch.library.custom_op("b200::moe_router_gemv", mutates_args=("ids", "wts", "logits", "counter"))
-def moe_router_gemv(ids: Tensor, wts: Tensor, logits: Tensor, counter: Tensor, x: Tensor,
-                    w_router: Tensor, norm_w: Optional[Tensor] = None, eps: float = 0.0,
-                    round_bf16: bool = False) -> None:
-    """Decode-time router in one launch: logits = w_router . rmsnorm(x), then top-k as moe_router.
-    counter is one int32 that is zero before the first call.  Measured on B200 at E = 128,
-    H = 2048 the 16-CTA launch with its last-arriver selection is slower than the full-width GEMV
-    followed by moe_router (2.63 against 2.51 ms per Qwen3-30B-A3B decode step), so the engine
-    keeps the pair; the op stays for hosts where launches cost more."""
-    _bf16(w_router, "w_router"); _bf16(norm_w, "norm_w")
-    if x.dtype != torch.float32 or logits.dtype != torch.float32:
-        raise TypeError("x and logits must be float32")
-    if ids.dtype != torch.int32 or wts.dtype != torch.float32 or counter.dtype != torch.int32:
-        raise TypeError("ids / counter must be int32 and wts float32")
-    E, H = w_router.shape
-    check(_lib.lib().b200_moe_router_gemv(
-        _ptr(ids), _ptr(wts), _ptr(logits), _ptr(counter), _ptr(x), _ptr(norm_w), eps,
-        _ptr(w_router), E, H, ids.numel(), 1 if round_bf16 else 0, _flags(), _stream()),
-        "b200_moe_router_gemv")
+                                     1 if round_bf16 else 0, status_word(ids.device).data_ptr(),
+                                     _flags(), _stream()), "b200_moe_router")
 
 
 def moe_permute_workspace(pairs: int, E: int, device) -> Tensor:
@@ -354,7 +398,8 @@ def moe_permute(order: Tensor, inv: Tensor, offsets: Tensor, workspace: Tensor, 
         if t.dtype != torch.int32:
             raise TypeError("moe_permute works on int32 tensors")
     check(_lib.lib().b200_moe_permute(_ptr(order), _ptr(inv), _ptr(offsets), _ptr(ids), ids.numel(),
-                                      offsets.numel() - 1, _ptr(workspace), _flags(), _stream()),
+                                      offsets.numel() - 1, _ptr(workspace),
+                                      status_word(ids.device).data_ptr(), _flags(), _stream()),
           "b200_moe_permute")
 
 
@@ -407,8 +452,8 @@ def moe_decode_down(y: Tensor, act: Tensor, w_down: Tensor, ids: Tensor,
 # ----------------------------------------------------------------------------- flash prefill
 @torch.library.custom_op("b200::flash_prefill", mutates_args=("out",))
 def flash_prefill(out: Tensor, q: Tensor, k: Tensor, v: Tensor, kv_len: int, causal: bool,
-                  scale: float, q_pos0: int = 0, impl: str = "tc") -> None:
-    """Flash attention over strided views.
+                  scale: float, q_pos0: int = 0) -> None:
+    """Flash attention over strided views (tcgen05 / TMEM kernel).
 
     q / out: [B, S, n_q, hd] views; k / v: [B, n_kv, L, hd] views (any strides with a
     contiguous last dimension), attending to the first kv_len of L keys.  A decode cache
@@ -419,19 +464,12 @@ def flash_prefill(out: Tensor, q: Tensor, k: Tensor, v: Tensor, kv_len: int, cau
             raise RuntimeError("last dimension must be contiguous")
     B, S, n_q, hd = q.shape
     n_kv = k.shape[1]
-    if impl == "tc":   # tcgen05 / TMEM kernel (the product path); "mma" keeps the mma.sync tiles
-        check(_lib.lib().b200_flash_prefill_tc(
-            out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, kv_len, q_pos0, n_q,
-            n_kv, hd, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(2), k.stride(1),
-            v.stride(0), v.stride(2), v.stride(1), out.stride(0), out.stride(1), out.stride(2),
-            1 if causal else 0, scale, status_word(q.device).data_ptr(), _flags(), _stream()),
-            "b200_flash_prefill_tc")
-        return
-    check(_lib.lib().b200_flash_prefill(
-        out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, kv_len, q_pos0, n_q, n_kv,
-        hd, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(2), k.stride(1),
+    check(_lib.lib().b200_flash_prefill_tc(
+        out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, kv_len, q_pos0, n_q,
+        n_kv, hd, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(2), k.stride(1),
         v.stride(0), v.stride(2), v.stride(1), out.stride(0), out.stride(1), out.stride(2),
-        1 if causal else 0, scale, _flags(), _stream()), "b200_flash_prefill")
+        1 if causal else 0, scale, status_word(q.device).data_ptr(), _flags(), _stream()),
+        "b200_flash_prefill_tc")
 
 
 # ----------------------------------------------------------------------------- small ops

@@ -263,6 +263,8 @@ class WhisperDecoder:
         self.state.copy_(saved[0]); self.tok.copy_(saved[1]); self.tok_log.copy_(saved[2])
 
     def set_step(self, tok: int, pos: int, generated: int = 0) -> None:
+        if pos < 0 or pos + 1 > self.cfg.max_target:
+            raise ValueError(f"position {pos} is outside the {self.cfg.max_target}-token window")
         self.tok.fill_(tok)
         self.state.copy_(torch.tensor([pos, pos + 1, generated, 0], dtype=torch.int32))
 
@@ -276,6 +278,12 @@ class WhisperDecoder:
     def generate(self, prefix: List[int], n_new: int, collect_logits: Optional[list] = None) -> List[int]:
         """Feeds the forced prefix token by token (teacher forcing), then decodes n_new tokens
         greedily.  Returns the generated tokens."""
+        if n_new > self.tok_log.numel() + 1:
+            raise ValueError("n_new exceeds max_new_tokens")
+        if len(prefix) + n_new - 1 > self.cfg.max_target:
+            # positions index the learned position table and the self-attention cache
+            raise ValueError(f"{len(prefix)} prefix + {n_new - 1} decode positions exceed the "
+                             f"{self.cfg.max_target}-token window")
         for p, t in enumerate(prefix):
             self.set_step(t, p, 0)
             if self.logit_bias is not None and p == len(prefix) - 1:
@@ -294,6 +302,7 @@ class WhisperDecoder:
             if collect_logits is not None:
                 collect_logits.append(self.logits.float().cpu().clone())
         out.extend(self.tok_log[:n_new - 1].tolist())
+        ops.check_status(self.device)
         return out
 
 

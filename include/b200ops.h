@@ -38,7 +38,8 @@ enum {
   B200_ERR_ARG = -4,       /* null pointer / bad enum */
   B200_ERR_TIMEOUT = -5,   /* a bounded device-side wait expired (status word) */
   B200_ERR_DRIVER = -6,    /* driver entry point (tensor-map encode) unavailable */
-  B200_ERR_SCRATCH = -7    /* request needs more scratch than the library's fixed array holds */
+  B200_ERR_SCRATCH = -7,   /* request needs more scratch than the library's fixed array holds */
+  B200_ERR_NUMERIC = -8    /* non-finite input where an index is derived from it (status word) */
 };
 
 /* launch flags */
@@ -54,14 +55,15 @@ enum {
 };
 
 int b200_version(void);
-/* Kernel tuning knobs (process-wide, host side): key B200_TUNE_GEMV selects the GEMV
- * variant (loads per batch / CTAs per SM / row mapping); 0 is the measured best; 3 is an
- * experimental inner loop on mma.sync (bf16 high / low split of x), not yet timed. */
-enum { B200_TUNE_GEMV = 0, B200_TUNE_GEMM_BN = 1 /* force the GEMM tile width: 256 / 128 / 64 */,
-       B200_TUNE_TP_PROTOCOL = 2 /* fused all-reduce: 0 tagged pairs summed by a few CTAs, 1 data +
-                                    sequence flags, 2 tagged pairs read directly by every CTA */,
-       B200_TUNE_FLASH_DECODE = 3 /* decode attention: 0 tensor-core kernel, 1 SIMT kernel */,
-       B200_TUNE_GEMV_NORM = 4 /* RMSNorm prologue: 0 scale the row sums, 1 normalise x in smem */ };
+/* Kernel tuning knobs (process-wide, host side).  Keys 2 and 3 selected kernel variants that
+ * were measured slower and removed; they are accepted and ignored. */
+enum { B200_TUNE_GEMV = 0 /* GEMV register blocking: 0 = 8 loads per batch, 2 CTAs per SM (the
+                             measured best); 1 = 4 loads / 4 CTAs; 2 = 4 loads / 3 CTAs */,
+       B200_TUNE_GEMM_BN = 1 /* force the GEMM tile width: 256 / 128 / 64 */,
+       B200_TUNE_GEMV_NORM = 4 /* RMSNorm prologue: 0 scale the row sums, 1 normalise x in smem */,
+       B200_TUNE_WAIT_KTICKS = 5 /* clock budget of every bounded device-side wait on another rank
+                                    or on the other CTAs of a persistent kernel, in units of 1024
+                                    ticks; 0 = the default of about two seconds */ };
 int b200_set_tuning(int key, int value);
 /* Number of SMs the library sizes its grids for (148 on B200). */
 int b200_sm_count(void);
@@ -120,7 +122,7 @@ int b200_gemv_bf16_tp(const void* x, const void* w, void* y, int K, int N, int l
 /* Expert parallelism: b200_moe_decode_down whose output (this rank's experts' share, + fp32 resid
  * on one rank) is pushed as all-reduce tp_out instead of being stored (the all-reduce after the
  * routed experts has no counterpart in the single-GPU reference; its call site is
- * models/qwen3-30b-a3b/qwen3_moe_optimized.py, the down projection of the expert MLP). */
+ * models/qwen3-30b-a3b/qwen3_optimized.py:494, the down projection of the expert MLP). */
 int b200_moe_decode_down_tp(const void* act, const void* w_down, const int* ids, int top_k,
                             int inter, int hidden, int expert_lo, int n_local, const void* resid,
                             int ctx, int tp_out, int* status, int flags, b200_stream_t stream);
@@ -235,6 +237,51 @@ int b200_flash_decode_static(void* out, int out_dtype, const void* q, int q_dtyp
                              int n_splits, float scale, int flags, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------
+ * a13. All layers of one batch-1 decode step of a dense decoder in ONE persistent launch
+ * (cooperative, one CTA per SM): q|k|v GEMV with RMSNorm prologue -> (QK-norm +) RoPE + cache
+ * append + split-KV attention + combine -> o_proj + residual -> gate|up GEMV with RMSNorm prologue
+ * and SwiGLU -> down + residual, layer after layer, with grid-wide waits between dependent phases
+ * and the next matrix's first weights already in flight across every wait.
+ * Reference: the body of the captured decode graph, models/llama31-8b/llama31_optimized.py:385-419
+ * and models/qwen3-4b/qwen3_optimized.py:385-420 (18 launches per layer there).
+ *
+ * Set-up (once, synchronous copy): b200_decode_layers_plan writes the phase table into plan_dev
+ * (b200_decode_layers_plan_bytes(n_layers) bytes of device memory) from host arrays of per-layer
+ * device pointers: w_qkv[i] [q_size + 2 kv_size, hidden], w_o[i] [hidden, q_size], w_gu[i]
+ * [2 inter, hidden] with gate / up rows interleaved, w_down[i] [hidden, inter] (bf16, HuggingFace
+ * [N, K] layout, contiguous), ln1[i] / ln2[i] RMSNorm weights, kcache[i] / vcache[i] the layer's
+ * [n_kv, max_seq, hd] bf16 caches, qn_w / kn_w the QK-norm weights (both arrays NULL for models
+ * without).  h [hidden], qkv [q_size + 2 kv_size], attn [q_size], act [inter] are the fp32
+ * activation vectors the step works on: h holds the embedded token on entry and the last layer's
+ * output on exit.  Sizes are the per-rank ones; hidden, q_size, inter % 256 == 0 and <= 16384.
+ * tp_ctx >= 0 (a b200_tp_create context): the all-reduces after o_proj and down are the fused
+ * peer-memory exchange of b200_gemv_bf16_tp, numbered 2 i and 2 i + 1 within the step; h is then
+ * complete only after the consumer of all-reduce 2 n_layers - 1 (b200_gemv_bf16_tp with tp_in) ran.
+ *
+ * Per step: b200_decode_layers.  kv_len_dev[0] - 1 is the new position; fd_workspace as for
+ * b200_flash_decode; sync_ws is b200_decode_layers_sync_bytes() of device memory, zero before the
+ * first launch and owned by this plan; status (required) receives B200_ERR_TIMEOUT if a bounded
+ * wait expired - the outputs are then invalid and sync_ws must be zeroed again.
+ * n_kv * n_splits <= b200_sm_count().  The launch is cooperative and carries no programmatic
+ * dependent launch attribute.
+ */
+int64_t b200_decode_layers_plan_bytes(int n_layers);
+int b200_decode_layers_sync_bytes(void);
+int b200_decode_layers_plan(void* plan_dev, int n_layers, const void* const* w_qkv,
+                            const void* const* w_o, const void* const* w_gu,
+                            const void* const* w_down, const void* const* ln1,
+                            const void* const* ln2, const void* const* kcache,
+                            const void* const* vcache, const void* const* qn_w,
+                            const void* const* kn_w, float* h, float* qkv, float* attn, float* act,
+                            int hidden, int q_size, int kv_size, int inter, int tp_ctx);
+int b200_decode_layers(const void* plan_dev, int n_layers, const float* qkv, float* attn,
+                       const float* cos_t, const float* sin_t, const int* kv_len_dev,
+                       void* fd_workspace, void* sync_ws, int n_q, int n_kv, int hd,
+                       int64_t kv_head_stride, int64_t kv_row_stride, int max_seq, int n_splits,
+                       float scale, float eps, int tp_ctx, int* status, int flags,
+                       b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
  * a2. Prefill / encoder GEMM  Y[M,N] = X[M,K] W[N,K]^T  (bf16 in, fp32 accumulate in
  * tensor memory, bf16 out; fp32 out for plain / bias / GELU epilogues, e.g. router logits) on
  * tcgen05 tensor cores fed by TMA.
@@ -271,19 +318,12 @@ int b200_moe_grouped_gemm(const void* x, const void* w, void* y, const int* offs
  * models/bge-m3/kernels/bge_fa2_attention_nokb_postvb_late.ptx:1-2329 (bidirectional d64),
  * flash-attn-4 call at models/whisper-large-v3/whisper_optimized.py:356-360.
  * hd in {64, 128}; all strides multiples of 8 elements.
+ * Runs on the tcgen05 tensor cores (TMA-fed, S and O accumulators in tensor memory, 128 x 128
+ * tiles).  Each of q / k / v must be expressible as a 2D row-major view: the batch stride a
+ * multiple of the row stride, and the head stride either a multiple of the row stride (heads are
+ * row blocks, as in the KV cache) or smaller than it (heads are column blocks, as in packed
+ * projections).  status (nullable) receives B200_ERR_TIMEOUT if a bounded wait expired.
  */
-int b200_flash_prefill(void* out, const void* q, const void* k, const void* v,
-                       int batch, int S, int kv_len, int q_pos0, int n_q, int n_kv, int hd,
-                       int64_t q_bs, int64_t q_rs, int64_t q_hs,
-                       int64_t k_bs, int64_t k_rs, int64_t k_hs,
-                       int64_t v_bs, int64_t v_rs, int64_t v_hs,
-                       int64_t o_bs, int64_t o_rs, int64_t o_hs,
-                       int causal, float scale, int flags, b200_stream_t stream);
-/* Same contract on the tcgen05 tensor cores (TMA-fed, S and O accumulators in tensor memory,
- * 128 x 128 tiles).  Each of q / k / v must be expressible as a 2D row-major view: the batch
- * stride a multiple of the row stride, and the head stride either a multiple of the row stride
- * (heads are row blocks, as in the KV cache) or smaller than it (heads are column blocks, as in
- * packed projections).  status (nullable) receives B200_ERR_TIMEOUT if a bounded wait expired. */
 int b200_flash_prefill_tc(void* out, const void* q, const void* k, const void* v,
                           int batch, int S, int kv_len, int q_pos0, int n_q, int n_kv, int hd,
                           int64_t q_bs, int64_t q_rs, int64_t q_hs,
@@ -297,32 +337,27 @@ int b200_flash_prefill_tc(void* out, const void* q, const void* k, const void* v
  * weights renormalised over the selected experts; ids in descending-probability order.
  *   logits: [s, E] fp32 or bf16; ids int32 [s, top_k]; wts fp32 [s, top_k]
  *   round_bf16: round the weights through bf16 like the reference kernel does
+ *   status: optional device int32; a token with a non-finite logit gets valid ids (its
+ *           probabilities count as zero) and status receives B200_ERR_NUMERIC
  * Reference: models/qwen3-30b-a3b/kernels/moe_router_parallel_topk_k.cu:2-111 (decode) and
  * the torch softmax/topk/renorm at models/qwen3-30b-a3b/qwen3_optimized.py:569-572 (prefill).
  * E % 32 == 0, E <= 256, top_k <= 32.
  */
 int b200_moe_router(int* ids, float* wts, const void* logits, int logits_dtype, int s, int E,
-                    int top_k, int round_bf16, int flags, b200_stream_t stream);
-/* Decode-time router in one launch: logits[E] = W_router[E, H] . rmsnorm(x) * norm_w (fp32 x,
- * bf16 weights), then the selection of b200_moe_router on those logits by the CTA that arrives
- * last.  counter: one device int32, zero before the first call (the kernel leaves it zero).
- * Reference: the router GEMV + moe_router_parallel_topk_k pair of the decode step,
- * models/qwen3-30b-a3b/qwen3_optimized.py:478-482.  H % 8 == 0, H <= 12288. */
-int b200_moe_router_gemv(int* ids, float* wts, float* logits, int* counter, const float* x,
-                         const void* norm_w, float eps, const void* w_router, int E, int H,
-                         int top_k, int round_bf16, int flags, b200_stream_t stream);
-
+                    int top_k, int round_bf16, int* status, int flags, b200_stream_t stream);
 /* a11. Expert-major permutation of the s * top_k (token, slot) pairs: a stable counting sort
  * by expert id, identical to torch.argsort(ids.flatten(), stable=True).
  *   order[r]  : flat pair index (token * top_k + slot) at sorted row r
  *   inv[p]    : sorted row of pair p (nullable)
  *   offsets   : int32 [E + 1], first sorted row of every expert (offsets[E] = pairs)
  *   workspace : b200_moe_permute_workspace_bytes(pairs, E) bytes
+ *   status    : optional device int32; an id outside [0, E) is sorted as expert 0 (nothing is
+ *               indexed out of range) and status receives B200_ERR_ARG
  * Reference: models/qwen3-30b-a3b/qwen3_optimized.py:573-581 (argsort + scatter_add + cumsum).
  */
 int64_t b200_moe_permute_workspace_bytes(int pairs, int E);
 int b200_moe_permute(int* order, int* inv, int* offsets, const int* ids, int pairs, int E,
-                     void* workspace, int flags, b200_stream_t stream);
+                     void* workspace, int* status, int flags, b200_stream_t stream);
 /* xg[r, :] = x[order[r] / top_k, :]  (bf16 rows of H elements).
  * Reference: index_select at models/qwen3-30b-a3b/qwen3_optimized.py:582. */
 int b200_moe_gather_rows(void* xg, const void* x, const int* order, int rows, int top_k, int H,

@@ -341,3 +341,39 @@ def gemv_tp_consume(y, w, ctx, tp_in, x_out=None, norm_w=None, eps=0.0, epilogue
 
 def tp_advance(ctx, inc):
     assert not _PUBLISHED, f"all-reduces {sorted(_PUBLISHED)} were published but never consumed"
+
+
+# ----------------------------------------------------------------------------- whole-step kernel
+class _Plan:
+    pass
+
+
+def decode_layers_plan(wqkv, wo, wgu, wd, ln1, ln2, kv, qn, kn, h, qkv, attn, act, tp_ctx=-1):
+    p = _Plan()
+    p.__dict__.update(locals())
+    return p
+
+
+def decode_layers(plan, cos, sin, kv_len, workspace, n_q, n_kv, n_splits, scale, eps):
+    """The five phases of every layer, as the persistent kernel orders them; with a link the two
+    all-reduces of layer i carry the numbers 2 i and 2 i + 1 and the last one is left published."""
+    p = plan
+    tp = p.tp_ctx >= 0
+    import torch.distributed as dist
+    lead = not tp or dist.get_rank() == 0
+    for i in range(len(p.wqkv)):
+        if tp and i > 0:
+            gemv_tp_consume(p.qkv, p.wqkv[i], p.tp_ctx, 2 * i - 1, x_out=p.h, norm_w=p.ln1[i], eps=eps)
+        else:
+            gemv(p.qkv, p.h, p.wqkv[i], norm_w=p.ln1[i], eps=eps)
+        rope_flash_decode(p.attn, p.kv[i, 0], p.kv[i, 1], workspace, p.qkv, cos, sin, kv_len, n_q,
+                          n_kv, n_splits, scale, eps=eps, qn_w=p.qn[i], kn_w=p.kn[i])
+        if tp:
+            gemv_tp_publish(p.attn, p.wo[i], p.tp_ctx, 2 * i, resid=p.h if lead else None)
+            gemv_tp_consume(p.act, p.wgu[i], p.tp_ctx, 2 * i, x_out=p.h, norm_w=p.ln2[i], eps=eps,
+                            epilogue=EPI_SWIGLU)
+            gemv_tp_publish(p.act, p.wd[i], p.tp_ctx, 2 * i + 1, resid=p.h if lead else None)
+        else:
+            gemv(p.h, p.attn, p.wo[i], resid=p.h)
+            gemv(p.act, p.h, p.wgu[i], norm_w=p.ln2[i], eps=eps, epilogue=EPI_SWIGLU)
+            gemv(p.h, p.act, p.wd[i], resid=p.h)

@@ -2,6 +2,10 @@
 reference's parity authority) on tiny seeded configurations.
 
     python tests/golden/make_golden.py
+    python tests/golden/make_golden.py --reference-listing <checkout of the reference project>
+
+The second form only writes reference_files.txt, the list of the reference project's file paths
+that tests/test_abi.py checks the header's citations against.
 
 Each file holds the token ids, the HF per-layer hidden state of the last position, the HF
 logits of the last four positions, 8 HF greedy tokens and (MoE) the HF router's top-k expert
@@ -88,5 +92,17 @@ def main():
         json.dump(meta, f, indent=1)
 
 
+def write_reference_listing(root: str) -> None:
+    paths = []
+    for d, dirs, files in os.walk(root):
+        dirs[:] = [x for x in dirs if x != ".git"]
+        paths += [os.path.relpath(os.path.join(d, f), root) for f in files]
+    with open(os.path.join(HERE, "reference_files.txt"), "w") as f:
+        f.write("\n".join(sorted(paths)) + "\n")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) == 3 and sys.argv[1] == "--reference-listing":
+        write_reference_listing(sys.argv[2])
+    else:
+        main()

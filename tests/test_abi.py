@@ -43,6 +43,20 @@ def test_header_cites_reference():
         if name in ("b200_version", "b200_sm_count") or name.endswith("_workspace_bytes"):
             continue
     assert text.count("Reference:") >= 10
+    # every cited path is a file of the reference project (listing committed beside the golden
+    # vectors: tests/golden/reference_files.txt, written by tests/golden/make_golden.py)
+    listing = os.path.join(os.path.dirname(__file__), "golden", "reference_files.txt")
+    known = set(open(listing).read().split())
+    cited = set(re.findall(r"models/[A-Za-z0-9_./-]+\.[a-z]+", text))
+    assert len(cited) >= 20
+    folders = {"llama31-8b", "qwen3-4b", "qwen3-30b-a3b", "bge-m3", "whisper-large-v3", "sdxl"}
+    for path in sorted(cited):
+        if path not in known:
+            # "kernels/x.cu" after a full path names a file in the same model folder
+            assert any(k.endswith("/" + path.split("/", 2)[-1]) for k in known), f"{path} is not a reference file"
+    short = set(re.findall(r"(?<![\w/])kernels/[A-Za-z0-9_.-]+\.[a-z]+", text))
+    for path in sorted(short):
+        assert any(k.endswith("/" + path) for k in known), f"{path} is not a reference file"
 
 
 def test_no_gpu_calls_needed_for_queries(lib):
@@ -82,7 +96,7 @@ def test_validation_of_the_newer_entry_points(lib):
     assert lib.b200_gemv_bf16(one, 0, one, one, 0, 256, 8, 256, None, one, 0.0, None, None, 0, 0, 0,
                               None) == -4
     # tensor-parallel link: sizes, and calls on a context that was never created
-    assert lib.b200_tp_buffer_bytes(2, 4096) == 256 + 256 + 2 * 2 * 4096 * 8 + 2 * 4096 * 8
+    assert lib.b200_tp_buffer_bytes(2, 4096) == 256 + 2 * 2 * 4096 * 8 + 2 * 4096 * 8
     assert lib.b200_tp_buffer_bytes(9, 4096) == 0 and lib.b200_tp_buffer_bytes(2, 0) == 0
     assert lib.b200_tp_create(None, 2, 0, 4096) == -4
     assert lib.b200_tp_advance(3, 64, 0, None) == -4
@@ -90,11 +104,16 @@ def test_validation_of_the_newer_entry_points(lib):
                                  None, None, 0, None) == -4
     assert lib.b200_moe_decode_down_tp(one, one, one, 8, 768, 2048, 0, 128, None, 3, 0, None, 0,
                                        None) == -4
-    # router GEMV: expert count must be a multiple of 32, k <= E
-    assert lib.b200_moe_router_gemv(one, one, one, one, one, None, 0.0, one, 100, 2048, 8, 0, 0,
-                                    None) == -1
-    assert lib.b200_moe_router_gemv(one, one, one, None, one, None, 0.0, one, 128, 2048, 8, 0, 0,
-                                    None) == -4
+    # router: expert count must be a multiple of 32, k <= E
+    assert lib.b200_moe_router(one, one, one, 1, 1, 100, 8, 0, None, 0, None) == -1
+    assert lib.b200_moe_router(one, one, None, 1, 1, 128, 8, 0, None, 0, None) == -4
+    # persistent decode kernel: table sizes, null plan, more attention CTAs than SMs
+    assert lib.b200_decode_layers_plan_bytes(32) == 32 * 5 * 112
+    assert lib.b200_decode_layers_sync_bytes() >= 4
+    assert lib.b200_decode_layers(None, 2, one, one, one, one, one, one, one, 8, 2, 128, 0, 0, 64, 4,
+                                  1.0, 1e-5, -1, one, 0, None) == -4
+    assert lib.b200_decode_layers(one, 2, one, one, one, one, one, one, one, 32, 8, 128, 1 << 20, 128,
+                                  64, 19, 1.0, 1e-5, -1, one, 0, None) == -1
     # the mixed-dtype RMSNorm keeps its shape rule
     assert lib.b200_add_rmsnorm(one, one, 0, one, 1, one, 0, one, 1, 12, 1e-5, 0, None) == -1
 

@@ -42,38 +42,6 @@ def test_router_matches_torch_topk(dev, s, E, k):
     assert rel_err(w.cpu()[ok], bf(w_ref2).float()[ok]) < 1e-2
 
 
-@pytest.mark.parametrize("E,H,k,norm", [(128, 2048, 8, True), (128, 2048, 8, False), (32, 4096, 4, True),
-                                          (256, 1024, 2, True)])
-def test_router_gemv_one_launch(dev, E, H, k, norm):
-    """Router GEMV + selection in one launch: logits against an fp32 reference, and the selection
-    bit-exact against the stand-alone router fed with the very logits the kernel produced."""
-    from hoid_optimized_models_b200 import ops
-    from oracle.ref_decoder import rmsnorm, moe_route
-    g = torch.Generator().manual_seed(E + H)
-    x = torch.randn(H, generator=g)
-    w = bf(torch.randn(E, H, generator=g) * 0.05)
-    nw = bf(1 + 0.1 * torch.randn(H, generator=g)) if norm else None
-    xin = rmsnorm(x, nw.float(), 1e-6) if norm else x
-    ref = w.float() @ xin
-    ids = torch.zeros(k, dtype=torch.int32, device=dev)
-    wt = torch.zeros(k, dtype=torch.float32, device=dev)
-    logits = torch.zeros(E, dtype=torch.float32, device=dev)
-    ctr = torch.zeros(1, dtype=torch.int32, device=dev)
-    for _ in range(2):                                   # the counter must come back to zero
-        logits.zero_()
-        ops.moe_router_gemv(ids, wt, logits, ctr, x.to(dev), w.to(dev),
-                            norm_w=nw.to(dev) if norm else None, eps=1e-6)
-        assert rel_err(logits, ref) < 1e-5
-        ids2 = torch.zeros(1, k, dtype=torch.int32, device=dev)
-        wt2 = torch.zeros(1, k, dtype=torch.float32, device=dev)
-        ops.moe_router(ids2, wt2, logits.view(1, E).clone())
-        assert torch.equal(ids.cpu(), ids2.cpu().view(-1))
-        assert torch.equal(wt.cpu(), wt2.cpu().view(-1))
-        assert int(ctr.item()) == 0
-    ids_ref, _ = moe_route(logits.cpu().view(1, E), k)
-    assert torch.equal(ids.cpu().long(), ids_ref.view(-1))
-
-
 def test_router_tie_break_is_lowest_index(dev):
     from hoid_optimized_models_b200 import ops
     logits = torch.zeros(2, 128)
@@ -86,6 +54,55 @@ def test_router_tie_break_is_lowest_index(dev):
     ref = torch.sort(logits, dim=-1, descending=True, stable=True).indices[:, :8]
     assert torch.equal(ids.cpu().long(), ref)
     assert abs(float(w[1].sum()) - 1.0) < 1e-6
+
+
+def test_router_non_finite_logit_reports_and_stays_in_range(dev):
+    """One NaN logit turns the whole softmax row into NaN.  The router must still write valid
+    expert numbers (the row's probabilities count as zero), flag the status word, and leave the
+    other tokens alone; the expert sort downstream indexes shared memory with these ids."""
+    from hoid_optimized_models_b200 import ops
+    from hoid_optimized_models_b200._lib import B200Error
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(5, 128, generator=g)
+    logits[2, 77] = float("nan")
+    logits[4, 3] = float("inf")
+    ids = torch.full((5, 8), -7, dtype=torch.int32, device=dev)
+    w = torch.zeros(5, 8, dtype=torch.float32, device=dev)
+    ops.check_status(dev)
+    ops.moe_router(ids, w, logits.to(dev))
+    with pytest.raises(B200Error, match="NUMERIC"):
+        ops.check_status(dev)
+    ops.check_status(dev)                                # the word was cleared
+    got = ids.cpu()
+    assert int(got.min()) >= 0 and int(got.max()) < 128
+    good = [0, 1, 3]
+    ref = torch.sort(logits[good], dim=-1, descending=True, stable=True).indices[:, :8]
+    assert torch.equal(got[good].long(), ref)
+    assert torch.isfinite(w.cpu()).all()
+    # and the sort takes them without a fault
+    order = torch.zeros(40, dtype=torch.int32, device=dev)
+    inv = torch.zeros(40, dtype=torch.int32, device=dev)
+    offs = torch.zeros(129, dtype=torch.int32, device=dev)
+    ops.moe_permute(order, inv, offs, ops.moe_permute_workspace(40, 128, dev), ids)
+    ops.check_status(dev)
+    assert int(offs[128]) == 40
+
+
+def test_permute_reports_out_of_range_ids(dev):
+    """Expert ids outside [0, E) are a caller error: they are sorted as expert 0 (every index
+    stays in range) and the status word says so."""
+    from hoid_optimized_models_b200 import ops
+    from hoid_optimized_models_b200._lib import B200Error
+    ids = torch.tensor([[3, 0x7fffffff], [-5, 1]], dtype=torch.int32, device=dev)
+    order = torch.zeros(4, dtype=torch.int32, device=dev)
+    inv = torch.zeros(4, dtype=torch.int32, device=dev)
+    offs = torch.zeros(9, dtype=torch.int32, device=dev)
+    ops.check_status(dev)
+    ops.moe_permute(order, inv, offs, ops.moe_permute_workspace(4, 8, dev), ids)
+    with pytest.raises(B200Error, match="ARG"):
+        ops.check_status(dev)
+    assert offs.cpu().tolist() == [0, 2, 3, 3, 4, 4, 4, 4, 4]
+    assert sorted(order.cpu().tolist()) == [0, 1, 2, 3]
 
 
 @pytest.mark.parametrize("S,E,k", [(1, 128, 8), (333, 128, 8), (8192, 128, 8), (50, 16, 2)])

@@ -14,14 +14,6 @@ def bf(t):
     return t.to(torch.bfloat16)
 
 
-@pytest.fixture
-def fd_impl():
-    """Selects the decode-attention kernel (0 tensor-core, 1 SIMT) for one test."""
-    from hoid_optimized_models_b200 import ops
-    yield lambda simt: ops.set_tuning(3, int(simt))      # B200_TUNE_FLASH_DECODE
-    ops.set_tuning(3, 0)
-
-
 def rel_err(a, b):
     return float((a.float().cpu() - b.float().cpu()).abs().max() / b.float().abs().max().clamp_min(1e-30))
 
@@ -72,41 +64,6 @@ def test_gemv_fusions(dev):
     ops.gemv(yb, act, wd.to(dev), epilogue=ops.EPI_GELU)
     ref3 = torch.nn.functional.gelu(wd.float() @ act.float().cpu())
     assert rel_err(yb, ref3) < 1e-2  # bf16 output rounding
-
-
-@pytest.mark.skipif(os.environ.get("B200_EXPERIMENTAL") != "1",
-                    reason="tensor-core GEMV loop: not yet validated on a GPU, opt in with B200_EXPERIMENTAL=1")
-@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 6144), (14336, 4096), (2048, 128), (256, 7),
-                                 (1280, 51866)])
-def test_gemv_tensor_core_variant(dev, K, N):
-    """B200_TUNE_GEMV = 3 against the fp32 reference and the default kernel, with the RMSNorm
-    prologue, bias / residual and the SwiGLU epilogue."""
-    from hoid_optimized_models_b200 import ops
-    from oracle.ref_decoder import rmsnorm
-    g = torch.Generator().manual_seed(K + N)
-    w = bf(torch.randn(N, K, generator=g) * 0.02).to(dev)
-    x = torch.randn(K, generator=g)
-    nw = bf(1 + 0.02 * torch.randn(K, generator=g))
-    bias = bf(torch.randn(N, generator=g))
-    res = torch.randn(N, generator=g)
-    ref = w.float().cpu() @ rmsnorm(x, nw.float(), 1e-5) + bias.float() + res
-    y0 = torch.empty(N, dtype=torch.float32, device=dev)
-    y1 = torch.empty(N, dtype=torch.float32, device=dev)
-    ops.gemv(y0, x.to(dev), w, norm_w=nw.to(dev), eps=1e-5, bias=bias.to(dev), resid=res.to(dev))
-    try:
-        ops.set_tuning(0, 3)
-        ops.gemv(y1, x.to(dev), w, norm_w=nw.to(dev), eps=1e-5, bias=bias.to(dev), resid=res.to(dev))
-        torch.cuda.synchronize()
-        assert rel_err(y1, ref) < 1e-4 and rel_err(y1, y0.cpu()) < 1e-4
-        if N % 2 == 0:
-            a0 = torch.empty(N // 2, dtype=torch.float32, device=dev)
-            a1 = torch.empty(N // 2, dtype=torch.float32, device=dev)
-            ops.gemv(a1, x.to(dev), w, epilogue=ops.EPI_SWIGLU)
-            ops.set_tuning(0, 0)
-            ops.gemv(a0, x.to(dev), w, epilogue=ops.EPI_SWIGLU)
-            assert rel_err(a1, a0.cpu()) < 1e-4
-    finally:
-        ops.set_tuning(0, 0)
 
 
 def test_gemv_rejects_bad_shapes(dev):
@@ -224,10 +181,8 @@ def test_qk_rope_cache(dev, s, n_q, n_kv, hd, qk_norm):
 @pytest.mark.parametrize("n_q,n_kv,hd,kv_len,n_splits", [
     (32, 8, 128, 1, 4), (32, 8, 128, 37, 16), (32, 8, 128, 1500, 37), (32, 4, 128, 1025, 64),
     (20, 20, 64, 1500, 8), (20, 20, 64, 5, 8), (4, 1, 128, 700, 74), (8, 4, 64, 333, 5)])
-@pytest.mark.parametrize("simt", [0, 1], ids=["tensor-core", "simt"])
-def test_flash_decode(dev, n_q, n_kv, hd, kv_len, n_splits, simt, fd_impl):
+def test_flash_decode(dev, n_q, n_kv, hd, kv_len, n_splits):
     from hoid_optimized_models_b200 import ops
-    fd_impl(simt)
     g = torch.Generator().manual_seed(kv_len)
     max_seq = kv_len + 3
     q = torch.randn(n_q, hd, generator=g)
@@ -246,7 +201,7 @@ def test_flash_decode(dev, n_q, n_kv, hd, kv_len, n_splits, simt, fd_impl):
         ops.flash_decode(out, q.to(dev), kc.to(dev), vc.to(dev), kl, ws, n_q, n_kv, n_splits,
                          hd ** -0.5)
         # the tensor-core kernel carries q and P as bf16 high + low parts (~16 mantissa bits)
-        assert rel_err(out, ref) < (2e-5 if simt else 5e-5)
+        assert rel_err(out, ref) < 5e-5
 
 
 @pytest.mark.parametrize("n_q,n_kv,hd,kv_len,n_splits,qk_norm", [
@@ -254,13 +209,10 @@ def test_flash_decode(dev, n_q, n_kv, hd, kv_len, n_splits, simt, fd_impl):
     (32, 8, 128, 8193, 18, False), (32, 8, 128, 1024, 16, True), (32, 4, 128, 1025, 37, True),
     (16, 4, 128, 129, 8, False), (20, 20, 64, 300, 7, False), (8, 4, 64, 333, 5, True),
     (4, 1, 128, 700, 74, False)])
-@pytest.mark.parametrize("simt", [0, 1], ids=["tensor-core", "simt"])
-def test_rope_flash_decode_matches_two_kernels(dev, n_q, n_kv, hd, kv_len, n_splits, qk_norm, simt,
-                                               fd_impl):
+def test_rope_flash_decode_matches_two_kernels(dev, n_q, n_kv, hd, kv_len, n_splits, qk_norm):
     """The fused launch against qk_rope_cache followed by flash_decode: same attention output,
     same appended cache row, every other cache row untouched."""
     from hoid_optimized_models_b200 import ops
-    fd_impl(simt)
     g = torch.Generator().manual_seed(kv_len + n_splits)
     max_seq = kv_len + 2
     pos = kv_len - 1
@@ -288,7 +240,7 @@ def test_rope_flash_decode_matches_two_kernels(dev, n_q, n_kv, hd, kv_len, n_spl
         out1.zero_()
         ops.rope_flash_decode(out1, k1, v1, ws, qkv, cos, sin, kl, n_q, n_kv, n_splits,
                               hd ** -0.5, eps=1e-6, qn_w=qn, kn_w=kn)
-        assert rel_err(out1, out2.cpu()) < (2e-5 if simt else 5e-5)
+        assert rel_err(out1, out2.cpu()) < 5e-5
         # the appended row: bf16 of the same fp32 arithmetic (an fma contraction may move one ulp)
         assert rel_err(k1[:, pos], k2[:, pos].cpu()) < 1e-2
         assert torch.equal(v1, v2)
@@ -297,11 +249,9 @@ def test_rope_flash_decode_matches_two_kernels(dev, n_q, n_kv, hd, kv_len, n_spl
         assert torch.equal(k1[:, keep], kc[:, keep])
 
 
-@pytest.mark.parametrize("simt", [0, 1], ids=["tensor-core", "simt"])
-def test_flash_decode_strided_cross_kv(dev, simt, fd_impl):
+def test_flash_decode_strided_cross_kv(dev):
     """Whisper cross-attention layout: K/V rows are [1500, 20 * 64] projections."""
     from hoid_optimized_models_b200 import ops
-    fd_impl(simt)
     g = torch.Generator().manual_seed(3)
     H, hd, L = 20, 64, 1500
     q = torch.randn(H, hd, generator=g)
@@ -316,7 +266,7 @@ def test_flash_decode_strided_cross_kv(dev, simt, fd_impl):
     kl = torch.tensor([L], dtype=torch.int32, device=dev)
     ops.flash_decode(out, q.to(dev), k.to(dev), v.to(dev), kl, ws, H, H, 16, hd ** -0.5,
                      kv_head_stride=hd, kv_row_stride=H * hd)
-    assert rel_err(out, ref) < (2e-5 if simt else 5e-5)
+    assert rel_err(out, ref) < 5e-5
 
 
 # ----------------------------------------------------------------------------- small ops
@@ -447,8 +397,7 @@ def test_moe_grouped_gemm(dev):
 @pytest.mark.parametrize("S,n_q,n_kv,hd,causal", [(64, 4, 1, 128, True), (200, 8, 2, 128, True),
                                                   (1000, 32, 8, 128, True), (512, 16, 16, 64, False),
                                                   (77, 4, 4, 64, False), (1500, 20, 20, 64, False)])
-@pytest.mark.parametrize("impl", ["tc", "mma"])
-def test_flash_prefill(dev, S, n_q, n_kv, hd, causal, impl):
+def test_flash_prefill(dev, S, n_q, n_kv, hd, causal):
     from hoid_optimized_models_b200 import ops
     from oracle.ref_decoder import causal_attention
     g = torch.Generator().manual_seed(S)
@@ -468,7 +417,7 @@ def test_flash_prefill(dev, S, n_q, n_kv, hd, causal, impl):
         ref = torch.einsum("hsk,hkd->shd", p, vv)
     out = torch.empty(1, S, n_q, hd, dtype=torch.bfloat16, device=dev)
     ops.flash_prefill(out, q.to(dev).view(1, S, n_q, hd), kc.to(dev).unsqueeze(0),
-                      vc.to(dev).unsqueeze(0), S, causal, hd ** -0.5, impl=impl)
+                      vc.to(dev).unsqueeze(0), S, causal, hd ** -0.5)
     ops.check_status(dev)
     # P and the output are rounded to bf16
     assert rel_err(out[0], ref) < 2e-2
