@@ -236,7 +236,7 @@ def run_secondary(args):
         eng = DenseDecoder(cfg, w, max_seq=P + W + K + 8, device=dev, max_new_tokens=W + K + 8,
                            free_source_weights=True, tp_rank=rank, tp_size=world, group=group,
                            fused_allreduce=args.tp_allreduce != "nccl",
-                           fused_layers=not args.per_phase_launches)
+                           fused_layers=args.persistent_layers)
         del w
         torch.cuda.empty_cache()
         ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(1)).to(dev)
@@ -349,8 +349,9 @@ def main():
     ap.add_argument("--ttft-runs", type=int, default=3)
     ap.add_argument("--tp-allreduce", default="fused", choices=["fused", "nccl"],
                     help="N>1: all-reduce fused into the decode kernels over peer memory, or NCCL calls")
-    ap.add_argument("--per-phase-launches", action="store_true",
-                    help="one launch per phase instead of the persistent all-layers kernel (A/B)")
+    ap.add_argument("--persistent-layers", action="store_true",
+                    help="all layers of a decode step as one persistent launch instead of one launch "
+                         "per phase (A/B; measured slower at 1 and 2 GPUs)")
     ap.add_argument("--workload", default="llama-3.1-8b",
                     help="llama-3.1-8b (headline) | qwen3-4b | qwen3-30b-a3b | xlm-roberta-large | whisper-large-v3")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
@@ -416,7 +417,7 @@ def main():
     eng = Llama31Optimized(cfg, weights, max_seq=max_seq, device=dev, tp_rank=rank, tp_size=world,
                            group=group, max_new_tokens=W + K + 8, free_source_weights=True,
                            fused_allreduce=args.tp_allreduce != "nccl",
-                           fused_layers=not args.per_phase_launches)
+                           fused_layers=args.persistent_layers)
     del weights
     torch.cuda.empty_cache()
     ids = torch.randint(0, cfg.vocab, (args.prompt,), generator=torch.Generator().manual_seed(2))

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200ops.so")
+# B200OPS_LIB points at another build of the same library (A/B runs of kernel variants)
+LIB_PATH = os.environ.get("B200OPS_LIB") or os.path.join(HERE, "libb200ops.so")
 
 BF16, F32 = 0, 1
 FLAG_PDL = 1
@@ -42,10 +43,10 @@ SIGNATURES = {
     "b200_gemv_bf16_tp": (_i, [_p, _p, _p, _i, _i, _i, _p, _f, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p]),
     "b200_moe_decode_down_tp": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _p, _i, _p]),
     "b200_decode_layers_plan_bytes": (_l, [_i]),
-    "b200_decode_layers_sync_bytes": (_i, []),
-    "b200_decode_layers_plan": (_i, [_p, _i] + [_p] * 10 + [_p] * 4 + [_i] * 5),
-    "b200_decode_layers": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _l, _l, _i, _i, _f,
-                                _f, _i, _p, _i, _p]),
+    "b200_decode_layers_sync_bytes": (_l, [_i, _i, _i, _i]),
+    "b200_decode_layers_plan": (_i, [_p, _p, _i] + [_p] * 10 + [_p] + [_i] * 5),
+    "b200_decode_layers": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _l, _l, _i, _i, _f, _f, _i,
+                                _p, _i, _p]),
     "b200_add_rmsnorm": (_i, [_p, _p, _i, _p, _i, _p, _i, _p, _i, _i, _f, _i, _p]),
     "b200_add_layernorm": (_i, [_p, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _f, _i, _p]),
     "b200_qk_rope_cache": (_i, [_p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,

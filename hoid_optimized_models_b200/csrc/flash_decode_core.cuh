@@ -6,6 +6,7 @@
 
 namespace b200 {
 
+constexpr int kFdOutPairs = 2;      // FdArgs::out_dtype: {fp32 value, tag} pairs, one 64-bit store each
 struct FdArgs {
   void* out; const void* q; const uint16_t* k; const uint16_t* v; const int* kv_len;
   int* counters; float* recs;
@@ -17,6 +18,7 @@ struct FdArgs {
   const float* qkv; const float* cos_t; const float* sin_t;
   const uint16_t* qn_w; const uint16_t* kn_w;
   float eps; int max_seq;
+  unsigned tag;                  // kFdOutPairs: the tag written beside every value
 };
 
 // ---- shared tail of both kernels -------------------------------------------------------------
@@ -114,7 +116,14 @@ __device__ __forceinline__ void fd_finish(const FdArgs& a, float* srec, float* s
     }
     const float inv = den > 0.f ? 1.f / den : 0.f;
     const size_t oi = (size_t)kvh * G * HD + (size_t)tid * 4;
-    if (a.out_dtype == B200_F32) {
+    if (a.out_dtype == kFdOutPairs) {
+      const float r[4] = {num.x * inv, num.y * inv, num.z * inv, num.w * inv};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const unsigned long long w2 = ((unsigned long long)a.tag << 32) | __float_as_uint(r[e]);
+        asm volatile("st.global.b64 [%0], %1;" ::"l"(reinterpret_cast<uint2*>(a.out) + oi + e), "l"(w2) : "memory");
+      }
+    } else if (a.out_dtype == B200_F32) {
       reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + oi)[0] =
           make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
     } else {

@@ -110,6 +110,26 @@ __device__ __forceinline__ float4 tp_read_reduced(const TpLink& l, unsigned slot
                                                   int* status) {
   return ll_reduce(l.xr + (size_t)slot * (l.H >> 1) + 2 * i, 1, 0, tag, status, l.wait_ticks);
 }
+// Element i of the reduced vector (polled, bounded).
+__device__ __forceinline__ float tp_read_one(const TpLink& l, unsigned slot, unsigned tag, int i,
+                                             int* status) {
+  const volatile uint2* p = reinterpret_cast<const volatile uint2*>(l.xr) + (size_t)slot * l.H + i;
+  long long t0 = 0;
+  int spins = 0;
+  while (true) {
+    // the pair as one 64-bit word: value and tag cannot be torn apart
+    const unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(p);
+    if ((unsigned)(w >> 32) == tag) return __uint_as_float((unsigned)w);
+    if ((++spins & 63) == 0) {
+      if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return 0.f;
+      if (t0 == 0) t0 = clock64();
+      if (clock64() - t0 > l.wait_ticks) {
+        if (status != nullptr) atomicExch(status, B200_ERR_TIMEOUT);
+        return 0.f;
+      }
+    }
+  }
+}
 // This rank's share `v` of element `oi` of all-reduce `seq` into every rank's inbox.
 __device__ __forceinline__ void tp_publish(const TpLink& l, unsigned seq, int oi, float v) {
   const size_t off = ((size_t)(seq & 1u) * l.world + l.rank) * l.H + oi;

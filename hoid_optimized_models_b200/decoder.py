@@ -46,7 +46,7 @@ class DenseDecoder:
                  device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None,
                  n_splits: Optional[int] = None, max_new_tokens: int = 1024,
                  free_source_weights: bool = False, fused_allreduce: bool = True,
-                 fuse_rope: bool = True, fused_layers: bool = True):
+                 fuse_rope: bool = True, fused_layers: bool = False):
         self.moe = cfg.n_experts > 0   # expert parallelism: attention replicated, experts sharded
         tpart.check_divisible(cfg, tp_size)
         self.cfg, self.device, self.max_seq = cfg, torch.device(device), max_seq
@@ -154,8 +154,7 @@ class DenseDecoder:
                 and self._fused_layers_supported()):
             self.plan = ops.decode_layers_plan(
                 self.wqkv, self.wo, self.wgu, self.wd, self.ln1, self.ln2, self.kv, self.qn, self.kn,
-                self.h, self.qkv, self.attn, self.act,
-                tp_ctx=self.link.ctx if self.link is not None else -1)
+                self.h, tp_ctx=self.link.ctx if self.link is not None else -1)
         if self.plan is not None:
             self.launches_per_step = 5 + (1 if self.link is not None else 0)
         else:
@@ -384,7 +383,7 @@ class DenseDecoder:
             ops.check_status(self.device)
         except Exception:
             if self.plan is not None:
-                ops.reset_decode_plan(self.plan)     # its barrier word may hold a partial count
+                ops.reset_decode_plan(self.plan)
             raise
 
     def set_step(self, tok: int, pos: int, generated: int = 0) -> None:

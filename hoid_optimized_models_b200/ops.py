@@ -123,25 +123,25 @@ def tp_advance(ctx: int, inc: int) -> None:
 
 # ----------------------------------------------------------------------------- whole-step kernel
 class DecodePlan:
-    """Phase table of b200_decode_layers on the device, its synchronisation word, and references
-    to every tensor the table points at (so that none of them is freed while the plan lives)."""
+    """Phase table of b200_decode_layers on the device, its synchronisation workspace (launch
+    counter + the tagged vectors the phases hand to one another), and references to every tensor
+    the table points at (so that none of them is freed while the plan lives)."""
 
     def __init__(self, table: Tensor, sync: Tensor, n_layers: int, tp_ctx: int, keep: tuple):
         self.table, self.sync, self.n_layers, self.tp_ctx, self.keep = table, sync, n_layers, tp_ctx, keep
 
 
-def decode_layers_plan(wqkv, wo, wgu, wd, ln1, ln2, kv: Tensor, qn, kn, h: Tensor, qkv: Tensor,
-                       attn: Tensor, act: Tensor, tp_ctx: int = -1) -> DecodePlan:
+def decode_layers_plan(wqkv, wo, wgu, wd, ln1, ln2, kv: Tensor, qn, kn, h: Tensor,
+                       tp_ctx: int = -1) -> DecodePlan:
     """Set-up of the persistent decode kernel: per-layer weight lists (packed q|k|v, o_proj,
     interleaved gate|up, down; RMSNorm weights; QK-norm weights or lists of None), the KV cache
-    [layers, 2, n_kv, max_seq, hd] and the fp32 activation vectors of the step."""
+    [layers, 2, n_kv, max_seq, hd] and the fp32 residual-stream vector of the step."""
     import ctypes as C
     L = len(wqkv)
     for t in (*wqkv, *wo, *wgu, *wd, *ln1, *ln2):
         _bf16(t, "weights")
-    for t in (h, qkv, attn, act):
-        if t.dtype != torch.float32:
-            raise TypeError("decode activations must be float32")
+    if h.dtype != torch.float32:
+        raise TypeError("the residual stream must be float32")
     _bf16(kv, "kv")
 
     def arr(ts):
@@ -150,37 +150,38 @@ def decode_layers_plan(wqkv, wo, wgu, wd, ln1, ln2, kv: Tensor, qn, kn, h: Tenso
     has_qk = qn[0] is not None
     lib = _lib.lib()
     dev = h.device
-    table = torch.zeros(lib.b200_decode_layers_plan_bytes(L), dtype=torch.uint8, device=dev)
-    sync = torch.zeros(lib.b200_decode_layers_sync_bytes() // 4, dtype=torch.int32, device=dev)
     H = h.numel()
-    q_size = attn.numel()
-    kv_size = (qkv.numel() - q_size) // 2
+    q_size = wo[0].shape[1]
+    kv_size = (wqkv[0].shape[0] - q_size) // 2
+    inter = wd[0].shape[1]
+    table = torch.zeros(lib.b200_decode_layers_plan_bytes(L), dtype=torch.uint8, device=dev)
+    sync = torch.zeros(lib.b200_decode_layers_sync_bytes(H, q_size, kv_size, inter) // 8,
+                       dtype=torch.int64, device=dev)
     check(lib.b200_decode_layers_plan(
-        _ptr(table), L, arr(wqkv), arr(wo), arr(wgu), arr(wd), arr(ln1), arr(ln2),
+        _ptr(table), _ptr(sync), L, arr(wqkv), arr(wo), arr(wgu), arr(wd), arr(ln1), arr(ln2),
         arr([kv[i, 0] for i in range(L)]), arr([kv[i, 1] for i in range(L)]),
         arr(qn) if has_qk else None, arr(kn) if has_qk else None,
-        _ptr(h), _ptr(qkv), _ptr(attn), _ptr(act), H, q_size, kv_size, act.numel(), tp_ctx),
-        "b200_decode_layers_plan")
-    return DecodePlan(table, sync, L, tp_ctx, (wqkv, wo, wgu, wd, ln1, ln2, kv, qn, kn, h, qkv, attn, act))
+        _ptr(h), H, q_size, kv_size, inter, tp_ctx), "b200_decode_layers_plan")
+    return DecodePlan(table, sync, L, tp_ctx, (wqkv, wo, wgu, wd, ln1, ln2, kv, qn, kn, h))
 
 
 def decode_layers(plan: DecodePlan, cos: Tensor, sin: Tensor, kv_len: Tensor, workspace: Tensor,
                   n_q: int, n_kv: int, n_splits: int, scale: float, eps: float) -> None:
     """Every layer of one decode step in one launch: h (the embedded token) -> h after the last
-    layer, the new position's k / v rows appended to the cache.  With a tensor-parallel plan the
-    last all-reduce (number 2 * layers - 1) is left for `gemv_tp_consume` to reduce."""
-    wqkv, kv, qkv, attn = plan.keep[0], plan.keep[6], plan.keep[10], plan.keep[11]
+    layer, the new position's k / v rows appended to the cache.  With a tensor-parallel plan h is
+    not written: the last all-reduce (number 2 * layers - 1) is left for `gemv_tp_consume`."""
+    kv = plan.keep[6]
     hd = kv.shape[-1]
     check(_lib.lib().b200_decode_layers(
-        _ptr(plan.table), plan.n_layers, _ptr(qkv), _ptr(attn), _ptr(cos), _ptr(sin), _ptr(kv_len),
+        _ptr(plan.table), plan.n_layers, _ptr(cos), _ptr(sin), _ptr(kv_len),
         _ptr(workspace), _ptr(plan.sync), n_q, n_kv, hd, kv.stride(-3), kv.stride(-2),
-        kv.shape[-2], n_splits, scale, eps, plan.tp_ctx, status_word(attn.device).data_ptr(),
+        kv.shape[-2], n_splits, scale, eps, plan.tp_ctx, status_word(kv.device).data_ptr(),
         _flags(), _stream()), "b200_decode_layers")
 
 
 def reset_decode_plan(plan: DecodePlan) -> None:
-    """After a B200_ERR_TIMEOUT: the grid barrier word may hold a partial count."""
-    plan.sync.zero_()
+    """After a B200_ERR_TIMEOUT nothing needs repair (every launch tags its vectors with its own
+    number); kept so that callers have one place to put recovery."""
 
 
 # ----------------------------------------------------------------------------- norms

@@ -240,8 +240,9 @@ int b200_flash_decode_static(void* out, int out_dtype, const void* q, int q_dtyp
  * a13. All layers of one batch-1 decode step of a dense decoder in ONE persistent launch
  * (cooperative, one CTA per SM): q|k|v GEMV with RMSNorm prologue -> (QK-norm +) RoPE + cache
  * append + split-KV attention + combine -> o_proj + residual -> gate|up GEMV with RMSNorm prologue
- * and SwiGLU -> down + residual, layer after layer, with grid-wide waits between dependent phases
- * and the next matrix's first weights already in flight across every wait.
+ * and SwiGLU -> down + residual, layer after layer.  The phases hand their vectors to one another
+ * as self-validating {value, tag} pairs that the next phase polls (no grid-wide barrier), and the
+ * next matrix's first weights are already in flight across every wait.
  * Reference: the body of the captured decode graph, models/llama31-8b/llama31_optimized.py:385-419
  * and models/qwen3-4b/qwen3_optimized.py:385-420 (18 launches per layer there).
  *
@@ -251,34 +252,34 @@ int b200_flash_decode_static(void* out, int out_dtype, const void* q, int q_dtyp
  * [2 inter, hidden] with gate / up rows interleaved, w_down[i] [hidden, inter] (bf16, HuggingFace
  * [N, K] layout, contiguous), ln1[i] / ln2[i] RMSNorm weights, kcache[i] / vcache[i] the layer's
  * [n_kv, max_seq, hd] bf16 caches, qn_w / kn_w the QK-norm weights (both arrays NULL for models
- * without).  h [hidden], qkv [q_size + 2 kv_size], attn [q_size], act [inter] are the fp32
- * activation vectors the step works on: h holds the embedded token on entry and the last layer's
- * output on exit.  Sizes are the per-rank ones; hidden, q_size, inter % 256 == 0 and <= 16384.
+ * without).  h is the fp32 residual stream [hidden]: the embedded token on entry, the last
+ * layer's output on exit.  sync_ws is b200_decode_layers_sync_bytes(...) bytes of device memory,
+ * 256-byte aligned, ZERO before the first launch and owned by this plan (launch counter + the
+ * pair vectors).  Sizes are the per-rank ones; hidden, q_size, inter % 256 == 0 and <= 16384.
  * tp_ctx >= 0 (a b200_tp_create context): the all-reduces after o_proj and down are the fused
  * peer-memory exchange of b200_gemv_bf16_tp, numbered 2 i and 2 i + 1 within the step; h is then
- * complete only after the consumer of all-reduce 2 n_layers - 1 (b200_gemv_bf16_tp with tp_in) ran.
+ * NOT written: the consumer of all-reduce 2 n_layers - 1 (b200_gemv_bf16_tp with tp_in, x_out)
+ * produces it.
  *
  * Per step: b200_decode_layers.  kv_len_dev[0] - 1 is the new position; fd_workspace as for
- * b200_flash_decode; sync_ws is b200_decode_layers_sync_bytes() of device memory, zero before the
- * first launch and owned by this plan; status (required) receives B200_ERR_TIMEOUT if a bounded
- * wait expired - the outputs are then invalid and sync_ws must be zeroed again.
- * n_kv * n_splits <= b200_sm_count().  The launch is cooperative and carries no programmatic
- * dependent launch attribute.
+ * b200_flash_decode; status (required) receives B200_ERR_TIMEOUT if a bounded wait expired - the
+ * outputs are then invalid.  n_kv * n_splits <= b200_sm_count().  The launch is cooperative and
+ * carries no programmatic dependent launch attribute.  Launches that share a plan must not
+ * overlap on the GPU.
  */
 int64_t b200_decode_layers_plan_bytes(int n_layers);
-int b200_decode_layers_sync_bytes(void);
-int b200_decode_layers_plan(void* plan_dev, int n_layers, const void* const* w_qkv,
+int64_t b200_decode_layers_sync_bytes(int hidden, int q_size, int kv_size, int inter);
+int b200_decode_layers_plan(void* plan_dev, void* sync_ws, int n_layers, const void* const* w_qkv,
                             const void* const* w_o, const void* const* w_gu,
                             const void* const* w_down, const void* const* ln1,
                             const void* const* ln2, const void* const* kcache,
                             const void* const* vcache, const void* const* qn_w,
-                            const void* const* kn_w, float* h, float* qkv, float* attn, float* act,
-                            int hidden, int q_size, int kv_size, int inter, int tp_ctx);
-int b200_decode_layers(const void* plan_dev, int n_layers, const float* qkv, float* attn,
-                       const float* cos_t, const float* sin_t, const int* kv_len_dev,
-                       void* fd_workspace, void* sync_ws, int n_q, int n_kv, int hd,
-                       int64_t kv_head_stride, int64_t kv_row_stride, int max_seq, int n_splits,
-                       float scale, float eps, int tp_ctx, int* status, int flags,
+                            const void* const* kn_w, float* h, int hidden, int q_size,
+                            int kv_size, int inter, int tp_ctx);
+int b200_decode_layers(const void* plan_dev, int n_layers, const float* cos_t, const float* sin_t,
+                       const int* kv_len_dev, void* fd_workspace, void* sync_ws, int n_q, int n_kv,
+                       int hd, int64_t kv_head_stride, int64_t kv_row_stride, int max_seq,
+                       int n_splits, float scale, float eps, int tp_ctx, int* status, int flags,
                        b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------

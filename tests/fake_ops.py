@@ -348,9 +348,11 @@ class _Plan:
     pass
 
 
-def decode_layers_plan(wqkv, wo, wgu, wd, ln1, ln2, kv, qn, kn, h, qkv, attn, act, tp_ctx=-1):
+def decode_layers_plan(wqkv, wo, wgu, wd, ln1, ln2, kv, qn, kn, h, tp_ctx=-1):
     p = _Plan()
     p.__dict__.update(locals())
+    q_size = wo[0].shape[1]
+    p.qkv, p.attn, p.act = torch.zeros(wqkv[0].shape[0]), torch.zeros(q_size), torch.zeros(wd[0].shape[1])
     return p
 
 

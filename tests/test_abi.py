@@ -108,11 +108,12 @@ def test_validation_of_the_newer_entry_points(lib):
     assert lib.b200_moe_router(one, one, one, 1, 1, 100, 8, 0, None, 0, None) == -1
     assert lib.b200_moe_router(one, one, None, 1, 1, 128, 8, 0, None, 0, None) == -4
     # persistent decode kernel: table sizes, null plan, more attention CTAs than SMs
-    assert lib.b200_decode_layers_plan_bytes(32) == 32 * 5 * 112
-    assert lib.b200_decode_layers_sync_bytes() >= 4
-    assert lib.b200_decode_layers(None, 2, one, one, one, one, one, one, one, 8, 2, 128, 0, 0, 64, 4,
+    assert lib.b200_decode_layers_plan_bytes(32) == 32 * 5 * 128
+    assert lib.b200_decode_layers_sync_bytes(4096, 4096, 1024, 14336) >= 256 + 8 * (4096 + 6144 + 4096 + 14336)
+    big = ctypes.c_void_p(1 << 20)
+    assert lib.b200_decode_layers(None, 2, one, one, one, one, big, 8, 2, 128, 0, 0, 64, 4,
                                   1.0, 1e-5, -1, one, 0, None) == -4
-    assert lib.b200_decode_layers(one, 2, one, one, one, one, one, one, one, 32, 8, 128, 1 << 20, 128,
+    assert lib.b200_decode_layers(one, 2, one, one, one, one, big, 32, 8, 128, 1 << 20, 128,
                                   64, 19, 1.0, 1e-5, -1, one, 0, None) == -1
     # the mixed-dtype RMSNorm keeps its shape rule
     assert lib.b200_add_rmsnorm(one, one, 0, one, 1, one, 0, one, 1, 12, 1e-5, 0, None) == -1
