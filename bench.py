@@ -236,7 +236,8 @@ def run_secondary(args):
         eng = DenseDecoder(cfg, w, max_seq=P + W + K + 8, device=dev, max_new_tokens=W + K + 8,
                            free_source_weights=True, tp_rank=rank, tp_size=world, group=group,
                            fused_allreduce=args.tp_allreduce != "nccl",
-                           fused_layers=args.persistent_layers)
+                           fused_layers=args.persistent_layers,
+                           ep_all_to_all=args.ep_all_to_all)
         del w
         torch.cuda.empty_cache()
         ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(1)).to(dev)
@@ -256,6 +257,8 @@ def run_secondary(args):
         ops.check_status(dev)
         line["parallelism"] = ("ep" if cfg.n_experts else "tp") + str(world)
         line["tp_allreduce"] = args.tp_allreduce if world > 1 else None
+        if cfg.n_experts and world > 1:
+            line["ep_prefill"] = "all-to-all" if eng._ep_dispatch(P) else "replicated routing + all-reduce"
         nbytes = cfg.decode_bytes_per_token(P + W + K // 2)
         ref = {"qwen3-4b": {"decode_tok_per_s": 269.8, "ttft_ms": 9.58},
                "qwen3-30b-a3b": {"decode_tok_per_s": 241.1, "ttft_ms": 28.66}}[name]
@@ -349,6 +352,9 @@ def main():
     ap.add_argument("--ttft-runs", type=int, default=3)
     ap.add_argument("--tp-allreduce", default="fused", choices=["fused", "nccl"],
                     help="N>1: all-reduce fused into the decode kernels over peer memory, or NCCL calls")
+    ap.add_argument("--ep-all-to-all", action="store_true",
+                    help="expert-parallel prefill with an all-to-all dispatch / combine of token rows "
+                         "instead of replicated routing + all-reduce (A/B; measured slower)")
     ap.add_argument("--persistent-layers", action="store_true",
                     help="all layers of a decode step as one persistent launch instead of one launch "
                          "per phase (A/B; measured slower at 1 and 2 GPUs)")

@@ -16,13 +16,14 @@ XLMR = ("xlm-roberta-large", C.XLMR_LARGE, 64, 512, 4)
 WHISPER = ("whisper-large-v3", C.WHISPER_LARGE_V3, 5)
 WHISPER_PREFIX = [50258, 50259, 50360, 50364]
 WHISPER_STEPS = 224
+WHISPER_LOGIT_ROWS = 68      # logit rows carried to the oracle (prefix + first decode steps)
 
 
 def prompt(cfg, P, seed):
     return torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(seed))
 
 
-def probe_rows(P, seed, n=64):
+def probe_rows(P, seed, n=32):
     """Token rows whose per-layer hidden states are carried from the GPU run to the oracle: the
     first and last positions plus a seeded sample (all P rows of all layers would be GBs)."""
     g = torch.Generator().manual_seed(1000 + seed)

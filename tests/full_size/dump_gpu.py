@@ -1,8 +1,8 @@
 """GPU half of the full-size parity check: runs one benchmark configuration at full depth and
 width on cuda:0 with the seeded weights the oracle can regenerate, and writes what the oracle
 comparison needs to a small .npz (generated tokens, the logits of every decode step in fp16,
-per-layer hidden states of a sample of prompt rows and of the first decode step, MoE routing of
-the sampled rows).  The CPU half is tests/full_size/compare_cpu.py.
+per-layer hidden states of a sample of prompt rows (fp16) and of the first decode step, MoE routing
+of the sampled rows).  The CPU half is tests/full_size/compare_cpu.py.
 
     python -m tests.full_size.dump_gpu <config> <out.npz>
     config: qwen3-4b | llama-3.1-8b | qwen3-30b-a3b | xlm-roberta-large | whisper-large-v3
@@ -62,7 +62,7 @@ def dump_decoder(name, out):
     ops.check_status(dev)
     np.savez(out, config=name, toks=np.array(toks), toks_device_loop=np.array(toks2),
              logits=torch.stack(logits).numpy(), rows=np.array(rows),
-             prefill_hidden=prefill_hidden.numpy(), routed=routed_rows.numpy(),
+             prefill_hidden=prefill_hidden.to(torch.float16).numpy(), routed=routed_rows.numpy(),
              step_hidden=torch.stack([h.float().cpu() for h in step_hidden]).numpy(),
              weight_checksum=check, persistent_kernel=eng.plan is not None)
     print(f"{name}: tokens {toks[:8]}... device loop equal: {toks2 == toks}", flush=True)
@@ -85,7 +85,7 @@ def dump_xlmr(out):
     eng.capture()
     again = eng.embed(ids.to(dev)).cpu()
     np.savez(out, config=name, pooled=pooled.numpy(), pooled_graph=again.numpy(), rows=np.array(rows),
-             hidden=torch.stack([h[rows].float().cpu() for h in hid]).numpy())
+             hidden=torch.stack([h[rows].float().cpu() for h in hid]).to(torch.float16).numpy())
     print(f"{name}: pooled {tuple(pooled.shape)}, graph replay equal: {torch.equal(again, pooled)}")
 
 
@@ -109,9 +109,9 @@ def dump_whisper(out):
     logits = []
     toks = dec.generate(cases.WHISPER_PREFIX, cases.WHISPER_STEPS, collect_logits=logits)
     got = torch.stack(logits)                            # [prefix + steps - 1, V]
-    np.savez(out, config=name, toks=np.array(toks), logits=got.to(torch.float16).numpy(),
+    np.savez(out, config=name, toks=np.array(toks), logits=got[:cases.WHISPER_LOGIT_ROWS].to(torch.float16).numpy(),
              enc_out=enc_out.to(torch.float16).numpy(), rows=np.array(rows),
-             enc_hidden=torch.stack([h[rows].float().cpu() for h in hid]).numpy())
+             enc_hidden=torch.stack([h[rows].float().cpu() for h in hid]).to(torch.float16).numpy())
     print(f"{name}: {len(toks)} tokens {toks[:8]}...")
 
 

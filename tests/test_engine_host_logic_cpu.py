@@ -96,11 +96,12 @@ def _worker(rank, size, port, kind, fused, out):
         from hoid_optimized_models_b200.weights import make_decoder_weights
         comm.PeerLink = lambda *a, **k: _FakeLink()      # no CUDA IPC on the CPU
         torch.set_num_threads(2)
-        cfg = _cfg(kind)
+        cfg = _cfg(kind.split("-")[0])
         w = make_decoder_weights(cfg, 3)
         ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(3))
         eng = _engine(cfg, w, tp_rank=rank, tp_size=size, group=dist.group.WORLD,
-                      fused_allreduce=fused)
+                      fused_allreduce=fused, ep_all_to_all=kind.endswith("-a2a"))
+        assert eng._ep_dispatch(P) == kind.endswith("-a2a")
         assert (eng.link is not None) == fused
         toks = _generate(eng, ids)
         out.put((rank, toks, eng.logits.float().tolist()))
@@ -109,10 +110,12 @@ def _worker(rank, size, port, kind, fused, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind,fused", [("llama", False), ("llama", True), ("moe", False), ("moe", True)])
+# "moe-a2a": expert-parallel prefill with the all-to-all dispatch / combine of token rows
+@pytest.mark.parametrize("kind,fused", [("llama", False), ("llama", True), ("moe", False), ("moe", True),
+                                        ("moe-a2a", True)])
 def test_two_gloo_ranks_match_one(kind, fused):
     from hoid_optimized_models_b200.weights import make_decoder_weights
-    cfg = _cfg(kind)
+    cfg = _cfg(kind.split("-")[0])
     w = make_decoder_weights(cfg, 3)
     ids = torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(3))
     ref_eng = _engine(cfg, dict(w))
@@ -131,7 +134,7 @@ def test_two_gloo_ranks_match_one(kind, fused):
     for rank, toks, _ in res:
         assert toks == toks_ref, f"rank {rank}: {toks} vs {toks_ref}"
     # dense: the vocabulary is sharded over the ranks; MoE: every rank holds all logits
-    full = torch.tensor(res[0][2]) if kind == "moe" else torch.cat([torch.tensor(r[2]) for r in res])
+    full = torch.tensor(res[0][2]) if kind.startswith("moe") else torch.cat([torch.tensor(r[2]) for r in res])
     assert float((full - logits_ref).abs().max() / logits_ref.abs().max()) < 2e-2
 
 

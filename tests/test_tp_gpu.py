@@ -21,7 +21,7 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 N_NEW = 9
-P = 150
+P = 152          # divisible by 2, 4 and 8: the all-to-all prefill splits the prompt over the ranks
 
 
 def _port():
@@ -40,9 +40,11 @@ def _cfg(moe):
 def _engine_kwargs(mode):
     # "layers": persistent kernel with the exchange inside; "gemv": one launch per phase with the
     # exchange fused into the GEMVs; "nccl": one launch per phase and library all-reduces
+    # "a2a": expert-parallel prefill with the all-to-all dispatch / combine of token rows
     return {"layers": dict(fused_allreduce=True, fused_layers=True),
             "gemv": dict(fused_allreduce=True, fused_layers=False),
-            "nccl": dict(fused_allreduce=False, fused_layers=False)}[mode]
+            "nccl": dict(fused_allreduce=False, fused_layers=False),
+            "a2a": dict(fused_allreduce=True, ep_all_to_all=True)}[mode]
 
 
 def _worker(rank, size, port, moe, mode, out):
@@ -113,8 +115,9 @@ def _run_ranks(target, size, args):
 
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("moe,mode", [(False, "layers"), (False, "gemv"), (False, "nccl"),
-                                      (True, "gemv"), (True, "nccl")],
-                         ids=["dense-layers", "dense-gemv", "dense-nccl", "moe-fused", "moe-nccl"])
+                                      (True, "gemv"), (True, "nccl"), (True, "a2a")],
+                         ids=["dense-layers", "dense-gemv", "dense-nccl", "moe-fused", "moe-nccl",
+                              "moe-all-to-all"])
 def test_ranks_match_oracle_and_one_rank(dev, world, moe, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
