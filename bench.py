@@ -314,12 +314,22 @@ def run_secondary(args):
         enc_ms = _time_graph(enc.graph, max(8, K // 4), W)
         dec.set_encoder(enc.out)
         ops.check_status(dev)
+        # cross K / V projection + the 4-token forced prefix as one prefill pass
+        prefix = [50258, 50259, 50360, 50364]
+        dec.prefill(prefix, enc_out=enc.out)
+        pre = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); dec.prefill(prefix, enc_out=enc.out); e1.record(); torch.cuda.synchronize()
+            pre.append(e0.elapsed_time(e1))
         dec.capture()
         dec.set_step(7, 0, 0)
         n = min(K, 224)
         ms = _time_graph(dec.graph, n, W)   # positions 0 .. W + n of the 448-slot window
         line.update({"metric": "decode_tok_per_s", "value": 1e3 / ms, "unit": "tok/s", "ms_per_step": ms,
-                     "encoder_forward_ms": enc_ms, "gpu_launches": dec.launches_per_step * n,
+                     "encoder_forward_ms": enc_ms, "prefix_prefill_ms": statistics.median(pre),
+                     "gpu_launches": dec.launches_per_step * n,
                      "published_reference": {"decode_tok_per_s": 499.7, "decode_step_ms": 1.8219,
                                              "encoder_forward_ms": 3.525}})
     else:

@@ -200,6 +200,7 @@ class WhisperDecoder:
         self.ws_cross = ops.flash_decode_workspace(H, H, hd, self.cross_splits, dev)
         self.am_ws = ops.argmax_workspace(dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}      # prefix-prefill buffers by length
         self.launches_per_step = 4 + 9 * cfg.dec_layers + 3
 
     @torch.no_grad()
@@ -262,6 +263,71 @@ class WhisperDecoder:
         torch.cuda.synchronize()
         self.state.copy_(saved[0]); self.tok.copy_(saved[1]); self.tok_log.copy_(saved[2])
 
+    @torch.no_grad()
+    def prefill(self, prefix: List[int], enc_out: Optional[torch.Tensor] = None) -> int:
+        """The forced prefix in ONE pass over all its positions (and, with enc_out, the window's
+        cross K / V projection in front of it), as the reference's decoder prefill does
+        (models/whisper-large-v3/whisper_decoder_optimized.py:285-331): bf16 rows through the
+        tensor-core GEMMs and the prefill attention instead of one decode step per prefix token.
+        Fills the self-attention cache rows 0 .. len(prefix) - 1, leaves the step state at the next
+        position and returns the first generated token."""
+        cfg, dev = self.cfg, self.device
+        s, D, H, hd = len(prefix), cfg.d_model, cfg.heads, cfg.head_dim
+        if s < 1 or s > cfg.max_target:
+            raise ValueError(f"a prefix of {s} tokens does not fit the {cfg.max_target}-token window")
+        if enc_out is not None:
+            self.set_encoder(enc_out)
+        b = self._pbuf.get(s)
+        if b is None:
+            bf = lambda *sh: torch.zeros(*sh, dtype=torch.bfloat16, device=dev)
+            b = self._pbuf[s] = {
+                "ids": torch.zeros(s, dtype=torch.int32, device=dev),
+                "pos_ids": torch.arange(s, dtype=torch.int32, device=dev),
+                "pos0": torch.zeros(1, dtype=torch.int32, device=dev),
+                "e_tok": bf(s, D), "e_pos": bf(s, D), "x": bf(s, D), "h": bf(s, D),
+                "qkv": bf(s, 3 * D), "q": bf(s, D), "att": bf(s, D), "cq": bf(s, D), "act": bf(s, cfg.ffn),
+            }
+        b["ids"].copy_(torch.tensor(prefix, dtype=torch.int32))
+        x, h, att = b["x"], b["h"], b["att"]
+        scale = hd ** -0.5
+        att4 = att.view(1, s, H, hd)
+        ops.embed_gather(b["e_tok"], self.embed_tok, b["ids"])
+        ops.embed_gather(b["e_pos"], self.embed_pos, b["pos_ids"])
+        for i, L in enumerate(self.layers):
+            if i == 0:    # residual stream = token + position embedding, fused with the first norm
+                ops.add_layernorm(h, x, b["e_tok"], L["ln1"][0], L["ln1"][1], cfg.eps, resid=b["e_pos"])
+            else:
+                ops.layernorm(h, x, L["ln1"][0], L["ln1"][1], cfg.eps)
+            ops.gemm(b["qkv"], h, L["wqkv"], bias=L["bqkv"])
+            # identity cos / sin tables: a plain write of the k / v rows into cache rows 0 .. s - 1
+            ops.qk_rope_cache(b["q"], self.kv[i, 0], self.kv[i, 1], b["qkv"], self.cos, self.sin,
+                              b["pos0"], H, H)
+            ops.flash_prefill(att4, b["q"].view(1, s, H, hd), self.kv[i, 0].unsqueeze(0),
+                              self.kv[i, 1].unsqueeze(0), s, True, scale)
+            ops.gemm(x, att, L["wo"], bias=L["bo"], resid=x)
+            ops.layernorm(h, x, L["ln2"][0], L["ln2"][1], cfg.eps)
+            ops.gemm(b["cq"], h, L["wcq"], bias=L["bcq"])
+            ck = self.cross_k[i].view(1, cfg.n_ctx, H, hd).permute(0, 2, 1, 3)
+            cv = self.cross_v[i].view(1, cfg.n_ctx, H, hd).permute(0, 2, 1, 3)
+            ops.flash_prefill(att4, b["cq"].view(1, s, H, hd), ck, cv, cfg.n_ctx, False, scale)
+            ops.gemm(x, att, L["wco"], bias=L["bco"], resid=x)
+            ops.layernorm(h, x, L["ln3"][0], L["ln3"][1], cfg.eps)
+            ops.gemm(b["act"], h, L["wf1"], bias=L["bf1"], epilogue=ops.EPI_GELU)
+            ops.gemm(x, b["act"], L["wf2"], bias=L["bf2"], resid=x)
+        # logits of the last prefix position only; it yields the first new token
+        if self.logit_bias is not None:
+            self.logit_bias.copy_(self._begin_bias)
+        ops.gemv(self.logits, x[s - 1], self.embed_tok, norm_w=self.ln_f[0], norm_b=self.ln_f[1],
+                 eps=cfg.eps, bias=self.logit_bias)
+        ops.argmax(self.cand, self.logits, self.am_ws)
+        ops.greedy_select(self.tok, self.cand)
+        first = int(self.tok.item())
+        if self.logit_bias is not None:
+            self.logit_bias.copy_(self._steady_bias)
+        self.state.copy_(torch.tensor([s, s + 1, 0, 0], dtype=torch.int32))
+        ops.check_status(dev)
+        return first
+
     def set_step(self, tok: int, pos: int, generated: int = 0) -> None:
         if pos < 0 or pos + 1 > self.cfg.max_target:
             raise ValueError(f"position {pos} is outside the {self.cfg.max_target}-token window")
@@ -275,28 +341,33 @@ class WhisperDecoder:
             self.step_static()
 
     @torch.no_grad()
-    def generate(self, prefix: List[int], n_new: int, collect_logits: Optional[list] = None) -> List[int]:
-        """Feeds the forced prefix token by token (teacher forcing), then decodes n_new tokens
-        greedily.  Returns the generated tokens."""
+    def generate(self, prefix: List[int], n_new: int, collect_logits: Optional[list] = None,
+                 prefix_prefill: bool = True) -> List[int]:
+        """Runs the forced prefix (one prefill pass; token by token when the logits of every
+        position are collected or prefix_prefill is off), then decodes n_new tokens greedily.
+        Returns the generated tokens."""
         if n_new > self.tok_log.numel() + 1:
             raise ValueError("n_new exceeds max_new_tokens")
         if len(prefix) + n_new - 1 > self.cfg.max_target:
             # positions index the learned position table and the self-attention cache
             raise ValueError(f"{len(prefix)} prefix + {n_new - 1} decode positions exceed the "
                              f"{self.cfg.max_target}-token window")
-        for p, t in enumerate(prefix):
-            self.set_step(t, p, 0)
-            if self.logit_bias is not None and p == len(prefix) - 1:
-                self.logit_bias.copy_(self._begin_bias)      # this step yields the first new token
-            self._run()
-            if collect_logits is not None:
-                collect_logits.append(self.logits.float().cpu().clone())
-        # the step for the last prefix token has already produced the first new token
-        out = [int(self.tok.item())]
-        if self.logit_bias is not None:
-            self.logit_bias.copy_(self._steady_bias)
-        pos = len(prefix)
-        self.state.copy_(torch.tensor([pos, pos + 1, 0, 0], dtype=torch.int32))
+        if prefix_prefill and collect_logits is None:
+            out = [self.prefill(prefix)]
+        else:
+            for p, t in enumerate(prefix):
+                self.set_step(t, p, 0)
+                if self.logit_bias is not None and p == len(prefix) - 1:
+                    self.logit_bias.copy_(self._begin_bias)      # this step yields the first new token
+                self._run()
+                if collect_logits is not None:
+                    collect_logits.append(self.logits.float().cpu().clone())
+            # the step for the last prefix token has already produced the first new token
+            out = [int(self.tok.item())]
+            if self.logit_bias is not None:
+                self.logit_bias.copy_(self._steady_bias)
+            pos = len(prefix)
+            self.state.copy_(torch.tensor([pos, pos + 1, 0, 0], dtype=torch.int32))
         for _ in range(n_new - 1):
             self._run()
             if collect_logits is not None:

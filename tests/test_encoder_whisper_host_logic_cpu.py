@@ -125,6 +125,17 @@ def test_whisper_matches_oracle_on_cpu():
     for j, (a, b) in enumerate(zip(toks, ref_toks)):
         k = len(prefix) - 1 + j
         assert a == b or float(top2[k, 0] - top2[k, 1]) < 2e-2, (j, toks, ref_toks)
+    # the forced prefix as one prefill pass: same cache rows, same first token and continuation
+    # (bf16 rows against fp32 vectors: a token may differ only at an oracle near-tie)
+    kv_steps = dec.kv[:, :, :, :len(prefix)].float().clone()
+    dec.kv.zero_()
+    toks2 = dec.generate(prefix, n_new)
+    assert float((dec.kv[:, :, :, :len(prefix)].float() - kv_steps).abs().max()) < 2e-2 * float(kv_steps.abs().max())
+    for j, (a, b) in enumerate(zip(toks2, ref_toks)):
+        k = len(prefix) - 1 + j
+        assert a == b or float(top2[k, 0] - top2[k, 1]) < 2e-2, (j, toks2, ref_toks)
+        if a != b:
+            break                                        # teacher forcing ends at the first flip
 
 
 def test_encoder_and_whisper_from_checkpoints_on_cpu(tmp_path):

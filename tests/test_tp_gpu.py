@@ -151,7 +151,13 @@ def test_ranks_match_oracle_and_one_rank(dev, world, moe, mode):
     _, logits_or, _ = decoder_forward(cfg, w, seq, logits_rows=range(P, P + N_NEW - 1),
                                       keep_hidden=False)
     cos = torch.nn.functional.cosine_similarity(full, logits_or, dim=-1)
-    assert float(cos.min()) >= 0.999, float(cos.min())
+    if moe:
+        # a decode step whose token is routed to a different expert at a near-tie of the router
+        # (bf16 router input against the fp32 oracle; the one-rank engine does the same, see the
+        # bound above) shows in the logits: allowed on a few steps, as in tests/test_decoder_gpu.py
+        assert int((cos < 0.999).sum()) <= 3 and float(cos.min()) >= 0.99, cos.tolist()
+    else:
+        assert float(cos.min()) >= 0.999, float(cos.min())
     top2 = logits_or.topk(2, -1).values
     noise = (full - logits_or).abs().max(-1).values
     for j in range(N_NEW - 1):                               # greedy parity, near-ties excepted
