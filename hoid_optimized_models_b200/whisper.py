@@ -201,6 +201,7 @@ class WhisperDecoder:
         self.am_ws = ops.argmax_workspace(dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._pbuf: Dict[int, Dict[str, torch.Tensor]] = {}      # prefix-prefill buffers by length
+        self._pgraphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 4 + 9 * cfg.dec_layers + 3
 
     @torch.no_grad()
@@ -263,31 +264,12 @@ class WhisperDecoder:
         torch.cuda.synchronize()
         self.state.copy_(saved[0]); self.tok.copy_(saved[1]); self.tok_log.copy_(saved[2])
 
-    @torch.no_grad()
-    def prefill(self, prefix: List[int], enc_out: Optional[torch.Tensor] = None) -> int:
-        """The forced prefix in ONE pass over all its positions (and, with enc_out, the window's
-        cross K / V projection in front of it), as the reference's decoder prefill does
-        (models/whisper-large-v3/whisper_decoder_optimized.py:285-331): bf16 rows through the
-        tensor-core GEMMs and the prefill attention instead of one decode step per prefix token.
-        Fills the self-attention cache rows 0 .. len(prefix) - 1, leaves the step state at the next
-        position and returns the first generated token."""
-        cfg, dev = self.cfg, self.device
-        s, D, H, hd = len(prefix), cfg.d_model, cfg.heads, cfg.head_dim
-        if s < 1 or s > cfg.max_target:
-            raise ValueError(f"a prefix of {s} tokens does not fit the {cfg.max_target}-token window")
+    def _prefill_launches(self, b: Dict[str, torch.Tensor], s: int, enc_out: Optional[torch.Tensor]) -> None:
+        """Every launch of one prefix prefill over the buffers `b` (no host synchronisation)."""
+        cfg = self.cfg
+        D, H, hd = cfg.d_model, cfg.heads, cfg.head_dim
         if enc_out is not None:
             self.set_encoder(enc_out)
-        b = self._pbuf.get(s)
-        if b is None:
-            bf = lambda *sh: torch.zeros(*sh, dtype=torch.bfloat16, device=dev)
-            b = self._pbuf[s] = {
-                "ids": torch.zeros(s, dtype=torch.int32, device=dev),
-                "pos_ids": torch.arange(s, dtype=torch.int32, device=dev),
-                "pos0": torch.zeros(1, dtype=torch.int32, device=dev),
-                "e_tok": bf(s, D), "e_pos": bf(s, D), "x": bf(s, D), "h": bf(s, D),
-                "qkv": bf(s, 3 * D), "q": bf(s, D), "att": bf(s, D), "cq": bf(s, D), "act": bf(s, cfg.ffn),
-            }
-        b["ids"].copy_(torch.tensor(prefix, dtype=torch.int32))
         x, h, att = b["x"], b["h"], b["att"]
         scale = hd ** -0.5
         att4 = att.view(1, s, H, hd)
@@ -315,12 +297,57 @@ class WhisperDecoder:
             ops.gemm(b["act"], h, L["wf1"], bias=L["bf1"], epilogue=ops.EPI_GELU)
             ops.gemm(x, b["act"], L["wf2"], bias=L["bf2"], resid=x)
         # logits of the last prefix position only; it yields the first new token
-        if self.logit_bias is not None:
-            self.logit_bias.copy_(self._begin_bias)
         ops.gemv(self.logits, x[s - 1], self.embed_tok, norm_w=self.ln_f[0], norm_b=self.ln_f[1],
                  eps=cfg.eps, bias=self.logit_bias)
         ops.argmax(self.cand, self.logits, self.am_ws)
         ops.greedy_select(self.tok, self.cand)
+
+    @torch.no_grad()
+    def prefill(self, prefix: List[int], enc_out: Optional[torch.Tensor] = None,
+                graph: Optional[bool] = None) -> int:
+        """The forced prefix in ONE pass over all its positions (and, with enc_out, the window's
+        cross K / V projection in front of it), as the reference's decoder prefill does
+        (models/whisper-large-v3/whisper_decoder_optimized.py:285-331): bf16 rows through the
+        tensor-core GEMMs and the prefill attention instead of one decode step per prefix token.
+        Fills the self-attention cache rows 0 .. len(prefix) - 1, leaves the step state at the next
+        position and returns the first generated token."""
+        cfg, dev = self.cfg, self.device
+        s, D, H, hd = len(prefix), cfg.d_model, cfg.heads, cfg.head_dim
+        if s < 1 or s > cfg.max_target:
+            raise ValueError(f"a prefix of {s} tokens does not fit the {cfg.max_target}-token window")
+        b = self._pbuf.get(s)
+        if b is None:
+            bf = lambda *sh: torch.zeros(*sh, dtype=torch.bfloat16, device=dev)
+            b = self._pbuf[s] = {
+                "ids": torch.zeros(s, dtype=torch.int32, device=dev),
+                "pos_ids": torch.arange(s, dtype=torch.int32, device=dev),
+                "pos0": torch.zeros(1, dtype=torch.int32, device=dev),
+                "e_tok": bf(s, D), "e_pos": bf(s, D), "x": bf(s, D), "h": bf(s, D),
+                "qkv": bf(s, 3 * D), "q": bf(s, D), "att": bf(s, D), "cq": bf(s, D), "act": bf(s, cfg.ffn),
+            }
+        b["ids"].copy_(torch.tensor(prefix, dtype=torch.int32))
+        if self.logit_bias is not None:
+            self.logit_bias.copy_(self._begin_bias)      # this pass yields the first new token
+        # ~15 launches per layer for a handful of rows: replayed from a CUDA graph captured per
+        # (prefix length, encoder buffer), the pass is bound by the kernels, not by the host
+        use_graph = graph if graph is not None else self.device.type == "cuda"
+        if use_graph:
+            key = (s, enc_out.data_ptr() if enc_out is not None else 0)
+            g = self._pgraphs.get(key)
+            if g is None:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    self._prefill_launches(b, s, enc_out)            # warm-up outside the capture
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._prefill_launches(b, s, enc_out)
+                self._pgraphs[key] = g
+            g.replay()
+        else:
+            self._prefill_launches(b, s, enc_out)
         first = int(self.tok.item())
         if self.logit_bias is not None:
             self.logit_bias.copy_(self._steady_bias)

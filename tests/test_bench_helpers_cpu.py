@@ -49,3 +49,18 @@ def test_cpu_arm_record_on_a_tiny_model():
     assert rec["kind"] == "reference" and rec["unit"] == "tok/s" and rec["cores"] >= 1
     assert rec["value"] > 0 and abs(rec["ms_per_step"] - 1e3 / rec["value"]) < 1e-6
     assert "2 of 8 layers" in rec["sample"] and "scaled x4" in rec["sample"]
+
+
+def test_traffic_is_read_from_the_tracked_figures_file(tmp_path):
+    """roofline.traffic comes from profiles/ncu_traffic.json (written beside the ncu summaries),
+    scaled by depth when the capture was taken on a reduced-depth model; no file, no number."""
+    b = _bench()
+    tracked = b.ncu_traffic("gemv_kernel_gate_up", 32)
+    assert tracked is not None and 2.3e8 < tracked < 2.5e8          # the committed capture
+    b.ROOT = str(tmp_path)
+    assert b.ncu_traffic("gemv_kernel_gate_up", 32) is None
+    os.makedirs(tmp_path / "profiles")
+    with open(tmp_path / "profiles" / "ncu_traffic.json", "w") as f:
+        json.dump({"k": {"dram_bytes_per_launch": 100.0, "layers": 2}, "flat": {"dram_bytes_per_launch": 7.0}}, f)
+    assert b.ncu_traffic("k", 32) == 1600.0 and b.ncu_traffic("flat", 32) == 7.0
+    assert b.ncu_traffic("missing", 32) is None

@@ -1,4 +1,4 @@
-"""The lane-to-element mappings of the two mma.sync kernels, checked on the CPU against an
+"""The lane-to-element mapping of the mma.sync decode-attention kernels, checked on the CPU against an
 emulation of the m16n8k16 fragment layout of the PTX ISA (lane = 4 g + tq):
   A (16x16): a0 = A[g][2tq, 2tq+1], a1 = A[g+8][same], a2 = A[g][2tq+8, 2tq+9], a3 = A[g+8][same]
   B (16x8) : b0 = B[2tq, 2tq+1][g], b1 = B[2tq+8, 2tq+9][g]
@@ -22,37 +22,6 @@ def mma(a_regs, b_regs):
     return np.array([[D[l >> 2, 2 * (l & 3)], D[l >> 2, 2 * (l & 3) + 1],
                       D[(l >> 2) + 8, 2 * (l & 3)], D[(l >> 2) + 8, 2 * (l & 3) + 1]]
                      for l in range(32)])
-
-
-def test_gemv_mapping_visits_every_weight_once():
-    """gemv_mma_kernel: lane (g, tq) loads 16 consecutive weights of rows g and g + 8 per 64-column
-    step and uses them in storage order; column 0 / 1 of B carry the high / low part of x."""
-    rng = np.random.default_rng(0)
-    K = 256
-    W, x = rng.standard_normal((16, K)), rng.standard_normal(K)
-    xh = np.round(x * 64) / 64
-    xl = x - xh                                   # any exact high + low split
-    acc = np.zeros((32, 4))
-    for u in range(K // 64):
-        def chunk(row, lane):
-            k = u * 64 + (lane & 3) * 16
-            return W[row, k:k + 16]
-        for m in range(4):                        # MMA m: elements 4m .. 4m+3 of the lane's 16
-            a, b = [], []
-            for lane in range(32):
-                g, tq = lane >> 2, lane & 3
-                ra, rb = chunk(g, lane), chunk(g + 8, lane)
-                a.append([ra[4 * m:4 * m + 2], rb[4 * m:4 * m + 2],
-                          ra[4 * m + 2:4 * m + 4], rb[4 * m + 2:4 * m + 4]])
-                col = xh if g == 0 else xl if g == 1 else np.zeros(K)
-                xs = col[u * 64 + tq * 16: u * 64 + tq * 16 + 16]
-                b.append([xs[4 * m:4 * m + 2], xs[4 * m + 2:4 * m + 4]])
-            acc += mma(a, b)
-    y = np.zeros(16)
-    for lane in range(0, 32, 4):                  # tq == 0 holds columns 0 and 1
-        y[lane >> 2] = acc[lane][0] + acc[lane][1]
-        y[(lane >> 2) + 8] = acc[lane][2] + acc[lane][3]
-    assert np.abs(y - W @ x).max() < 1e-12
 
 
 def test_attention_rows_carry_high_and_low_parts():
@@ -89,42 +58,6 @@ def test_attention_rows_carry_high_and_low_parts():
             got = [s[lane, nb, 0] + s[lane, nb, 2], s[lane, nb, 1] + s[lane, nb, 3]]
             want = ref[g, nb * 8 + tq * 2: nb * 8 + tq * 2 + 2]
             assert np.abs(np.array(got) - want).max() < 1e-12
-
-
-def _gemv_visits(K, nrows):
-    """Replays the work split of gemv_mma_kernel for one CTA: which (row, k) every lane of every
-    warp loads in every step, with the kernel's own index arithmetic."""
-    warps = 8
-    units = K >> 6
-    ngroups = (nrows + 15) >> 4
-    seen = np.zeros((nrows, K), dtype=np.int32)
-    parked = np.zeros((ngroups * 16, warps), dtype=np.int32)
-    for warp in range(warps):
-        u0, u1 = units * warp // warps, units * (warp + 1) // warps
-        nu = u1 - u0
-        for s in range(ngroups * nu):
-            grp = s // nu
-            u = u0 + (s - grp * nu)
-            for lane in range(32):
-                g, tq = lane >> 2, lane & 3
-                for half in (0, 8):
-                    row = grp * 16 + g + half
-                    if row < nrows:                       # clamped rows are loaded but never used
-                        k = u * 64 + tq * 16
-                        seen[row, k:k + 16] += 1
-            if s - grp * nu == nu - 1:
-                parked[grp * 16:(grp + 1) * 16, warp] += 1
-    return seen, parked, units
-
-
-def test_gemv_work_split_covers_every_weight_exactly_once():
-    for K in (256, 768, 1280, 4096, 14336):
-        for nrows in (1, 7, 16, 21, 98):
-            seen, parked, units = _gemv_visits(K, nrows)
-            assert (seen == 1).all(), (K, nrows)
-            # a warp parks its sums for a group exactly once iff it owns part of K
-            owns = np.array([units * (w + 1) // 8 > units * w // 8 for w in range(8)])
-            assert (parked[:, owns] == 1).all() and (parked[:, ~owns] == 0).all(), (K, nrows)
 
 
 def test_decode_attention_tiles_cover_every_key_exactly_once():
