@@ -1,19 +1,31 @@
 // Prefill / encoder flash attention on the sm_100a tensor cores (tcgen05 + TMEM + TMA).
 //
-// One CTA owns 128 query rows of one head and walks the keys in tiles of 128:
-//   warp 0     TMA producer: Q once, then K and V tiles into a 2-stage ring
+// Persistent: one CTA per SM walks a list of work items (128 query rows of one head each) and,
+// inside an item, the keys in tiles of 128.  The three roles run decoupled through mbarrier
+// rings that are never drained between items, so the next item's Q / K / V loads and its first
+// S = Q K^T are in flight while the softmax warps finish the current one:
+//   warp 0     TMA producer: Q per item (two buffers at head dim 64), K and V tiles into a ring
+//              of 4 (head dim 64) or 2 (head dim 128) stages
 //   warp 1     MMA issuer (one lane): S_j = Q K_j^T (M128 N128, K = head dim) into one of two
 //              S accumulators in tensor memory, and O_j = P_j V_j (V consumed in its natural
-//              [key][dim] layout as an MN-major operand) into one of two O-tile accumulators
+//              [key][dim] layout as an MN-major operand) into the O-tile accumulator
 //   warps 2-17 softmax: four threads per query row (= TMEM lane), each owning 32 key columns
 //              and a quarter of the output dims.  A thread pulls its 32 scores with one
 //              tcgen05.ld, the row maximum is exchanged between the four through shared memory,
-//              O_{j-1} is folded from tensor memory into fp32 registers with the online-softmax
-//              correction, and P_j = exp2(...) is written as bf16 into the 128-byte-swizzled
-//              shared tile the second MMA reads.  S is double-buffered, so the tensor core works
-//              on S_{j+1} and O_j while the softmax warps are busy with tile j.
+//              P_j = exp2(...) is written as bf16 into the 128-byte-swizzled shared tile the
+//              second MMA reads, and only then O_{j-1} is folded from tensor memory into fp32
+//              registers with the online-softmax correction.  S and O are double-buffered in
+//              tensor memory, so the tensor core works on S_{j+1} and O_j while the softmax
+//              warps are busy, and the softmax warps never wait for an MMA they just asked for.
+// Work order: causal items heaviest query tile first, dealt to the CTAs in alternating direction
+// (round r forwards, round r + 1 backwards) so every CTA gets the same number of key tiles to
+// within one round; bidirectional items with the query tiles of one head adjacent, so a head's
+// K / V are read from DRAM once and from L2 afterwards.
 // The score matrix never leaves the SM.  Causal tiles above the diagonal are never visited.
 // Every mbarrier wait is bounded (status word + clean TMEM release on expiry).
+#include <algorithm>
+#include <climits>
+
 #include "sm100.cuh"
 
 namespace b200 {
@@ -27,12 +39,39 @@ struct FaArgs {
   uint16_t* o; long o_bs, o_rs, o_hs;
   int* status;
   int S, kv_len, q_pos0, group, causal, n_q;
+  int n_mt, n_bh, n_items;          // query tiles per head, batch x heads, work items
   // row / column bookkeeping of the 2D views the tensor maps cover
   int q_batch_rows, q_head_rows, q_head_cols;
   int k_batch_rows, k_head_rows, k_head_cols;
   int v_batch_rows, v_head_rows, v_head_cols;
   float scale_log2;
 };
+
+struct FaItem { int b, head, m0, ntiles; };
+
+// The work item of this CTA in round r (false: the round has none for it).  All three roles
+// call this with the same arguments and therefore walk identical lists.
+__device__ __forceinline__ bool fa_item(const FaArgs& a, int r, FaItem& it) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  const int w = r * G + ((a.causal && (r & 1)) ? G - 1 - c : c);
+  if (w >= a.n_items) return false;
+  int mt, bh;
+  if (a.causal) { mt = a.n_mt - 1 - w / a.n_bh; bh = w % a.n_bh; }
+  else { mt = w % a.n_mt; bh = w / a.n_mt; }
+  it.head = bh % a.n_q;
+  it.b = bh / a.n_q;
+  it.m0 = mt * FA_BM;
+  int kv_end = a.kv_len;
+  if (a.causal) kv_end = min(kv_end, a.q_pos0 + it.m0 + FA_BM);
+  it.ntiles = (kv_end + FA_BN - 1) / FA_BN;      // >= 1: kv_len >= 1 and q_pos0 >= 0
+  return true;
+}
+
+// Bounded wait without an abort flag, for the teardown of a role that already gave up.
+__device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity, long long ticks) {
+  const long long t0 = clock64();
+  while (!mbar_try(bar, parity) && clock64() - t0 < ticks) {}
+}
 
 // UMMA descriptor for an MN-major, 128-byte-swizzled operand: 64 contiguous MN elements per
 // 128-byte row, rows = K index; 8-row groups SBO bytes apart, 64-element MN blocks LBO apart.
@@ -66,43 +105,42 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                         const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, FaArgs a) {
   constexpr int ATOMS = HD / 64;                        // 64-column boxes per operand tile
+  constexpr int NQ = HD == 64 ? 2 : 1;                  // Q buffers
+  constexpr int NST = HD == 64 ? 4 : 2;                 // K | V stages
   constexpr uint32_t kQBytes = ATOMS * kAtomBytes;      // Q / K / V tile bytes
   constexpr uint32_t kPBytes = 2 * kAtomBytes;          // P tile: 128 rows x 128 keys
   constexpr uint32_t kStage = 2 * kQBytes;              // K + V
+  constexpr uint32_t kTiles = NQ * kQBytes + NST * kStage + kPBytes;   // 192 KiB either way
+  // barrier indices
+  constexpr int QF = 0, QE = NQ, KF = 2 * NQ, KE = 2 * NQ + NST, SF = 2 * NQ + 2 * NST,
+                PF = SF + 2, OF = SF + 3, NBAR = SF + 4;
+  static_assert(NBAR <= 16, "barrier block is 16 entries");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // Operand tiles need 1024-byte alignment.  The whole 227 KB of shared memory is in use at
-  // head dim 128, so there is no room for alignment slack: the dynamic window starts 1 KB into
-  // the CTA's shared memory (after the system-reserved kilobyte) and is therefore aligned; if a
-  // future toolchain breaks that assumption the kernel reports it instead of corrupting tiles.
+  // Operand tiles need 1024-byte alignment.  The dynamic window starts 1 KB into the CTA's
+  // shared memory (after the system-reserved kilobyte) and is therefore aligned; if a future
+  // toolchain breaks that assumption the kernel reports it instead of corrupting tiles.
   const uint32_t base = smem_u32(smem_raw);
   if ((base & 1023u) != 0) {
     if (threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, B200_ERR_ALIGN);
     return;
   }
   unsigned char* gen = smem_raw;
-  const uint32_t sQ = base;
-  const uint32_t sKV = sQ + kQBytes;                    // 2 stages x (K | V)
-  const uint32_t sP = sKV + 2 * kStage;                 // one buffer (freed by the O_j commit)
-  unsigned char* gP = gen + kQBytes + 2 * kStage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kQBytes + 2 * kStage + kPBytes);
-  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7 p_full | 9 o_full
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  const uint32_t sQ = base;                             // NQ buffers
+  const uint32_t sKV = sQ + NQ * kQBytes;               // NST stages x (K | V)
+  unsigned char* gP = gen + NQ * kQBytes + NST * kStage;   // one buffer (freed by the O_j commit)
+  const uint32_t sP = smem_u32(gP);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kTiles);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xch = reinterpret_cast<float*>(tmem_slot + 4);   // [2 parities][4 parts][128 rows] + seq
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mtile = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int m0 = mtile * FA_BM;
-  const int head = blockIdx.y, b = blockIdx.z;
-  const int kvh = head / a.group;
+  const int n_rounds = (a.n_items + (int)gridDim.x - 1) / (int)gridDim.x;
 
   pdl_launch_dependents();
   if (tid == 0) {
-    mbar_init(bar(0), 1);
-    for (int i = 1; i <= 6; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(7), 128 * kFaParts); mbar_init(bar(8), 1);
-    mbar_init(bar(9), 1); mbar_init(bar(10), 1);
+    for (int i = 0; i < NBAR; ++i) mbar_init(bar(i), i == PF ? 4 * kFaParts : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -122,79 +160,108 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base;            // S buffers at columns 0 and 128
-  const uint32_t tO = tmem_base + 256;      // O-tile accumulator
-
-  // keys this query tile can see
-  int kv_end = a.kv_len;
-  if (a.causal) kv_end = min(kv_end, a.q_pos0 + m0 + FA_BM);
-  const int ntiles = (kv_end + FA_BN - 1) / FA_BN;
+  const uint32_t tO = tmem_base + 256;      // two O-tile accumulators, HD columns each
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && ntiles > 0) {
-      const int q_row = b * a.q_batch_rows + head * a.q_head_rows + m0;
-      const int q_col = head * a.q_head_cols;
-      mbar_expect_tx(bar(0), kQBytes);
-#pragma unroll
-      for (int t = 0; t < ATOMS; ++t) tma_load_2d(sQ + t * kAtomBytes, &map_q, bar(0), q_col + 64 * t, q_row);
-      const int k_row0 = b * a.k_batch_rows + kvh * a.k_head_rows, k_col = kvh * a.k_head_cols;
-      const int v_row0 = b * a.v_batch_rows + kvh * a.v_head_rows, v_col = kvh * a.v_head_cols;
+    if (lane == 0) {
+      int qi = 0, g = 0;           // items and key tiles issued so far
       bool ok = true;
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(bar(3 + st), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        const uint32_t sk = sKV + st * kStage, sv = sk + kQBytes;
-        mbar_expect_tx(bar(1 + st), kStage);
+      for (int r = 0; r < n_rounds && ok; ++r) {
+        FaItem it;
+        if (!fa_item(a, r, it)) continue;
+        const int kvh = it.head / a.group;
+        const int qb = qi % NQ;
+        if (!mbar_wait(bar(QE + qb), ((qi / NQ) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const int q_row = it.b * a.q_batch_rows + it.head * a.q_head_rows + it.m0;
+        const int q_col = it.head * a.q_head_cols;
+        mbar_expect_tx(bar(QF + qb), kQBytes);
 #pragma unroll
-        for (int t = 0; t < ATOMS; ++t) {
-          tma_load_2d(sk + t * kAtomBytes, &map_k, bar(1 + st), k_col + 64 * t, k_row0 + j * FA_BN);
-          tma_load_2d(sv + t * kAtomBytes, &map_v, bar(1 + st), v_col + 64 * t, v_row0 + j * FA_BN);
+        for (int t = 0; t < ATOMS; ++t)
+          tma_load_2d(sQ + qb * kQBytes + t * kAtomBytes, &map_q, bar(QF + qb), q_col + 64 * t, q_row);
+        ++qi;
+        const int k_row0 = it.b * a.k_batch_rows + kvh * a.k_head_rows, k_col = kvh * a.k_head_cols;
+        const int v_row0 = it.b * a.v_batch_rows + kvh * a.v_head_rows, v_col = kvh * a.v_head_cols;
+        for (int j = 0; j < it.ntiles; ++j, ++g) {
+          const int st = g % NST;
+          if (!mbar_wait(bar(KE + st), ((g / NST) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t sk = sKV + st * kStage, sv = sk + kQBytes;
+          mbar_expect_tx(bar(KF + st), kStage);
+#pragma unroll
+          for (int t = 0; t < ATOMS; ++t) {
+            tma_load_2d(sk + t * kAtomBytes, &map_k, bar(KF + st), k_col + 64 * t, k_row0 + j * FA_BN);
+            tma_load_2d(sv + t * kAtomBytes, &map_v, bar(KF + st), v_col + 64 * t, v_row0 + j * FA_BN);
+          }
         }
       }
       if (!ok) {
-        for (int i = 0; i <= 2; ++i) {
-          const long long t0 = clock64();
-          while (!mbar_try(bar(i), 0) && !mbar_try(bar(i), 1) && clock64() - t0 < 2000000) {}
-        }
+        // give the copies still in flight a bounded time to land before the CTA retires
+        for (int i = 1; i <= min(g, NST); ++i)
+          mbar_wait_quiet(bar(KF + (g - i) % NST), ((g - i) / NST) & 1, 2000000);
+        for (int i = 1; i <= min(qi, NQ); ++i)
+          mbar_wait_quiet(bar(QF + (qi - i) % NQ), ((qi - i) / NQ) & 1, 2000000);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && ntiles > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_s = fa_idesc(FA_BN, 0);
       constexpr uint32_t idesc_o = fa_idesc(HD, 1);
-      bool ok = mbar_wait(bar(0), 0, abort_flag);
-      auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(bar(1 + st), (j >> 1) & 1, abort_flag)) return false;
+      // key tiles of all my items
+      int total = 0;
+      for (int r = 0; r < n_rounds; ++r) { FaItem it; if (fa_item(a, r, it)) total += it.ntiles; }
+      // Cursor of the S = Q K^T issue.  It runs one tile ahead of the O = P V issue and crosses
+      // item boundaries; when its operands have not landed yet the O MMAs go first.
+      int s_r = -1, s_j = 0, s_n = 0, s_qi = -1, s_g = 0;
+      bool s_new_q = false;
+      // 1 issued, 0 operands not there yet (only when !blocking), -1 gave up
+      auto issue_s = [&](bool blocking) -> int {
+        if (s_j == s_n) {                     // first tile of the next item
+          FaItem it;
+          do { ++s_r; } while (s_r < n_rounds && !fa_item(a, s_r, it));
+          if (s_r >= n_rounds) return -1;
+          s_n = it.ntiles; s_j = 0; ++s_qi; s_new_q = true;
+        }
+        const int st = s_g % NST, qb = s_qi % NQ;
+        if (!blocking) {
+          if (s_new_q && !mbar_try(bar(QF + qb), (s_qi / NQ) & 1)) return 0;
+          if (!mbar_try(bar(KF + st), (s_g / NST) & 1)) return 0;
+        } else {
+          if (s_new_q && !mbar_wait(bar(QF + qb), (s_qi / NQ) & 1, abort_flag)) return -1;
+          if (!mbar_wait(bar(KF + st), (s_g / NST) & 1, abort_flag)) return -1;
+        }
+        s_new_q = false;
         tc_fence_after();
-        const uint32_t sk = sKV + st * kStage;
+        const uint32_t sk = sKV + st * kStage, sq = sQ + qb * kQBytes;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          tc_mma(tS + st * FA_BN, umma_desc_k(sQ + off), umma_desc_k(sk + off), idesc_s, k != 0 ? 1u : 0u);
+          tc_mma(tS + (s_g & 1) * FA_BN, umma_desc_k(sq + off), umma_desc_k(sk + off), idesc_s, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar(5 + st));
-        return true;
+        tc_commit(bar(SF + (s_g & 1)));
+        ++s_j; ++s_g;
+        if (s_j == s_n) tc_commit(bar(QE + qb));   // Q buffer free once these MMAs retire
+        return 1;
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int st = j & 1;
-        if (j + 1 < ntiles) { if (!issue_s(j + 1)) { ok = false; break; } }
-        if (!mbar_wait(bar(7), j & 1, abort_flag)) { ok = false; break; }
+      bool ok = total > 0 && issue_s(true) == 1;
+      for (int g = 0; g < total && ok; ++g) {
+        const int st = g % NST;
+        int ahead = 1;
+        if (g + 1 < total) { ahead = issue_s(false); if (ahead < 0) { ok = false; break; } }
+        if (!mbar_wait(bar(PF), g & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sv = sKV + st * kStage + kQBytes;
-        const uint32_t sp = sP;
 #pragma unroll
         for (int k = 0; k < FA_BN / 16; ++k) {
           // A = P (K-major over keys): 16 keys = 32 bytes inside a 64-key atom
-          const uint64_t da = umma_desc_k(sp + (k >> 2) * kAtomBytes + (k & 3) * 32);
+          const uint64_t da = umma_desc_k(sP + (k >> 2) * kAtomBytes + (k & 3) * 32);
           // B = V (MN-major over dims): 16 keys = two 8-row groups = 2048 bytes
           const uint64_t db = umma_desc_mn(sv + k * 2048, kAtomBytes, 1024);
-          tc_mma(tO, da, db, idesc_o, k != 0 ? 1u : 0u);
+          tc_mma(tO + (g & 1) * HD, da, db, idesc_o, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar(9));         // O tile ready, P buffer free
-        tc_commit(bar(3 + st));    // K/V stage free
+        tc_commit(bar(OF));          // O tile ready, P buffer free
+        tc_commit(bar(KE + st));     // K/V stage free
+        if (ahead == 0 && issue_s(true) != 1) { ok = false; break; }
       }
     }
   } else {
@@ -203,13 +270,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int slab = warp & 3;                        // TMEM lanes [32 slab, 32 slab + 32)
     const int part = (warp - 2) >> 2;                 // which 32 key columns / quarter of the dims
     const int row = slab * 32 + lane;                 // query row inside the tile = TMEM lane
-    const int qpos = a.q_pos0 + m0 + row;             // absolute position for the causal rule
     const uint32_t lane_addr = (uint32_t)(slab * 32) << 16;
     constexpr int OD = HD / NP;                       // output dims owned by this thread (32 / 16)
-    float o_acc[OD];
-#pragma unroll
-    for (int d = 0; d < OD; ++d) o_acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
     bool ok = true;
     auto ex2 = [](float x) -> float {
       float y;
@@ -218,9 +280,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     };
     // Exchange one float per tile between the NP threads of a row: value slots are
     // double-buffered by sequence parity, a per-thread 16-bit sequence number publishes them,
-    // and the reader's wait is bounded like every other wait in this kernel.
+    // and the reader's wait is bounded like every other wait in this kernel.  The sequence
+    // runs on across items (equality tests only, so wrapping at 65536 is harmless).
     volatile float* xval = xch;                                                   // [2][NP][128]
     volatile unsigned short* xseq = reinterpret_cast<volatile unsigned short*>(xch + 256 * NP);
+    int xs = 0;
     auto publish = [&](int seq, float mine) {
       xval[((seq & 1) * NP + part) * 128 + row] = mine;
       __threadfence_block();
@@ -232,7 +296,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int o = 1; o < NP; ++o) {
         const int p2 = (part + o) & (NP - 1);
         int spins = 0;
-        // a partner is never more than one tile ahead, so these two values are the only ones
+        // a partner is never more than one exchange ahead, so these two values are the only ones
         while (xseq[p2 * 128 + row] != (unsigned short)seq &&
                xseq[p2 * 128 + row] != (unsigned short)(seq + 1)) {
           if ((++spins & 255) == 0) {
@@ -248,97 +312,117 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       return true;
     };
 
-    auto fold_o = [&](int j, float corr) -> bool {
-      // o_acc = o_acc * corr + O_j  (O_j was produced with the row maximum after tile j)
-      if (!mbar_wait(bar(9), j & 1, abort_flag)) return false;
-      tc_fence_after();
+    int g = 0;                                        // key tiles consumed so far, all items
+    for (int r = 0; r < n_rounds && ok; ++r) {
+      FaItem it;
+      if (!fa_item(a, r, it)) continue;
+      const int ntiles = it.ntiles, m0 = it.m0;
+      const int qpos = a.q_pos0 + m0 + row;           // absolute position for the causal rule
+      float o_acc[OD];
 #pragma unroll
-      for (int c = 0; c < OD / 16; ++c) {   // 16 columns at a time keeps the register count low
-        uint32_t r[16];
-        tc_ld16(tO + part * OD + c * 16 + lane_addr, r);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = fmaf(o_acc[c * 16 + i], corr, __uint_as_float(r[i]));
-      }
-      return true;
-    };
+      for (int d = 0; d < OD; ++d) o_acc[d] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
 
-    for (int j = 0; j < ntiles && ok; ++j) {
-      const int st = j & 1;
-      if (!mbar_wait(bar(5 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      const int key0 = j * FA_BN + part * 32;          // first key of this thread's columns
-      uint32_t r[32];
-      tc_ld32(tS + st * FA_BN + part * 32 + lane_addr, r);
-      tc_wait_ld();
-      float sv[32];
+      auto fold_o = [&](int gg, float corr) {
+        // o_acc = o_acc * corr + O_j  (O_j was produced with the row maximum after tile j).
+        // The caller has already waited for that tile's O barrier phase; waiting a second time
+        // could meet the barrier two phases further on, where the same parity reads "not yet".
 #pragma unroll
-      for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
-      // only the last tile(s) need masking: end of the keys, or the causal diagonal
-      const bool need_mask = (j * FA_BN + FA_BN > a.kv_len) ||
-                             (a.causal && j * FA_BN + FA_BN - 1 > a.q_pos0 + m0);
-      if (need_mask) {
-        int valid = a.kv_len - key0;
-        if (a.causal) valid = min(valid, qpos - key0 + 1);
+        for (int c = 0; c < OD / 16; ++c) {   // 16 columns at a time keeps the register count low
+          uint32_t rr[16];
+          tc_ld16(tO + (gg & 1) * HD + part * OD + c * 16 + lane_addr, rr);
+          tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[i] = (i < valid) ? sv[i] : -INFINITY;
+          for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = fmaf(o_acc[c * 16 + i], corr, __uint_as_float(rr[i]));
+        }
+      };
+
+      for (int j = 0; j < ntiles && ok; ++j, ++g) {
+        const int sb = g & 1;
+        if (!mbar_wait(bar(SF + sb), (g >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const int key0 = j * FA_BN + part * 32;          // first key of this thread's columns
+        uint32_t rr[32];
+        tc_ld32(tS + sb * FA_BN + part * 32 + lane_addr, rr);
+        tc_wait_ld();
+        float sv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(rr[i]);
+        // only the last tile(s) need masking: end of the keys, or the causal diagonal
+        const bool need_mask = (j * FA_BN + FA_BN > a.kv_len) ||
+                               (a.causal && j * FA_BN + FA_BN - 1 > a.q_pos0 + m0);
+        if (need_mask) {
+          int valid = a.kv_len - key0;
+          if (a.causal) valid = min(valid, qpos - key0 + 1);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[i] = (i < valid) ? sv[i] : -INFINITY;
+        }
+        float mt = sv[0];
+#pragma unroll
+        for (int i = 1; i < 32; ++i) mt = fmaxf(mt, sv[i]);
+        publish(++xs, mt);
+        float mo[NP - 1];
+        if (!collect(xs, mo)) { ok = false; break; }
+#pragma unroll
+        for (int o = 0; o < NP - 1; ++o) mt = fmaxf(mt, mo[o]);
+        const float m_new = fmaxf(m_run, mt * a.scale_log2);
+        const float mu = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = ex2(m_run - mu);
+        // p = exp2(s * scale - m), row sum, P tile (bf16, 128-byte swizzle, K-major): this
+        // thread's 32 keys are four 16-byte chunks of atom part / 2
+        float ps = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { sv[i] = ex2(fmaf(sv[i], a.scale_log2, -mu)); ps += sv[i]; }
+        // The P buffer is free once the tensor core has finished O_{j-1}; that MMA was issued a
+        // whole tile of exponentials ago, so this wait does not normally spin.  (At j = 0 the
+        // previous item's last fold already proved it.)
+        if (j > 0) {
+          if (!mbar_wait(bar(OF), (g - 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+        }
+        unsigned char* prow = gP + (part >> 1) * kAtomBytes + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16(sv[q4 * 8 + 0], sv[q4 * 8 + 1]); w.y = pack_bf16(sv[q4 * 8 + 2], sv[q4 * 8 + 3]);
+          w.z = pack_bf16(sv[q4 * 8 + 4], sv[q4 * 8 + 5]); w.w = pack_bf16(sv[q4 * 8 + 6], sv[q4 * 8 + 7]);
+          const int chunk = (part & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+        }
+        // make the P tile visible to the tensor core (async proxy) and hand it over
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(PF));            // one arrival per warp
+        // fold the previous tile's output while the tensor core works on this one (the two O
+        // accumulators alternate, so O_j may be written while O_{j-1} is read)
+        if (j > 0) fold_o(g - 1, corr_prev);
+        l_run = l_run * corr + ps;
+        m_run = m_new;
+        corr_prev = corr;
       }
-      float mt = sv[0];
+      if (ok) ok = mbar_wait(bar(OF), (g - 1) & 1, abort_flag);
+      if (ok) { tc_fence_after(); fold_o(g - 1, corr_prev); }
+      // the row sum is split between the NP threads of the row
+      if (ok) {
+        publish(++xs, l_run);
+        float lo[NP - 1];
+        ok = collect(xs, lo);
 #pragma unroll
-      for (int i = 1; i < 32; ++i) mt = fmaxf(mt, sv[i]);
-      publish(j + 1, mt);
-      // while the partners catch up: fold the previous tile's output (this also proves that
-      // the tensor core is done reading the P buffer)
-      if (j > 0) { if (!fold_o(j - 1, corr_prev)) { ok = false; break; } }
-      float mo[NP - 1];
-      if (!collect(j + 1, mo)) { ok = false; break; }
-#pragma unroll
-      for (int o = 0; o < NP - 1; ++o) mt = fmaxf(mt, mo[o]);
-      const float m_new = fmaxf(m_run, mt * a.scale_log2);
-      const float mu = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = ex2(m_run - mu);
-      // p = exp2(s * scale - m), row sum, P tile (bf16, 128-byte swizzle, K-major): this
-      // thread's 32 keys are four 16-byte chunks of atom part / 2
-      float ps = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) { sv[i] = ex2(fmaf(sv[i], a.scale_log2, -mu)); ps += sv[i]; }
-      unsigned char* prow = gP + (part >> 1) * kAtomBytes + row * 128;
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        uint4 w;
-        w.x = pack_bf16(sv[q4 * 8 + 0], sv[q4 * 8 + 1]); w.y = pack_bf16(sv[q4 * 8 + 2], sv[q4 * 8 + 3]);
-        w.z = pack_bf16(sv[q4 * 8 + 4], sv[q4 * 8 + 5]); w.w = pack_bf16(sv[q4 * 8 + 6], sv[q4 * 8 + 7]);
-        const int chunk = (part & 1) * 4 + q4;
-        *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+        for (int o = 0; o < NP - 1; ++o) l_run += lo[o];
       }
-      l_run = l_run * corr + ps;
-      m_run = m_new;
-      corr_prev = corr;
-      // make the P tile visible to the tensor core (async proxy) and hand it over
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      tc_fence_before();
-      mbar_arrive(bar(7));
-    }
-    if (ok && ntiles > 0) ok = fold_o(ntiles - 1, corr_prev);
-    // the row sum is split between the NP threads of the row
-    if (ok) {
-      publish(ntiles + 1, l_run);
-      float lo[NP - 1];
-      ok = collect(ntiles + 1, lo);
+      if (ok && m0 + row < a.S) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint16_t* dst = a.o + (long)it.b * a.o_bs + (long)(m0 + row) * a.o_rs + (long)it.head * a.o_hs + part * OD;
 #pragma unroll
-      for (int o = 0; o < NP - 1; ++o) l_run += lo[o];
-    }
-    if (ok && m0 + row < a.S) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint16_t* dst = a.o + (long)b * a.o_bs + (long)(m0 + row) * a.o_rs + (long)head * a.o_hs + part * OD;
-#pragma unroll
-      for (int d = 0; d < OD; d += 8) {
-        uint4 w;
-        w.x = pack_bf16(o_acc[d] * inv, o_acc[d + 1] * inv);
-        w.y = pack_bf16(o_acc[d + 2] * inv, o_acc[d + 3] * inv);
-        w.z = pack_bf16(o_acc[d + 4] * inv, o_acc[d + 5] * inv);
-        w.w = pack_bf16(o_acc[d + 6] * inv, o_acc[d + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + d) = w;
+        for (int d = 0; d < OD; d += 8) {
+          uint4 w;
+          w.x = pack_bf16(o_acc[d] * inv, o_acc[d + 1] * inv);
+          w.y = pack_bf16(o_acc[d + 2] * inv, o_acc[d + 3] * inv);
+          w.z = pack_bf16(o_acc[d + 4] * inv, o_acc[d + 5] * inv);
+          w.w = pack_bf16(o_acc[d + 6] * inv, o_acc[d + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + d) = w;
+        }
       }
     }
   }
@@ -370,8 +454,9 @@ static bool split_strides(int64_t bs, int64_t rs, int64_t hs, int* batch_rows, i
 template <int HD>
 static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                      const FaArgs& a, dim3 grid, cudaStream_t st, bool pdl) {
-  // tiles (Q, 2 x K, 2 x V, P) + 11 barriers + TMEM slot / flags + exchange values and sequence numbers
-  constexpr size_t smem = (size_t)(HD / 64) * kAtomBytes * 5 + 2 * kAtomBytes + 88 + 16 +
+  // tiles (Q buffers, K | V ring, P: 192 KiB at either head dim) + 16 barriers + TMEM slot /
+  // flags + exchange values and sequence numbers
+  constexpr size_t smem = (size_t)12 * kAtomBytes + 128 + 16 +
                           (size_t)2 * kFaParts * 128 * 4 + (size_t)kFaParts * 128 * 2;
   static bool attr_set[kMaxDevices] = {false};
   if (opt_in_smem(flash_prefill_tc_kernel<HD>, (int)smem, attr_set) != cudaSuccess) return B200_ERR_LAUNCH;
@@ -393,7 +478,7 @@ extern "C" int b200_flash_prefill_tc(void* out, const void* q, const void* k, co
                                      int causal, float scale, int* status, int flags,
                                      b200_stream_t stream) {
   if (!out || !q || !k || !v) return B200_ERR_ARG;
-  if (batch <= 0 || S <= 0 || kv_len <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 ||
+  if (batch <= 0 || S <= 0 || kv_len <= 0 || q_pos0 < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 ||
       (hd != 64 && hd != 128) || batch > 65535 || n_q > 65535)
     return B200_ERR_SHAPE;
   const int64_t strides[12] = {q_bs, q_rs, q_hs, k_bs, k_rs, k_hs, v_bs, v_rs, v_hs, o_bs, o_rs, o_hs};
@@ -423,7 +508,12 @@ extern "C" int b200_flash_prefill_tc(void* out, const void* q, const void* k, co
   if ((rc = make_map(&mq, q, q_rows, q_cols, (uint64_t)q_rs, 128, 64)) != B200_OK) return rc;
   if ((rc = make_map(&mk, k, k_rows, k_cols, (uint64_t)k_rs, 128, 64)) != B200_OK) return rc;
   if ((rc = make_map(&mv, v, v_rows, v_cols, (uint64_t)v_rs, 128, 64)) != B200_OK) return rc;
-  dim3 grid((S + FA_BM - 1) / FA_BM, n_q, batch);
+  a.n_mt = (S + FA_BM - 1) / FA_BM;
+  a.n_bh = n_q * batch;
+  const int64_t n_items = (int64_t)a.n_mt * a.n_bh;
+  if (n_items > INT_MAX) return B200_ERR_SHAPE;
+  a.n_items = (int)n_items;
+  dim3 grid((unsigned)std::min<int64_t>(n_items, kNumSMs));
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   return hd == 128 ? fa_launch<128>(mq, mk, mv, a, grid, (cudaStream_t)stream, pdl)
                    : fa_launch<64>(mq, mk, mv, a, grid, (cudaStream_t)stream, pdl);

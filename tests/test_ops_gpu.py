@@ -421,3 +421,26 @@ def test_flash_prefill(dev, S, n_q, n_kv, hd, causal):
     ops.check_status(dev)
     # P and the output are rounded to bf16
     assert rel_err(out[0], ref) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,n_q,n_kv,hd,causal", [(12, 512, 16, 16, 64, False), (5, 700, 8, 2, 128, True),
+                                                     (3, 130, 6, 6, 64, False)])
+def test_flash_prefill_batched_many_rounds(dev, B, S, n_q, n_kv, hd, causal):
+    """More work items than SMs: every CTA walks several (batch, head, query tile) items back
+    to back, with the Q / K / V rings and the S accumulators carried across item boundaries."""
+    from hoid_optimized_models_b200 import ops
+    g = torch.Generator().manual_seed(B * S)
+    q = bf(torch.randn(B, S, n_q, hd, generator=g))
+    kc = bf(torch.randn(B, n_kv, S + 3, hd, generator=g))
+    vc = bf(torch.randn(B, n_kv, S + 3, hd, generator=g))
+    G = n_q // n_kv
+    kk = kc[:, :, :S].float().repeat_interleave(G, 1)
+    vv = vc[:, :, :S].float().repeat_interleave(G, 1)
+    sc = torch.einsum("bshd,bhkd->bhsk", q.float(), kk) * hd ** -0.5
+    if causal:
+        sc = sc.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+    ref = torch.einsum("bhsk,bhkd->bshd", torch.softmax(sc, -1), vv)
+    out = torch.full((B, S, n_q, hd), float("nan"), dtype=torch.bfloat16, device=dev)
+    ops.flash_prefill(out, q.to(dev), kc.to(dev), vc.to(dev), S, causal, hd ** -0.5)
+    ops.check_status(dev)
+    assert rel_err(out, ref) < 2e-2
