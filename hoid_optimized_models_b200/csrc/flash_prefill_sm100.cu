@@ -1,28 +1,27 @@
 // Prefill / encoder flash attention on the sm_100a tensor cores (tcgen05 + TMEM + TMA).
 //
-// Persistent: one CTA per SM walks a list of work items (128 query rows of one head each) and,
-// inside an item, the keys in tiles of 128.  The three roles run decoupled through mbarrier
-// rings that are never drained between items, so the next item's Q / K / V loads and its first
-// S = Q K^T are in flight while the softmax warps finish the current one:
-//   warp 0     TMA producer: Q per item (two buffers at head dim 64), K and V tiles into a ring
-//              of 4 (head dim 64) or 2 (head dim 128) stages
-//   warp 1     MMA issuer (one lane): S_j = Q K_j^T (M128 N128, K = head dim) into one of two
-//              S accumulators in tensor memory, and O_j = P_j V_j (V consumed in its natural
-//              [key][dim] layout as an MN-major operand) into the O-tile accumulator
-//   warps 2-17 softmax: four threads per query row (= TMEM lane), each owning 32 key columns
-//              and a quarter of the output dims.  A thread pulls its 32 scores with one
-//              tcgen05.ld, the row maximum is exchanged between the four through shared memory,
-//              P_j = exp2(...) is written as bf16 into the 128-byte-swizzled shared tile the
-//              second MMA reads, and only then O_{j-1} is folded from tensor memory into fp32
-//              registers with the online-softmax correction.  S and O are double-buffered in
-//              tensor memory, so the tensor core works on S_{j+1} and O_j while the softmax
-//              warps are busy, and the softmax warps never wait for an MMA they just asked for.
-// Work order: causal items heaviest query tile first, dealt to the CTAs in alternating direction
-// (round r forwards, round r + 1 backwards) so every CTA gets the same number of key tiles to
-// within one round; bidirectional items with the query tiles of one head adjacent, so a head's
-// K / V are read from DRAM once and from L2 afterwards.
-// The score matrix never leaves the SM.  Causal tiles above the diagonal are never visited.
-// Every mbarrier wait is bounded (status word + clean TMEM release on expiry).
+// Persistent: one CTA per SM walks a list of work items.  An item is 256 query rows of one head,
+// handled as two independent streams A and B of 128 rows that share the K / V tiles, so the
+// latencies of one stream (score load, barrier hand-overs, MMA completion) are covered by the
+// exponentials of the other.  Ten warps:
+//   warps 0-3  softmax of stream A, warps 4-7 of stream B: ONE thread per query row (= TMEM
+//              lane; warp w may only touch lanes 32 (w % 4) ..).  A thread pulls its whole row
+//              of 128 scores with tcgen05.ld, takes the row maximum and sum in registers (no
+//              exchange between threads), and writes P = exp2(...) as packed bf16 back into
+//              tensor memory over the first 64 columns of the scores it has just consumed.
+//   warp 8     TMA producer: Q tiles per item and stream, K and V tiles into one ring
+//   warp 9     MMA issuer (one lane): S_X = Q_X K^T (M128 N128, K = head dim) into the stream's
+//              score accumulator, and O_X += P_X V with P read straight from tensor memory and V
+//              consumed in its natural [key][dim] layout as an MN-major operand.
+// The output accumulates in tensor memory across key tiles.  The running maximum is raised only
+// when a row's tile maximum exceeds it by more than 2^8 (exact after the final division by the
+// row sum; P stays within bf16 range), and only then is the row of O rescaled in place, so most
+// tiles never touch O.  Scores and probabilities never leave the SM.
+// Work order: causal items heaviest first, dealt to the CTAs in alternating direction so every
+// CTA gets the same number of key tiles to within one round; bidirectional items with the query
+// blocks of one head adjacent, so a head's K / V come from DRAM once and from L2 afterwards.
+// Causal tiles above the diagonal are never visited.  Every mbarrier wait is bounded (status
+// word + clean TMEM release on expiry).
 #include <algorithm>
 #include <climits>
 
@@ -31,15 +30,15 @@
 namespace b200 {
 
 constexpr int FA_BM = 128, FA_BN = 128;
-constexpr int kFaParts = 4;        // softmax threads per query row
-constexpr int kFaThreads = 64 + 128 * kFaParts;   // TMA warp, MMA warp, 16 softmax warps
+constexpr int kFaThreads = 320;              // 8 softmax warps, TMA warp, MMA warp
 constexpr uint32_t kAtomBytes = 128 * 128;   // a 128-row x 64-column bf16 box: 16 KiB
+constexpr float kFaLazy = 8.f;               // log2 of the growth of a row maximum that is tolerated
 
 struct FaArgs {
   uint16_t* o; long o_bs, o_rs, o_hs;
   int* status;
   int S, kv_len, q_pos0, group, causal, n_q;
-  int n_mt, n_bh, n_items;          // query tiles per head, batch x heads, work items
+  int n_mp, n_bh, n_items;          // 256-row query blocks per head, batch x heads, work items
   // row / column bookkeeping of the 2D views the tensor maps cover
   int q_batch_rows, q_head_rows, q_head_cols;
   int k_batch_rows, k_head_rows, k_head_cols;
@@ -47,24 +46,51 @@ struct FaArgs {
   float scale_log2;
 };
 
-struct FaItem { int b, head, m0, ntiles; };
+// One work item: key-tile counts of the two streams (n[1] == 0: the item has no rows for B).
+struct FaItem { int b, head, m0, n[2], nt; };
 
-// The work item of this CTA in round r (false: the round has none for it).  All three roles
-// call this with the same arguments and therefore walk identical lists.
+// The work item of this CTA in round r (false: the round has none for it).  All roles call
+// this with the same arguments and therefore walk identical lists.
 __device__ __forceinline__ bool fa_item(const FaArgs& a, int r, FaItem& it) {
   const int G = (int)gridDim.x, c = (int)blockIdx.x;
   const int w = r * G + ((a.causal && (r & 1)) ? G - 1 - c : c);
   if (w >= a.n_items) return false;
-  int mt, bh;
-  if (a.causal) { mt = a.n_mt - 1 - w / a.n_bh; bh = w % a.n_bh; }
-  else { mt = w % a.n_mt; bh = w / a.n_mt; }
+  int mp, bh;
+  if (a.causal) { mp = a.n_mp - 1 - w / a.n_bh; bh = w % a.n_bh; }
+  else { mp = w % a.n_mp; bh = w / a.n_mp; }
   it.head = bh % a.n_q;
   it.b = bh / a.n_q;
-  it.m0 = mt * FA_BM;
-  int kv_end = a.kv_len;
-  if (a.causal) kv_end = min(kv_end, a.q_pos0 + it.m0 + FA_BM);
-  it.ntiles = (kv_end + FA_BN - 1) / FA_BN;      // >= 1: kv_len >= 1 and q_pos0 >= 0
+  it.m0 = mp * 2 * FA_BM;
+  int kv0 = a.kv_len, kv1 = a.kv_len;
+  if (a.causal) {
+    kv0 = min(kv0, a.q_pos0 + it.m0 + FA_BM);
+    kv1 = min(kv1, a.q_pos0 + it.m0 + 2 * FA_BM);
+  }
+  it.n[0] = (kv0 + FA_BN - 1) / FA_BN;             // >= 1: kv_len >= 1 and q_pos0 >= 0
+  it.n[1] = it.m0 + FA_BM < a.S ? (kv1 + FA_BN - 1) / FA_BN : 0;
+  it.nt = max(it.n[0], it.n[1]);
   return true;
+}
+
+// Position in the flat sequence of key tiles of all my items.
+struct FaCursor {
+  int r, j;          // round of the item, key tile inside it
+  int e;             // ring entry of the tile's K (its V is e + 1)
+  bool valid;
+  FaItem it;
+};
+__device__ __forceinline__ void fa_cursor_next_item(const FaArgs& a, int n_rounds, FaCursor& c) {
+  c.j = 0;
+  do { ++c.r; } while (c.r < n_rounds && !fa_item(a, c.r, c.it));
+  c.valid = c.r < n_rounds;
+}
+__device__ __forceinline__ void fa_cursor_init(const FaArgs& a, int n_rounds, FaCursor& c) {
+  c.r = -1; c.e = 0;
+  fa_cursor_next_item(a, n_rounds, c);
+}
+__device__ __forceinline__ void fa_cursor_advance(const FaArgs& a, int n_rounds, FaCursor& c) {
+  c.e += 2;
+  if (++c.j == c.it.nt) fa_cursor_next_item(a, n_rounds, c);
 }
 
 // Bounded wait without an abort flag, for the teardown of a role that already gave up.
@@ -105,16 +131,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                         const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, FaArgs a) {
   constexpr int ATOMS = HD / 64;                        // 64-column boxes per operand tile
-  constexpr int NQ = HD == 64 ? 2 : 1;                  // Q buffers
-  constexpr int NST = HD == 64 ? 4 : 2;                 // K | V stages
-  constexpr uint32_t kQBytes = ATOMS * kAtomBytes;      // Q / K / V tile bytes
-  constexpr uint32_t kPBytes = 2 * kAtomBytes;          // P tile: 128 rows x 128 keys
-  constexpr uint32_t kStage = 2 * kQBytes;              // K + V
-  constexpr uint32_t kTiles = NQ * kQBytes + NST * kStage + kPBytes;   // 192 KiB either way
-  // barrier indices
-  constexpr int QF = 0, QE = NQ, KF = 2 * NQ, KE = 2 * NQ + NST, SF = 2 * NQ + 2 * NST,
-                PF = SF + 2, OF = SF + 3, NBAR = SF + 4;
-  static_assert(NBAR <= 16, "barrier block is 16 entries");
+  constexpr int NQ = HD == 64 ? 2 : 1;                  // Q buffers per stream
+  constexpr int NR = HD == 64 ? 8 : 5;                  // ring entries (a K tile or a V tile each)
+  constexpr uint32_t kTile = ATOMS * kAtomBytes;        // Q / K / V tile bytes
+  constexpr uint32_t kTiles = (2 * NQ + NR) * kTile;    // 192 KiB at head dim 64, 224 KiB at 128
+  // barrier indices: Q full / empty per (buffer, stream), ring full / empty, and per stream
+  // S ready, P ready, O ready
+  constexpr int QF = 0, QE = 2 * NQ, RF = 4 * NQ, RE = 4 * NQ + NR, SF = 4 * NQ + 2 * NR,
+                PF = SF + 2, OF = SF + 4, NBAR = SF + 6;
+  static_assert(NBAR <= 32, "barrier block is 32 entries");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // Operand tiles need 1024-byte alignment.  The dynamic window starts 1 KB into the CTA's
   // shared memory (after the system-reserved kilobyte) and is therefore aligned; if a future
@@ -124,15 +149,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     if (threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, B200_ERR_ALIGN);
     return;
   }
-  unsigned char* gen = smem_raw;
-  const uint32_t sQ = base;                             // NQ buffers
-  const uint32_t sKV = sQ + NQ * kQBytes;               // NST stages x (K | V)
-  unsigned char* gP = gen + NQ * kQBytes + NST * kStage;   // one buffer (freed by the O_j commit)
-  const uint32_t sP = smem_u32(gP);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kTiles);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  const uint32_t sQ = base;                             // [NQ][2 streams]
+  const uint32_t sR = sQ + 2 * NQ * kTile;              // NR ring entries
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kTiles);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xch = reinterpret_cast<float*>(tmem_slot + 4);   // [2 parities][4 parts][128 rows] + seq
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -140,289 +161,281 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
   pdl_launch_dependents();
   if (tid == 0) {
-    for (int i = 0; i < NBAR; ++i) mbar_init(bar(i), i == PF ? 4 * kFaParts : 1);
+    for (int i = 0; i < NBAR; ++i) mbar_init(bar(i), (i == PF || i == PF + 1) ? 4 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
   }
-  if (warp == 1) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  for (int i = tid; i < 64 * kFaParts; i += kFaThreads)
-    reinterpret_cast<int*>(xch + 256 * kFaParts)[i] = 0;   // 16-bit exchange sequence numbers
   pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base;            // S buffers at columns 0 and 128
-  const uint32_t tO = tmem_base + 256;      // two O-tile accumulators, HD columns each
+  // columns: S_A 0..127, S_B 128..255 (P_X overlays the first 64 columns of S_X), O_A, O_B
+  auto tS = [&](int x) { return tmem_base + (uint32_t)x * FA_BN; };
+  auto tO = [&](int x) { return tmem_base + 256u + (uint32_t)x * HD; };
 
-  if (warp == 0) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int qi = 0, g = 0;           // items and key tiles issued so far
+      int qn[2] = {0, 0};          // Q tiles loaded so far, per stream
+      int e = 0;                   // ring entries issued so far
       bool ok = true;
       for (int r = 0; r < n_rounds && ok; ++r) {
         FaItem it;
         if (!fa_item(a, r, it)) continue;
         const int kvh = it.head / a.group;
-        const int qb = qi % NQ;
-        if (!mbar_wait(bar(QE + qb), ((qi / NQ) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        const int q_row = it.b * a.q_batch_rows + it.head * a.q_head_rows + it.m0;
         const int q_col = it.head * a.q_head_cols;
-        mbar_expect_tx(bar(QF + qb), kQBytes);
 #pragma unroll
-        for (int t = 0; t < ATOMS; ++t)
-          tma_load_2d(sQ + qb * kQBytes + t * kAtomBytes, &map_q, bar(QF + qb), q_col + 64 * t, q_row);
-        ++qi;
+        for (int x = 0; x < 2; ++x) {
+          if (it.n[x] == 0 || !ok) continue;
+          const int qb = qn[x] % NQ, bi = qb * 2 + x;
+          if (!mbar_wait(bar(QE + bi), ((qn[x] / NQ) & 1) ^ 1, abort_flag)) { ok = false; continue; }
+          const int q_row = it.b * a.q_batch_rows + it.head * a.q_head_rows + it.m0 + x * FA_BM;
+          mbar_expect_tx(bar(QF + bi), kTile);
+#pragma unroll
+          for (int t = 0; t < ATOMS; ++t)
+            tma_load_2d(sQ + bi * kTile + t * kAtomBytes, &map_q, bar(QF + bi), q_col + 64 * t, q_row);
+          ++qn[x];
+        }
         const int k_row0 = it.b * a.k_batch_rows + kvh * a.k_head_rows, k_col = kvh * a.k_head_cols;
         const int v_row0 = it.b * a.v_batch_rows + kvh * a.v_head_rows, v_col = kvh * a.v_head_cols;
-        for (int j = 0; j < it.ntiles; ++j, ++g) {
-          const int st = g % NST;
-          if (!mbar_wait(bar(KE + st), ((g / NST) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          const uint32_t sk = sKV + st * kStage, sv = sk + kQBytes;
-          mbar_expect_tx(bar(KF + st), kStage);
+        for (int j = 0; j < it.nt && ok; ++j) {
 #pragma unroll
-          for (int t = 0; t < ATOMS; ++t) {
-            tma_load_2d(sk + t * kAtomBytes, &map_k, bar(KF + st), k_col + 64 * t, k_row0 + j * FA_BN);
-            tma_load_2d(sv + t * kAtomBytes, &map_v, bar(KF + st), v_col + 64 * t, v_row0 + j * FA_BN);
+          for (int kv = 0; kv < 2; ++kv, ++e) {
+            if (!ok) continue;
+            const int slot = e % NR;
+            if (!mbar_wait(bar(RE + slot), ((e / NR) & 1) ^ 1, abort_flag)) { ok = false; continue; }
+            mbar_expect_tx(bar(RF + slot), kTile);
+#pragma unroll
+            for (int t = 0; t < ATOMS; ++t) {
+              if (kv == 0)
+                tma_load_2d(sR + slot * kTile + t * kAtomBytes, &map_k, bar(RF + slot), k_col + 64 * t, k_row0 + j * FA_BN);
+              else
+                tma_load_2d(sR + slot * kTile + t * kAtomBytes, &map_v, bar(RF + slot), v_col + 64 * t, v_row0 + j * FA_BN);
+            }
           }
         }
       }
       if (!ok) {
         // give the copies still in flight a bounded time to land before the CTA retires
-        for (int i = 1; i <= min(g, NST); ++i)
-          mbar_wait_quiet(bar(KF + (g - i) % NST), ((g - i) / NST) & 1, 2000000);
-        for (int i = 1; i <= min(qi, NQ); ++i)
-          mbar_wait_quiet(bar(QF + (qi - i) % NQ), ((qi - i) / NQ) & 1, 2000000);
+        for (int i = 1; i <= min(e, NR); ++i)
+          mbar_wait_quiet(bar(RF + (e - i) % NR), ((e - i) / NR) & 1, 2000000);
+        for (int x = 0; x < 2; ++x)
+          for (int i = 1; i <= min(qn[x], NQ); ++i)
+            mbar_wait_quiet(bar(QF + ((qn[x] - i) % NQ) * 2 + x), ((qn[x] - i) / NQ) & 1, 2000000);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = fa_idesc(FA_BN, 0);
       constexpr uint32_t idesc_o = fa_idesc(HD, 1);
-      // key tiles of all my items
-      int total = 0;
-      for (int r = 0; r < n_rounds; ++r) { FaItem it; if (fa_item(a, r, it)) total += it.ntiles; }
-      // Cursor of the S = Q K^T issue.  It runs one tile ahead of the O = P V issue and crosses
-      // item boundaries; when its operands have not landed yet the O MMAs go first.
-      int s_r = -1, s_j = 0, s_n = 0, s_qi = -1, s_g = 0;
-      bool s_new_q = false;
+      // Two positions in the flat tile sequence: `pv` is the tile whose O += P V is issued,
+      // `ps` the tile whose S = Q K^T is issued, one tile further on (across item boundaries),
+      // so a stream's next scores are being computed while its softmax warps work.
+      FaCursor pv, ps;
+      fa_cursor_init(a, n_rounds, pv);
+      ps = pv;
+      int sq[2] = {0, 0};         // Q tiles consumed, per stream
+      int sg[2] = {0, 0};         // S tiles issued, per stream
+      int pg[2] = {0, 0};         // O tiles issued, per stream
+      int k_seen = -1;            // ring entry of the last K tile whose arrival was awaited
+      bool ok = pv.valid;
       // 1 issued, 0 operands not there yet (only when !blocking), -1 gave up
-      auto issue_s = [&](bool blocking) -> int {
-        if (s_j == s_n) {                     // first tile of the next item
-          FaItem it;
-          do { ++s_r; } while (s_r < n_rounds && !fa_item(a, s_r, it));
-          if (s_r >= n_rounds) return -1;
-          s_n = it.ntiles; s_j = 0; ++s_qi; s_new_q = true;
-        }
-        const int st = s_g % NST, qb = s_qi % NQ;
+      auto issue_s = [&](int x, bool blocking) -> int {
+        const int qb = sq[x] % NQ, bi = qb * 2 + x, slot = ps.e % NR;
+        const bool new_q = ps.j == 0;
         if (!blocking) {
-          if (s_new_q && !mbar_try(bar(QF + qb), (s_qi / NQ) & 1)) return 0;
-          if (!mbar_try(bar(KF + st), (s_g / NST) & 1)) return 0;
+          if (new_q && !mbar_try(bar(QF + bi), (sq[x] / NQ) & 1)) return 0;
+          if (k_seen != ps.e && !mbar_try(bar(RF + slot), (ps.e / NR) & 1)) return 0;
         } else {
-          if (s_new_q && !mbar_wait(bar(QF + qb), (s_qi / NQ) & 1, abort_flag)) return -1;
-          if (!mbar_wait(bar(KF + st), (s_g / NST) & 1, abort_flag)) return -1;
+          if (new_q && !mbar_wait(bar(QF + bi), (sq[x] / NQ) & 1, abort_flag)) return -1;
+          if (k_seen != ps.e && !mbar_wait(bar(RF + slot), (ps.e / NR) & 1, abort_flag)) return -1;
         }
-        s_new_q = false;
+        k_seen = ps.e;
         tc_fence_after();
-        const uint32_t sk = sKV + st * kStage, sq = sQ + qb * kQBytes;
+        const uint32_t sk = sR + slot * kTile, sq_ = sQ + bi * kTile;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          tc_mma(tS + (s_g & 1) * FA_BN, umma_desc_k(sq + off), umma_desc_k(sk + off), idesc_s, k != 0 ? 1u : 0u);
+          tc_mma(tS(x), umma_desc_k(sq_ + off), umma_desc_k(sk + off), idesc_s, k != 0 ? 1u : 0u);
         }
-        tc_commit(bar(SF + (s_g & 1)));
-        ++s_j; ++s_g;
-        if (s_j == s_n) tc_commit(bar(QE + qb));   // Q buffer free once these MMAs retire
+        tc_commit(bar(SF + x));
+        ++sg[x];
+        if (ps.j == ps.it.n[x] - 1) { tc_commit(bar(QE + bi)); ++sq[x]; }   // Q free once these retire
         return 1;
       };
-      bool ok = total > 0 && issue_s(true) == 1;
-      for (int g = 0; g < total && ok; ++g) {
-        const int st = g % NST;
-        int ahead = 1;
-        if (g + 1 < total) { ahead = issue_s(false); if (ahead < 0) { ok = false; break; } }
-        if (!mbar_wait(bar(PF), g & 1, abort_flag)) { ok = false; break; }
+      auto issue_pv = [&](int x) -> bool {
+        const int slot = (pv.e + 1) % NR;
+        if (!mbar_wait(bar(PF + x), pg[x] & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(RF + slot), ((pv.e + 1) / NR) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sv = sKV + st * kStage + kQBytes;
+        const uint32_t sv = sR + slot * kTile;
 #pragma unroll
         for (int k = 0; k < FA_BN / 16; ++k) {
-          // A = P (K-major over keys): 16 keys = 32 bytes inside a 64-key atom
-          const uint64_t da = umma_desc_k(sP + (k >> 2) * kAtomBytes + (k & 3) * 32);
+          // A = P from tensor memory: 16 keys = 8 columns of packed bf16 pairs
           // B = V (MN-major over dims): 16 keys = two 8-row groups = 2048 bytes
           const uint64_t db = umma_desc_mn(sv + k * 2048, kAtomBytes, 1024);
-          tc_mma(tO + (g & 1) * HD, da, db, idesc_o, k != 0 ? 1u : 0u);
+          tc_mma_ts(tO(x), tS(x) + k * 8, db, idesc_o, (pv.j != 0 || k != 0) ? 1u : 0u);
         }
-        tc_commit(bar(OF));          // O tile ready, P buffer free
-        tc_commit(bar(KE + st));     // K/V stage free
-        if (ahead == 0 && issue_s(true) != 1) { ok = false; break; }
+        tc_commit(bar(OF + x));
+        ++pg[x];
+        return true;
+      };
+      if (ok) {      // scores of the very first tile
+        if (issue_s(0, true) != 1) ok = false;
+        if (ok && ps.it.n[1] > 0 && issue_s(1, true) != 1) ok = false;
+        if (ok) { tc_commit(bar(RE + ps.e % NR)); fa_cursor_advance(a, n_rounds, ps); }
+      }
+      while (ok && pv.valid) {
+        const bool act_a = pv.j < pv.it.n[0], act_b = pv.j < pv.it.n[1];
+        bool todo_a = ps.valid && ps.j < ps.it.n[0], todo_b = ps.valid && ps.j < ps.it.n[1];
+        const bool any_s = todo_a || todo_b;
+        if (act_a) { if (!issue_pv(0)) { ok = false; break; } }
+        if (todo_a) {
+          // stream A's next scores; if their operands have not landed, stream B's O goes first
+          const int r = issue_s(0, !act_b);
+          if (r < 0) { ok = false; break; }
+          if (r == 1) todo_a = false;
+        }
+        if (act_b) { if (!issue_pv(1)) { ok = false; break; } }
+        tc_commit(bar(RE + (pv.e + 1) % NR));          // V tile free once both O MMAs retire
+        if (todo_a) { if (issue_s(0, true) != 1) { ok = false; break; } }
+        if (todo_b) { if (issue_s(1, true) != 1) { ok = false; break; } }
+        if (any_s) tc_commit(bar(RE + ps.e % NR));     // K tile free once both S MMAs retire
+        fa_cursor_advance(a, n_rounds, pv);
+        if (ps.valid) fa_cursor_advance(a, n_rounds, ps);
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax warps
-    constexpr int NP = kFaParts;
-    const int slab = warp & 3;                        // TMEM lanes [32 slab, 32 slab + 32)
-    const int part = (warp - 2) >> 2;                 // which 32 key columns / quarter of the dims
-    const int row = slab * 32 + lane;                 // query row inside the tile = TMEM lane
-    const uint32_t lane_addr = (uint32_t)(slab * 32) << 16;
-    constexpr int OD = HD / NP;                       // output dims owned by this thread (32 / 16)
+    const int x = warp >> 2;                          // stream
+    const int row = (warp & 3) * 32 + lane;           // query row inside the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t my_s = tS(x) + lane_addr, my_o = tO(x) + lane_addr;
     bool ok = true;
-    auto ex2 = [](float x) -> float {
+    auto ex2 = [](float v) -> float {
       float y;
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(v));
       return y;
     };
-    // Exchange one float per tile between the NP threads of a row: value slots are
-    // double-buffered by sequence parity, a per-thread 16-bit sequence number publishes them,
-    // and the reader's wait is bounded like every other wait in this kernel.  The sequence
-    // runs on across items (equality tests only, so wrapping at 65536 is harmless).
-    volatile float* xval = xch;                                                   // [2][NP][128]
-    volatile unsigned short* xseq = reinterpret_cast<volatile unsigned short*>(xch + 256 * NP);
-    int xs = 0;
-    auto publish = [&](int seq, float mine) {
-      xval[((seq & 1) * NP + part) * 128 + row] = mine;
-      __threadfence_block();
-      xseq[part * 128 + row] = (unsigned short)seq;
-    };
-    auto collect = [&](int seq, float* others) -> bool {   // others[NP - 1]
-      const long long t0 = clock64();
-#pragma unroll
-      for (int o = 1; o < NP; ++o) {
-        const int p2 = (part + o) & (NP - 1);
-        int spins = 0;
-        // a partner is never more than one exchange ahead, so these two values are the only ones
-        while (xseq[p2 * 128 + row] != (unsigned short)seq &&
-               xseq[p2 * 128 + row] != (unsigned short)(seq + 1)) {
-          if ((++spins & 255) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitBudget) { *abort_flag = 1; return false; }
-          }
-        }
-      }
-      __threadfence_block();
-#pragma unroll
-      for (int o = 1; o < NP; ++o)
-        others[o - 1] = xval[((seq & 1) * NP + ((part + o) & (NP - 1))) * 128 + row];
-      return true;
-    };
-
-    int g = 0;                                        // key tiles consumed so far, all items
+    int g = 0;                                        // key tiles of this stream consumed so far
     for (int r = 0; r < n_rounds && ok; ++r) {
       FaItem it;
       if (!fa_item(a, r, it)) continue;
-      const int ntiles = it.ntiles, m0 = it.m0;
+      const int ntiles = it.n[x];
+      if (ntiles == 0) continue;
+      const int m0 = it.m0 + x * FA_BM;
       const int qpos = a.q_pos0 + m0 + row;           // absolute position for the causal rule
-      float o_acc[OD];
-#pragma unroll
-      for (int d = 0; d < OD; ++d) o_acc[d] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
-
-      auto fold_o = [&](int gg, float corr) {
-        // o_acc = o_acc * corr + O_j  (O_j was produced with the row maximum after tile j).
-        // The caller has already waited for that tile's O barrier phase; waiting a second time
-        // could meet the barrier two phases further on, where the same parity reads "not yet".
-#pragma unroll
-        for (int c = 0; c < OD / 16; ++c) {   // 16 columns at a time keeps the register count low
-          uint32_t rr[16];
-          tc_ld16(tO + (gg & 1) * HD + part * OD + c * 16 + lane_addr, rr);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = fmaf(o_acc[c * 16 + i], corr, __uint_as_float(rr[i]));
-        }
-      };
+      float m_used = 0.f, l_run = 0.f;
 
       for (int j = 0; j < ntiles && ok; ++j, ++g) {
-        const int sb = g & 1;
-        if (!mbar_wait(bar(SF + sb), (g >> 1) & 1, abort_flag)) { ok = false; break; }
+        // (waits are voted on so that the warp-collective tensor-memory accesses stay convergent)
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(SF + x), g & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        const int key0 = j * FA_BN + part * 32;          // first key of this thread's columns
-        uint32_t rr[32];
-        tc_ld32(tS + sb * FA_BN + part * 32 + lane_addr, rr);
-        tc_wait_ld();
-        float sv[32];
+        uint32_t sr[FA_BN];                            // the row's scores (fp32 bit patterns)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(rr[i]);
+        for (int c = 0; c < FA_BN / 32; ++c) tc_ld32(my_s + c * 32, sr + c * 32);
+        tc_wait_ld();
+#define SV(i) __uint_as_float(sr[i])
         // only the last tile(s) need masking: end of the keys, or the causal diagonal
         const bool need_mask = (j * FA_BN + FA_BN > a.kv_len) ||
                                (a.causal && j * FA_BN + FA_BN - 1 > a.q_pos0 + m0);
         if (need_mask) {
-          int valid = a.kv_len - key0;
-          if (a.causal) valid = min(valid, qpos - key0 + 1);
+          int valid = a.kv_len - j * FA_BN;
+          if (a.causal) valid = min(valid, qpos - j * FA_BN + 1);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) sv[i] = (i < valid) ? sv[i] : -INFINITY;
+          for (int i = 0; i < FA_BN; ++i) sr[i] = (i < valid) ? sr[i] : 0xff800000u;   // -inf
         }
-        float mt = sv[0];
+        float mx[4] = {SV(0), SV(1), SV(2), SV(3)};
 #pragma unroll
-        for (int i = 1; i < 32; ++i) mt = fmaxf(mt, sv[i]);
-        publish(++xs, mt);
-        float mo[NP - 1];
-        if (!collect(xs, mo)) { ok = false; break; }
-#pragma unroll
-        for (int o = 0; o < NP - 1; ++o) mt = fmaxf(mt, mo[o]);
-        const float m_new = fmaxf(m_run, mt * a.scale_log2);
-        const float mu = (m_new == -INFINITY) ? 0.f : m_new;
-        const float corr = ex2(m_run - mu);
-        // p = exp2(s * scale - m), row sum, P tile (bf16, 128-byte swizzle, K-major): this
-        // thread's 32 keys are four 16-byte chunks of atom part / 2
-        float ps = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[i] = ex2(fmaf(sv[i], a.scale_log2, -mu)); ps += sv[i]; }
-        // The P buffer is free once the tensor core has finished O_{j-1}; that MMA was issued a
-        // whole tile of exponentials ago, so this wait does not normally spin.  (At j = 0 the
-        // previous item's last fold already proved it.)
-        if (j > 0) {
-          if (!mbar_wait(bar(OF), (g - 1) & 1, abort_flag)) { ok = false; break; }
+        for (int i = 4; i < FA_BN; i += 4) {
+          mx[0] = fmaxf(mx[0], SV(i)); mx[1] = fmaxf(mx[1], SV(i + 1));
+          mx[2] = fmaxf(mx[2], SV(i + 2)); mx[3] = fmaxf(mx[3], SV(i + 3));
+        }
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
+        if (j == 0) {
+          m_used = (mt == -INFINITY) ? 0.f : mt;
+        } else if (__any_sync(0xffffffffu, mt > m_used + kFaLazy)) {
+          // Some row of this warp outgrew its reference maximum: rescale the warp's rows of O
+          // (in tensor memory) once the tensor core has finished the previous tile's O.
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(OF + x), (g - 1) & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
-        }
-        unsigned char* prow = gP + (part >> 1) * kAtomBytes + row * 128;
+          const float m_new = fmaxf(m_used, mt);
+          const float f = ex2(m_used - m_new);
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16(sv[q4 * 8 + 0], sv[q4 * 8 + 1]); w.y = pack_bf16(sv[q4 * 8 + 2], sv[q4 * 8 + 3]);
-          w.z = pack_bf16(sv[q4 * 8 + 4], sv[q4 * 8 + 5]); w.w = pack_bf16(sv[q4 * 8 + 6], sv[q4 * 8 + 7]);
-          const int chunk = (part & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+          for (int c = 0; c < HD / 16; ++c) {
+            uint32_t rr[16];
+            tc_ld16(my_o + c * 16, rr);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * f);
+            tc_st16(my_o + c * 16, rr);
+          }
+          l_run *= f;
+          m_used = m_new;
         }
-        // make the P tile visible to the tensor core (async proxy) and hand it over
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // p = exp2(s * scale - m) as packed bf16 pairs, row sum in fp32; 64 keys at a time so
+        // that the first half is on its way to tensor memory while the second is computed
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 64; i += 4) {
+            const float p0 = ex2(fmaf(SV(h * 64 + i), a.scale_log2, -m_used));
+            const float p1 = ex2(fmaf(SV(h * 64 + i + 1), a.scale_log2, -m_used));
+            const float p2 = ex2(fmaf(SV(h * 64 + i + 2), a.scale_log2, -m_used));
+            const float p3 = ex2(fmaf(SV(h * 64 + i + 3), a.scale_log2, -m_used));
+            ps[0] += p0; ps[1] += p1; ps[2] += p2; ps[3] += p3;
+            pk[i / 2] = pack_bf16(p0, p1);
+            pk[i / 2 + 1] = pack_bf16(p2, p3);
+          }
+          tc_st32(my_s + h * 32, pk);
+        }
+#undef SV
+        l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        tc_wait_st();
+        // hand P (and a possibly rescaled O) to the tensor core: one arrival per warp
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(PF));            // one arrival per warp
-        // fold the previous tile's output while the tensor core works on this one (the two O
-        // accumulators alternate, so O_j may be written while O_{j-1} is read)
-        if (j > 0) fold_o(g - 1, corr_prev);
-        l_run = l_run * corr + ps;
-        m_run = m_new;
-        corr_prev = corr;
+        if (lane == 0) mbar_arrive(bar(PF + x));
       }
-      if (ok) ok = mbar_wait(bar(OF), (g - 1) & 1, abort_flag);
-      if (ok) { tc_fence_after(); fold_o(g - 1, corr_prev); }
-      // the row sum is split between the NP threads of the row
+      // item epilogue: O / row sum -> bf16 -> global
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(OF + x), (g - 1) & 1, abort_flag));
       if (ok) {
-        publish(++xs, l_run);
-        float lo[NP - 1];
-        ok = collect(xs, lo);
-#pragma unroll
-        for (int o = 0; o < NP - 1; ++o) l_run += lo[o];
-      }
-      if (ok && m0 + row < a.S) {
+        tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        uint16_t* dst = a.o + (long)it.b * a.o_bs + (long)(m0 + row) * a.o_rs + (long)it.head * a.o_hs + part * OD;
+        const bool live = m0 + row < a.S;
+        uint16_t* dst = a.o + (long)it.b * a.o_bs + (long)(m0 + row) * a.o_rs + (long)it.head * a.o_hs;
 #pragma unroll
-        for (int d = 0; d < OD; d += 8) {
-          uint4 w;
-          w.x = pack_bf16(o_acc[d] * inv, o_acc[d + 1] * inv);
-          w.y = pack_bf16(o_acc[d + 2] * inv, o_acc[d + 3] * inv);
-          w.z = pack_bf16(o_acc[d + 4] * inv, o_acc[d + 5] * inv);
-          w.w = pack_bf16(o_acc[d + 6] * inv, o_acc[d + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + d) = w;
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t rr[32];
+          tc_ld32(my_o + c * 32, rr);
+          tc_wait_ld();
+          if (live) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(rr[q4 * 8 + 0]) * inv, __uint_as_float(rr[q4 * 8 + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(rr[q4 * 8 + 2]) * inv, __uint_as_float(rr[q4 * 8 + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(rr[q4 * 8 + 4]) * inv, __uint_as_float(rr[q4 * 8 + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(rr[q4 * 8 + 6]) * inv, __uint_as_float(rr[q4 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = w;
+            }
+          }
         }
+        // the next item's first O MMA overwrites this accumulator: order the loads before the
+        // arrival that releases it
+        tc_fence_before();
       }
     }
   }
@@ -431,7 +444,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag && a.status != nullptr) atomicExch(a.status, B200_ERR_TIMEOUT);
-  if (warp == 1) {
+  if (warp == 9) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
                  : "memory");
@@ -454,10 +467,8 @@ static bool split_strides(int64_t bs, int64_t rs, int64_t hs, int* batch_rows, i
 template <int HD>
 static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                      const FaArgs& a, dim3 grid, cudaStream_t st, bool pdl) {
-  // tiles (Q buffers, K | V ring, P: 192 KiB at either head dim) + 16 barriers + TMEM slot /
-  // flags + exchange values and sequence numbers
-  constexpr size_t smem = (size_t)12 * kAtomBytes + 128 + 16 +
-                          (size_t)2 * kFaParts * 128 * 4 + (size_t)kFaParts * 128 * 2;
+  // tiles (Q buffers of both streams + the K / V ring) + 32 barriers + TMEM slot / abort flag
+  constexpr size_t smem = (size_t)(HD == 64 ? 12 : 7) * (HD / 64) * kAtomBytes + 256 + 16;
   static bool attr_set[kMaxDevices] = {false};
   if (opt_in_smem(flash_prefill_tc_kernel<HD>, (int)smem, attr_set) != cudaSuccess) return B200_ERR_LAUNCH;
   cudaError_t e = launch(flash_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, st, pdl, mq, mk, mv, a);
@@ -477,7 +488,7 @@ extern "C" int b200_flash_prefill_tc(void* out, const void* q, const void* k, co
                                      int64_t o_bs, int64_t o_rs, int64_t o_hs,
                                      int causal, float scale, int* status, int flags,
                                      b200_stream_t stream) {
-  if (!out || !q || !k || !v) return B200_ERR_ARG;
+  if (!out || !q || !k || !v || !(scale > 0.f)) return B200_ERR_ARG;
   if (batch <= 0 || S <= 0 || kv_len <= 0 || q_pos0 < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 ||
       (hd != 64 && hd != 128) || batch > 65535 || n_q > 65535)
     return B200_ERR_SHAPE;
@@ -508,9 +519,9 @@ extern "C" int b200_flash_prefill_tc(void* out, const void* q, const void* k, co
   if ((rc = make_map(&mq, q, q_rows, q_cols, (uint64_t)q_rs, 128, 64)) != B200_OK) return rc;
   if ((rc = make_map(&mk, k, k_rows, k_cols, (uint64_t)k_rs, 128, 64)) != B200_OK) return rc;
   if ((rc = make_map(&mv, v, v_rows, v_cols, (uint64_t)v_rs, 128, 64)) != B200_OK) return rc;
-  a.n_mt = (S + FA_BM - 1) / FA_BM;
+  a.n_mp = (S + 2 * FA_BM - 1) / (2 * FA_BM);
   a.n_bh = n_q * batch;
-  const int64_t n_items = (int64_t)a.n_mt * a.n_bh;
+  const int64_t n_items = (int64_t)a.n_mp * a.n_bh;
   if (n_items > INT_MAX) return B200_ERR_SHAPE;
   a.n_items = (int)n_items;
   dim3 grid((unsigned)std::min<int64_t>(n_items, kNumSMs));
