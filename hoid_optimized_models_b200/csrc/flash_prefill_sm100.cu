@@ -75,7 +75,7 @@ __device__ __forceinline__ bool fa_item(const FaArgs& a, int r, FaItem& it) {
 // Position in the flat sequence of key tiles of all my items.
 struct FaCursor {
   int r, j;          // round of the item, key tile inside it
-  int e;             // ring entry of the tile's K (its V is e + 1)
+  int e;             // ring entry of the tile's K (its V is e + 1) = 2 x the flat tile index
   bool valid;
   FaItem it;
 };
@@ -91,6 +91,32 @@ __device__ __forceinline__ void fa_cursor_init(const FaArgs& a, int n_rounds, Fa
 __device__ __forceinline__ void fa_cursor_advance(const FaArgs& a, int n_rounds, FaCursor& c) {
   c.e += 2;
   if (++c.j == c.it.nt) fa_cursor_next_item(a, n_rounds, c);
+}
+
+// sm_100 arithmetic that halves the instruction count of the softmax inner loops: three-input
+// max, and fp32 add / fma on register pairs.
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fa_pair(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void fa_unpair(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fa_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fa_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
 // Bounded wait without an abort flag, for the teardown of a role that already gave up.
@@ -138,7 +164,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   // barrier indices: Q full / empty per (buffer, stream), ring full / empty, and per stream
   // S ready, P ready, O ready
   constexpr int QF = 0, QE = 2 * NQ, RF = 4 * NQ, RE = 4 * NQ + NR, SF = 4 * NQ + 2 * NR,
-                PF = SF + 2, OF = SF + 4, NBAR = SF + 6;
+                PF = SF + 2, OF = SF + 4, CF = SF + 6, NBAR = SF + 8;
+  // At head dim 64 tensor memory has room for P beside S, so a stream's next scores can be
+  // computed as soon as its softmax warps have pulled the current ones into registers.
+  constexpr bool SEP = HD == 64;
   static_assert(NBAR <= 32, "barrier block is 32 entries");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // Operand tiles need 1024-byte alignment.  The dynamic window starts 1 KB into the CTA's
@@ -161,7 +190,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
   pdl_launch_dependents();
   if (tid == 0) {
-    for (int i = 0; i < NBAR; ++i) mbar_init(bar(i), (i == PF || i == PF + 1) ? 4 : 1);
+    for (int i = 0; i < NBAR; ++i) mbar_init(bar(i), (i >= PF && i < PF + 2) || (i >= CF && i < CF + 2) ? 4 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -178,9 +207,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // columns: S_A 0..127, S_B 128..255 (P_X overlays the first 64 columns of S_X), O_A, O_B
+  // columns: S_A 0..127, S_B 128..255, O_A, O_B from 256; P_X (64 columns of packed bf16)
+  // from 384 at head dim 64, else over the first 64 columns of S_X
   auto tS = [&](int x) { return tmem_base + (uint32_t)x * FA_BN; };
   auto tO = [&](int x) { return tmem_base + 256u + (uint32_t)x * HD; };
+  auto tP = [&](int x) { return SEP ? tmem_base + 384u + (uint32_t)x * 64 : tS(x); };
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
@@ -284,7 +315,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           // A = P from tensor memory: 16 keys = 8 columns of packed bf16 pairs
           // B = V (MN-major over dims): 16 keys = two 8-row groups = 2048 bytes
           const uint64_t db = umma_desc_mn(sv + k * 2048, kAtomBytes, 1024);
-          tc_mma_ts(tO(x), tS(x) + k * 8, db, idesc_o, (pv.j != 0 || k != 0) ? 1u : 0u);
+          tc_mma_ts(tO(x), tP(x) + k * 8, db, idesc_o, (pv.j != 0 || k != 0) ? 1u : 0u);
         }
         tc_commit(bar(OF + x));
         ++pg[x];
@@ -299,15 +330,32 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         const bool act_a = pv.j < pv.it.n[0], act_b = pv.j < pv.it.n[1];
         bool todo_a = ps.valid && ps.j < ps.it.n[0], todo_b = ps.valid && ps.j < ps.it.n[1];
         const bool any_s = todo_a || todo_b;
-        if (act_a) { if (!issue_pv(0)) { ok = false; break; } }
-        if (todo_a) {
-          // stream A's next scores; if their operands have not landed, stream B's O goes first
-          const int r = issue_s(0, !act_b);
-          if (r < 0) { ok = false; break; }
-          if (r == 1) todo_a = false;
+        if (SEP) {
+          // P has columns of its own: a stream's next scores go out as soon as its softmax warps
+          // have the current ones in registers, ahead of the O MMA that waits for P
+          if (todo_a && act_a) {
+            if (!mbar_wait(bar(CF + 0), pg[0] & 1, abort_flag) || issue_s(0, true) != 1) { ok = false; break; }
+            todo_a = false;
+          }
+          if (act_a) { if (!issue_pv(0)) { ok = false; break; } }
+          if (todo_b && act_b) {
+            if (!mbar_wait(bar(CF + 1), pg[1] & 1, abort_flag) || issue_s(1, true) != 1) { ok = false; break; }
+            todo_b = false;
+          }
+          if (act_b) { if (!issue_pv(1)) { ok = false; break; } }
+        } else {
+          if (act_a) { if (!issue_pv(0)) { ok = false; break; } }
+          if (todo_a) {
+            // stream A's next scores; if their operands have not landed, stream B's O goes first
+            const int r = issue_s(0, !act_b);
+            if (r < 0) { ok = false; break; }
+            if (r == 1) todo_a = false;
+          }
+          if (act_b) { if (!issue_pv(1)) { ok = false; break; } }
         }
-        if (act_b) { if (!issue_pv(1)) { ok = false; break; } }
         tc_commit(bar(RE + (pv.e + 1) % NR));          // V tile free once both O MMAs retire
+        // (a stream that was idle on this tile, or whose operands were late, gets its scores now;
+        // its previous scores were consumed long ago)
         if (todo_a) { if (issue_s(0, true) != 1) { ok = false; break; } }
         if (todo_b) { if (issue_s(1, true) != 1) { ok = false; break; } }
         if (any_s) tc_commit(bar(RE + ps.e % NR));     // K tile free once both S MMAs retire
@@ -320,7 +368,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int x = warp >> 2;                          // stream
     const int row = (warp & 3) * 32 + lane;           // query row inside the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t my_s = tS(x) + lane_addr, my_o = tO(x) + lane_addr;
+    const uint32_t my_s = tS(x) + lane_addr, my_o = tO(x) + lane_addr, my_p = tP(x) + lane_addr;
     bool ok = true;
     auto ex2 = [](float v) -> float {
       float y;
@@ -345,6 +393,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int c = 0; c < FA_BN / 32; ++c) tc_ld32(my_s + c * 32, sr + c * 32);
         tc_wait_ld();
+        if (SEP) {   // the scores are in registers: the tensor core may start on the next tile's
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(CF + x));
+        }
 #define SV(i) __uint_as_float(sr[i])
         // only the last tile(s) need masking: end of the keys, or the causal diagonal
         const bool need_mask = (j * FA_BN + FA_BN > a.kv_len) ||
@@ -357,10 +410,12 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         float mx[4] = {SV(0), SV(1), SV(2), SV(3)};
 #pragma unroll
-        for (int i = 4; i < FA_BN; i += 4) {
-          mx[0] = fmaxf(mx[0], SV(i)); mx[1] = fmaxf(mx[1], SV(i + 1));
-          mx[2] = fmaxf(mx[2], SV(i + 2)); mx[3] = fmaxf(mx[3], SV(i + 3));
+        for (int i = 4; i < FA_BN - 4; i += 8) {
+          mx[0] = fa_max3(mx[0], SV(i), SV(i + 1)); mx[1] = fa_max3(mx[1], SV(i + 2), SV(i + 3));
+          mx[2] = fa_max3(mx[2], SV(i + 4), SV(i + 5)); mx[3] = fa_max3(mx[3], SV(i + 6), SV(i + 7));
         }
+        mx[0] = fa_max3(mx[0], SV(FA_BN - 4), SV(FA_BN - 3));
+        mx[1] = fa_max3(mx[1], SV(FA_BN - 2), SV(FA_BN - 1));
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
         if (j == 0) {
           m_used = (mt == -INFINITY) ? 0.f : mt;
@@ -385,24 +440,38 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         // p = exp2(s * scale - m) as packed bf16 pairs, row sum in fp32; 64 keys at a time so
         // that the first half is on its way to tensor memory while the second is computed
-        float ps[4] = {0.f, 0.f, 0.f, 0.f};
+        if (SEP && j > 0) {
+          // P has columns of its own here: the previous tile's O MMA must be done reading them.
+          // It was issued a tile of exponentials ago, so this does not normally spin.  (A second
+          // wait on the phase the rescale above may have waited for is safe: the barrier cannot
+          // move on before this warp's next arrival.)
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(OF + x), (g - 1) & 1, abort_flag))) { ok = false; break; }
+        }
+        const uint64_t sc2 = fa_pair(a.scale_log2, a.scale_log2), nm2 = fa_pair(-m_used, -m_used);
+        uint64_t ps2[2] = {0ull, 0ull};                 // two pairs of partial row sums
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t pk[32];
 #pragma unroll
           for (int i = 0; i < 64; i += 4) {
-            const float p0 = ex2(fmaf(SV(h * 64 + i), a.scale_log2, -m_used));
-            const float p1 = ex2(fmaf(SV(h * 64 + i + 1), a.scale_log2, -m_used));
-            const float p2 = ex2(fmaf(SV(h * 64 + i + 2), a.scale_log2, -m_used));
-            const float p3 = ex2(fmaf(SV(h * 64 + i + 3), a.scale_log2, -m_used));
-            ps[0] += p0; ps[1] += p1; ps[2] += p2; ps[3] += p3;
+            float t0, t1, t2, t3;
+            fa_unpair(fa_fma2(fa_pair(SV(h * 64 + i), SV(h * 64 + i + 1)), sc2, nm2), t0, t1);
+            fa_unpair(fa_fma2(fa_pair(SV(h * 64 + i + 2), SV(h * 64 + i + 3)), sc2, nm2), t2, t3);
+            const float p0 = ex2(t0), p1 = ex2(t1), p2 = ex2(t2), p3 = ex2(t3);
+            ps2[0] = fa_add2(ps2[0], fa_pair(p0, p1));
+            ps2[1] = fa_add2(ps2[1], fa_pair(p2, p3));
             pk[i / 2] = pack_bf16(p0, p1);
             pk[i / 2 + 1] = pack_bf16(p2, p3);
           }
-          tc_st32(my_s + h * 32, pk);
+          tc_st32(my_p + h * 32, pk);
         }
 #undef SV
-        l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        {
+          float s0, s1, s2, s3;
+          fa_unpair(ps2[0], s0, s1);
+          fa_unpair(ps2[1], s2, s3);
+          l_run += (s0 + s1) + (s2 + s3);
+        }
         tc_wait_st();
         // hand P (and a possibly rescaled O) to the tensor core: one arrival per warp
         tc_fence_before();
