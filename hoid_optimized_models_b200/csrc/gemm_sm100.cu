@@ -12,8 +12,8 @@
 //               load), so every global access of the epilogue is a full coalesced box
 //               instead of 32 row-strided 64-byte pieces.  Two accumulators alternate,
 //               so the epilogue of tile i overlaps the main loop of tile i+1.
-// The N extent of the tile (256 / 128 / 64) is chosen per problem so that small
-// problems (e.g. M = 1500) still give every SM a tile.
+// The N extent of the tile (256 / 128 / 64) is chosen per problem: 256 unless the problem
+// has too few such tiles to occupy even a fraction of the SMs.
 //
 // Grouped mode (MoE experts): rows of X are sorted by expert, `offsets[e]` is the
 // first row of expert e, W is [E, N, K]; M-tiles never straddle an expert for
@@ -450,12 +450,15 @@ static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M
     if (resid && (rc = make_map(&mr, resid, (uint64_t)M, (uint64_t)N, (uint64_t)ldr, 32, 64)) != B200_OK)
       return rc;
   }
-  // tile width: the widest that still gives (almost) every SM a tile
+  // Tile width.  Narrow tiles fill more SMs but each moves (128 + bn) rows of operands for
+  // 128 x bn outputs and runs the MMA below its rate at N = 64, so 256 wins as soon as it keeps
+  // well under half of the SMs busy (measured on M = 1024 / 1500 prefill shapes: 256 beats 128
+  // by 1.2-1.5x from 80 tiles up and is within 8 % at 60).
   const long tiles256 = (long)max_tiles_m * ((N + 255) / 256);
   const long tiles128 = (long)max_tiles_m * ((N + 127) / 128);
   const bool pdl = (flags & B200_FLAG_PDL) != 0;
   const int forced = g_tuning[B200_TUNE_GEMM_BN];
-  int bn = tiles256 >= 2 * kNumSMs ? 256 : (tiles128 >= kNumSMs ? 128 : 64);
+  int bn = tiles256 >= 64 ? 256 : (tiles128 >= 32 ? 128 : 64);
   if (forced == 256 || forced == 128 || forced == 64) bn = forced;
   if (bn == 256) return gemm_launch_bn<256>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);
   if (bn == 128) return gemm_launch_bn<128>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);
