@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("B200OPS_LIB") or os.path.join(HERE, "libb200ops.so")
 
 BF16, F32 = 0, 1
 FLAG_PDL = 1
-EPI_NONE, EPI_SWIGLU, EPI_GELU = 0, 1, 2
+EPI_NONE, EPI_SWIGLU, EPI_GELU, EPI_GEGLU = 0, 1, 2, 3
 
 ERRORS = {
     -1: "B200_ERR_SHAPE (unsupported size / divisibility)",

@@ -15,6 +15,10 @@
 // The N extent of the tile (256 / 128 / 64) is chosen per problem: 256 unless the problem
 // has too few such tiles to occupy even a fraction of the SMs.
 //
+// GEGLU mode (a stock [2 O, K] projection, value half first): a tile's 256 W rows are 128 rows of
+// the value half and the matching 128 rows of the gate half, loaded as two boxes, so ONE N = 256
+// MMA produces both and the epilogue writes only (value + bias) * gelu(gate + bias).
+//
 // Grouped mode (MoE experts): rows of X are sorted by expert, `offsets[e]` is the
 // first row of expert e, W is [E, N, K]; M-tiles never straddle an expert for
 // stores (loads may read the neighbour's rows, the epilogue masks them).
@@ -174,7 +178,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
           const uint32_t sa = base + stage * kStageBytes;
           mbar_expect_tx(full_bar(stage), kStageBytes);
           tma_load_2d(sa, &map_x, full_bar(stage), kb * BK, tl.row0);
-          tma_load_2d(sa + kABytes, &map_w, full_bar(stage), kb * BK, tl.wrow0);
+          if (a.epilogue == B200_EPI_GEGLU) {
+            // value rows [n0 / 2, +128) and gate rows [N / 2 + n0 / 2, +128) through a 128-row box
+            tma_load_2d(sa + kABytes, &map_w, full_bar(stage), kb * BK, tl.n0 >> 1);
+            tma_load_2d(sa + kABytes + kBBytes / 2, &map_w, full_bar(stage), kb * BK, (a.N >> 1) + (tl.n0 >> 1));
+          } else {
+            tma_load_2d(sa + kABytes, &map_w, full_bar(stage), kb * BK, tl.wrow0);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -301,6 +311,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
           }
         }
         if (!ok) break;
+      } else if (a.epilogue == B200_EPI_GEGLU) {
+        // accumulator columns [0, BN/2) are the value half, [BN/2, BN) the gate half of output
+        // columns n0 / 2 ..
+        const int O = a.N >> 1;
+#pragma unroll 1
+        for (int c = half; c < BN / 64; c += 2) {
+          const int ocol0 = (tl.n0 >> 1) + c * 32;
+          if (ocol0 >= O) break;  // warp-uniform
+          uint32_t rv[32], rg[32];
+          tc_ld32(taddr + c * 32, rv);
+          tc_ld32(taddr + BN / 2 + c * 32, rg);
+          tc_wait_ld();
+          if (row_ok) {
+            uint16_t* dst = a.y + (size_t)row * a.ldy + ocol0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (ocol0 + j < O) {
+                float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, bg[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (a.bias != nullptr) {
+                  unpack8(*reinterpret_cast<const uint4*>(a.bias + ocol0 + j), bv);
+                  unpack8(*reinterpret_cast<const uint4*>(a.bias + O + ocol0 + j), bg);
+                }
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  o[e] = (__uint_as_float(rv[j + e]) + bv[e]) * gelu_erf(__uint_as_float(rg[j + e]) + bg[e]);
+                uint4 w;
+                w.x = pack_bf16(o[0], o[1]); w.y = pack_bf16(o[2], o[3]);
+                w.z = pack_bf16(o[4], o[5]); w.w = pack_bf16(o[6], o[7]);
+                *reinterpret_cast<uint4*>(dst + j) = w;
+              }
+            }
+          }
+        }
       } else {
 #pragma unroll 1
       for (int c = half; c < BN / 32; c += 2) {
@@ -404,7 +448,7 @@ static int gemm_launch_bn(const CUtensorMap& mx, const void* w, uint64_t wrows, 
   constexpr size_t smem = 1024 + (size_t)kStages * (kABytes + BN * BK * 2) +
                           kEpiWarps * kStageBoxBytes + 256 + 2 * (kMaxExperts + 1) * 4;
   CUtensorMap mw;
-  int rc = make_map(&mw, w, wrows, (uint64_t)K, (uint64_t)ldw, BN, BK);
+  int rc = make_map(&mw, w, wrows, (uint64_t)K, (uint64_t)ldw, a.epilogue == B200_EPI_GEGLU ? BN / 2 : BN, BK);
   if (rc != B200_OK) return rc;
   const int nt = (a.N + BN - 1) / BN;
   long tiles = (long)max_tiles_m * nt;
@@ -427,9 +471,11 @@ static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)y & 15) ||
       ((uintptr_t)bias & 15) || ((uintptr_t)resid & 15))
     return B200_ERR_ALIGN;
-  if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_GELU) return B200_ERR_ARG;
-  if (epilogue == B200_EPI_SWIGLU && (resid != nullptr || (N & 15))) return B200_ERR_SHAPE;
-  if (y_dtype == B200_F32 && (resid != nullptr || epilogue == B200_EPI_SWIGLU)) return B200_ERR_ARG;
+  if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_GEGLU) return B200_ERR_ARG;
+  const bool halves = epilogue == B200_EPI_SWIGLU || epilogue == B200_EPI_GEGLU;
+  if (halves && (resid != nullptr || (N & 15))) return B200_ERR_SHAPE;
+  if (epilogue == B200_EPI_GEGLU && n_groups > 0) return B200_ERR_ARG;
+  if (y_dtype == B200_F32 && (resid != nullptr || halves)) return B200_ERR_ARG;
   if (n_groups < 0 || n_groups > kMaxExperts || (n_groups > 0 && !offsets)) return B200_ERR_ARG;
   int rc = get_encode();
   if (rc != B200_OK) return rc;
@@ -439,7 +485,7 @@ static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M
   a.offsets = offsets; a.status = status;
   a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.ldr = ldr; a.epilogue = epilogue; a.n_groups = n_groups;
   a.y_dtype = y_dtype;
-  a.tma_epilogue = (y_dtype == B200_BF16 && epilogue != B200_EPI_SWIGLU) ? 1 : 0;
+  a.tma_epilogue = (y_dtype == B200_BF16 && !halves) ? 1 : 0;
 
   CUtensorMap mx, my, mr;
   const uint64_t wrows = n_groups > 0 ? (uint64_t)n_groups * N : (uint64_t)N;
@@ -460,6 +506,7 @@ static int gemm_launch(const void* x, const void* w, void* y, int y_dtype, int M
   const int forced = g_tuning[B200_TUNE_GEMM_BN];
   int bn = tiles256 >= 64 ? 256 : (tiles128 >= 32 ? 128 : 64);
   if (forced == 256 || forced == 128 || forced == 64) bn = forced;
+  if (epilogue == B200_EPI_GEGLU) bn = 256;   // the two halves of a tile are 128 W rows each
   if (bn == 256) return gemm_launch_bn<256>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);
   if (bn == 128) return gemm_launch_bn<128>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);
   return gemm_launch_bn<64>(mx, w, wrows, K, ldw, my, mr, a, max_tiles_m, stream, pdl);

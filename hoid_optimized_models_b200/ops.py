@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import BF16, F32, FLAG_PDL, EPI_NONE, EPI_SWIGLU, EPI_GELU, check
+from ._lib import BF16, F32, FLAG_PDL, EPI_NONE, EPI_SWIGLU, EPI_GELU, EPI_GEGLU, check
 
 Tensor = torch.Tensor
 
@@ -340,14 +340,16 @@ def check_status(device) -> None:
 @torch.library.custom_op("b200::gemm", mutates_args=("y",))
 def gemm(y: Tensor, x: Tensor, w: Tensor, bias: Optional[Tensor] = None,
          resid: Optional[Tensor] = None, epilogue: int = EPI_NONE) -> None:
-    """y[M, N] = x[M, K] w[N, K]^T (+ bias) (+ resid) with optional SwiGLU / GELU epilogue."""
+    """y[M, N] = x[M, K] w[N, K]^T (+ bias) (+ resid) with optional SwiGLU / GELU epilogue, or
+    EPI_GEGLU: w is a stock [2 O, K] GEGLU projection (value half first) and
+    y[M, O] = (x Wv^T + bv) * gelu(x Wg^T + bg)."""
     for t, n in ((x, "x"), (w, "w"), (bias, "bias"), (resid, "resid")):
         _bf16(t, n)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise RuntimeError("x / w inner dimensions differ")
-    n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    n_out = N // 2 if epilogue in (EPI_SWIGLU, EPI_GEGLU) else N
     if y.shape[0] != M or y.shape[1] != n_out:
         raise RuntimeError(f"y must be [{M}, {n_out}]")
     if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:

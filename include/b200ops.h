@@ -51,7 +51,9 @@ enum {
 enum {
   B200_EPI_NONE = 0,
   B200_EPI_SWIGLU = 1,     /* rows interleaved (gate_j, up_j): out[j] = silu(y[2j]) * y[2j+1] */
-  B200_EPI_GELU = 2        /* exact erf GELU on (y + bias) */
+  B200_EPI_GELU = 2,       /* exact erf GELU on (y + bias) */
+  B200_EPI_GEGLU = 3       /* GEMM only. W is a stock [2 O, K] GEGLU projection, value half first:
+                              out[M, O] = (x Wv^T + bv) * gelu_erf(x Wg^T + bg) */
 };
 
 int b200_version(void);
@@ -287,7 +289,12 @@ int b200_decode_layers(const void* plan_dev, int n_layers, const float* cos_t, c
  * tensor memory, bf16 out; fp32 out for plain / bias / GELU epilogues, e.g. router logits) on
  * tcgen05 tensor cores fed by TMA.
  *   bias  : optional bf16 [N];  resid : optional bf16 [M, ldr], Y = resid + X W^T (may alias y)
- *   epilogue: B200_EPI_SWIGLU (W rows interleaved gate/up, Y is [M, N/2]) or B200_EPI_GELU
+ *   epilogue: B200_EPI_SWIGLU (W rows interleaved gate/up, Y is [M, N/2]), B200_EPI_GELU, or
+ *             B200_EPI_GEGLU (W = [value half; gate half] as torch.chunk(2, -1) splits the stock
+ *             projection, bias likewise, Y is [M, N/2]; both halves of an output tile come from
+ *             one N = 256 MMA.  Replaces the dual-GEMM of
+ *             models/sdxl/kernels/dual_geglu.cutedsl.py, called at
+ *             models/sdxl/sdxl_optimized.py:380-393)
  *   status: optional device int32; receives B200_ERR_TIMEOUT if a bounded wait expired
  * Reference: torch.matmul at M = P, models/llama31-8b/llama31_optimized.py:479-499;
  * torch.mm(out=) models/bge-m3/bge_optimized.py:340-349; the CuTe-DSL GEMMs

@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-EPI_NONE, EPI_SWIGLU, EPI_GELU = 0, 1, 2
+EPI_NONE, EPI_SWIGLU, EPI_GELU, EPI_GEGLU = 0, 1, 2, 3
 Tensor = torch.Tensor
 _STATUS = torch.zeros(1, dtype=torch.int32)
 

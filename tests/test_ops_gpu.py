@@ -393,6 +393,23 @@ def test_moe_grouped_gemm(dev):
             assert rel_err(y[a:b], ref) < 1e-2, f"expert {e}"
 
 
+@pytest.mark.parametrize("M,K,O", [(300, 640, 2560), (4096, 1280, 5120), (130, 64, 200)])
+def test_gemm_geglu(dev, M, K, O):
+    """Stock GEGLU projection [2 O, K], value half first: (x Wv^T + bv) * gelu(x Wg^T + bg) from one
+    GEMM launch (the dual-GEMM of models/sdxl/kernels/dual_geglu.cutedsl.py)."""
+    from hoid_optimized_models_b200 import ops
+    g = torch.Generator().manual_seed(M + O)
+    x = bf(torch.randn(M, K, generator=g)).to(dev)
+    w = bf(torch.randn(2 * O, K, generator=g) * K ** -0.5).to(dev)
+    b = bf(torch.randn(2 * O, generator=g) * 0.1).to(dev)
+    y = torch.full((M, O), float("nan"), dtype=torch.bfloat16, device=dev)
+    ops.gemm(y, x, w, bias=b, epilogue=ops.EPI_GEGLU)
+    ops.check_status(dev)
+    full = x.float() @ w.float().T + b.float()
+    ref = full[:, :O] * torch.nn.functional.gelu(full[:, O:])
+    assert rel_err(y, ref) < 1e-2
+
+
 # ----------------------------------------------------------------------------- flash prefill
 @pytest.mark.parametrize("S,n_q,n_kv,hd,causal", [(64, 4, 1, 128, True), (200, 8, 2, 128, True),
                                                   (1000, 32, 8, 128, True), (512, 16, 16, 64, False),
