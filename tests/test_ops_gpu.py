@@ -440,6 +440,35 @@ def test_flash_prefill(dev, S, n_q, n_kv, hd, causal):
     assert rel_err(out[0], ref) < 2e-2
 
 
+@pytest.mark.parametrize("S,n_q,n_kv,hd,causal", [(640, 4, 2, 128, False), (900, 4, 4, 64, False),
+                                                  (1100, 8, 2, 128, True)])
+def test_flash_prefill_growing_row_maxima(dev, S, n_q, n_kv, hd, causal):
+    """Keys grow with position, so the row maxima rise by far more than 2^8 from one key tile to
+    the next: every tile takes the path that rescales the output accumulator in tensor memory
+    (with well-scaled inputs the reference maximum is almost never raised after the first tile)."""
+    from hoid_optimized_models_b200 import ops
+    g = torch.Generator().manual_seed(S)
+    q = bf(torch.randn(1, S, n_q, hd, generator=g) * 2.0)
+    grow = (1.0 + 7.0 * torch.arange(S + 2) / S).view(1, 1, S + 2, 1)
+    kc = bf(torch.randn(1, n_kv, S + 2, hd, generator=g) * grow)
+    vc = bf(torch.randn(1, n_kv, S + 2, hd, generator=g))
+    G = n_q // n_kv
+    kk = kc[:, :, :S].float().repeat_interleave(G, 1)
+    vv = vc[:, :, :S].float().repeat_interleave(G, 1)
+    sc = torch.einsum("bshd,bhkd->bhsk", q.float(), kk) * hd ** -0.5
+    if causal:
+        sc = sc.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+    # the scores really do outgrow the lazy-rescale threshold (8 in log2 units) tile after tile
+    tile_max = torch.stack([sc[..., j:j + 128].amax(-1) for j in range(0, S - 127, 128)], -1) * 1.4427
+    last_rows = tile_max[:, :, -64:]                    # these see every key tile, causal or not
+    assert float((last_rows[..., -1] - last_rows[..., 0]).median()) > 16
+    ref = torch.einsum("bhsk,bhkd->bshd", torch.softmax(sc, -1), vv)
+    out = torch.full((1, S, n_q, hd), float("nan"), dtype=torch.bfloat16, device=dev)
+    ops.flash_prefill(out, q.to(dev), kc.to(dev), vc.to(dev), S, causal, hd ** -0.5)
+    ops.check_status(dev)
+    assert rel_err(out, ref) < 2e-2
+
+
 @pytest.mark.parametrize("B,S,n_q,n_kv,hd,causal", [(12, 512, 16, 16, 64, False), (5, 700, 8, 2, 128, True),
                                                      (3, 130, 6, 6, 64, False)])
 def test_flash_prefill_batched_many_rounds(dev, B, S, n_q, n_kv, hd, causal):
