@@ -151,6 +151,119 @@ constexpr uint32_t fa_idesc(int n, int b_major) {
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// One key tile of one query row: scores from tensor memory -> row maximum -> (rarely) rescale of
+// the output accumulator -> P = exp2(.) as packed bf16 back to tensor memory -> hand-over.
+// By itself (one warp per scheduler, nothing else running) this body takes ~1500 clocks per tile,
+// 1024 of them the 128 exponentials at 8 clocks each on the special-function unit.  Measured and
+// rejected: reading the row from tensor memory twice, 32 columns at a time, to halve the registers
+// held (no faster by itself, slower in the kernel); a quarter or half of the exponentials as a
+// cubic on the FMA pipe (12 % faster by itself at a quarter, no gain in the kernel, where the
+// stream's MMAs and hand-overs are the other half of the period).
+struct FaRowState { float m_used, l_run; int ok; };
+
+template <int HD, bool SEP>
+__device__ __forceinline__ FaRowState fa_softmax_tile(uint32_t my_s, uint32_t my_p, uint32_t my_o,
+                                                   float scale_log2, float m_used, float l_run,
+                                                   int first, int valid, uint32_t bar_cf,
+                                                   uint32_t bar_of, uint32_t of_parity,
+                                                   uint32_t bar_pf, volatile int* abort_flag) {
+  const int lane = threadIdx.x & 31;
+  FaRowState st;
+  st.ok = 0;
+  auto ex2 = [](float v) -> float {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(v));
+    return y;
+  };
+  uint32_t sr[FA_BN];                            // the row's scores (fp32 bit patterns)
+#pragma unroll
+  for (int c = 0; c < FA_BN / 32; ++c) tc_ld32(my_s + c * 32, sr + c * 32);
+  tc_wait_ld();
+  if (SEP) {   // the scores are in registers: the tensor core may start on the next tile's
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_cf);
+  }
+#define SV(i) __uint_as_float(sr[i])
+  // only the last tile(s) need masking: end of the keys, or the causal diagonal
+  if (valid < FA_BN) {
+#pragma unroll
+    for (int i = 0; i < FA_BN; ++i) sr[i] = (i < valid) ? sr[i] : 0xff800000u;   // -inf
+  }
+  float mx[4] = {SV(0), SV(1), SV(2), SV(3)};
+#pragma unroll
+  for (int i = 4; i < FA_BN - 4; i += 8) {
+    mx[0] = fa_max3(mx[0], SV(i), SV(i + 1)); mx[1] = fa_max3(mx[1], SV(i + 2), SV(i + 3));
+    mx[2] = fa_max3(mx[2], SV(i + 4), SV(i + 5)); mx[3] = fa_max3(mx[3], SV(i + 6), SV(i + 7));
+  }
+  mx[0] = fa_max3(mx[0], SV(FA_BN - 4), SV(FA_BN - 3));
+  mx[1] = fa_max3(mx[1], SV(FA_BN - 2), SV(FA_BN - 1));
+  const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+  if (first) {
+    m_used = (mt == -INFINITY) ? 0.f : mt;
+  } else if (__any_sync(0xffffffffu, mt > m_used + kFaLazy)) {
+    // Some row of this warp outgrew its reference maximum: rescale the warp's rows of O
+    // (in tensor memory) once the tensor core has finished the previous tile's O.
+    // (waits are voted on so that the warp-collective tensor-memory accesses stay convergent)
+    if (!__all_sync(0xffffffffu, mbar_wait(bar_of, of_parity, abort_flag))) return st;
+    tc_fence_after();
+    const float m_new = fmaxf(m_used, mt);
+    const float f = ex2(m_used - m_new);
+#pragma unroll
+    for (int c = 0; c < HD / 16; ++c) {
+      uint32_t rr[16];
+      tc_ld16(my_o + c * 16, rr);
+      tc_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * f);
+      tc_st16(my_o + c * 16, rr);
+    }
+    l_run *= f;
+    m_used = m_new;
+  }
+  if (SEP && !first) {
+    // P has columns of its own here: the previous tile's O MMA must be done reading them.
+    // It was issued a tile of exponentials ago, so this does not normally spin.  (A second
+    // wait on the phase the rescale above may have waited for is safe: the barrier cannot
+    // move on before this warp's next arrival.)
+    if (!__all_sync(0xffffffffu, mbar_wait(bar_of, of_parity, abort_flag))) return st;
+  }
+  // p = exp2(s * scale - m) as packed bf16 pairs, row sum in fp32; 64 keys at a time so
+  // that the first half is on its way to tensor memory while the second is computed
+  const uint64_t sc2 = fa_pair(scale_log2, scale_log2), nm2 = fa_pair(-m_used, -m_used);
+  uint64_t ps2[2] = {0ull, 0ull};                 // two pairs of partial row sums
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t pk[32];
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) {
+      float t0, t1, t2, t3;
+      fa_unpair(fa_fma2(fa_pair(SV(h * 64 + i), SV(h * 64 + i + 1)), sc2, nm2), t0, t1);
+      fa_unpair(fa_fma2(fa_pair(SV(h * 64 + i + 2), SV(h * 64 + i + 3)), sc2, nm2), t2, t3);
+      const float p0 = ex2(t0), p1 = ex2(t1), p2 = ex2(t2), p3 = ex2(t3);
+      ps2[0] = fa_add2(ps2[0], fa_pair(p0, p1));
+      ps2[1] = fa_add2(ps2[1], fa_pair(p2, p3));
+      pk[i / 2] = pack_bf16(p0, p1);
+      pk[i / 2 + 1] = pack_bf16(p2, p3);
+    }
+    tc_st32(my_p + h * 32, pk);
+  }
+#undef SV
+  {
+    float s0, s1, s2, s3;
+    fa_unpair(ps2[0], s0, s1);
+    fa_unpair(ps2[1], s2, s3);
+    l_run += (s0 + s1) + (s2 + s3);
+  }
+  tc_wait_st();
+  // hand P (and a possibly rescaled O) to the tensor core: one arrival per warp
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_pf);
+  st.m_used = m_used; st.l_run = l_run; st.ok = 1;
+  return st;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kFaThreads, 1)
 flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -370,11 +483,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t my_s = tS(x) + lane_addr, my_o = tO(x) + lane_addr, my_p = tP(x) + lane_addr;
     bool ok = true;
-    auto ex2 = [](float v) -> float {
-      float y;
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(v));
-      return y;
-    };
     int g = 0;                                        // key tiles of this stream consumed so far
     for (int r = 0; r < n_rounds && ok; ++r) {
       FaItem it;
@@ -389,94 +497,18 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         // (waits are voted on so that the warp-collective tensor-memory accesses stay convergent)
         if (!__all_sync(0xffffffffu, mbar_wait(bar(SF + x), g & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        uint32_t sr[FA_BN];                            // the row's scores (fp32 bit patterns)
-#pragma unroll
-        for (int c = 0; c < FA_BN / 32; ++c) tc_ld32(my_s + c * 32, sr + c * 32);
-        tc_wait_ld();
-        if (SEP) {   // the scores are in registers: the tensor core may start on the next tile's
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(CF + x));
-        }
-#define SV(i) __uint_as_float(sr[i])
         // only the last tile(s) need masking: end of the keys, or the causal diagonal
-        const bool need_mask = (j * FA_BN + FA_BN > a.kv_len) ||
-                               (a.causal && j * FA_BN + FA_BN - 1 > a.q_pos0 + m0);
-        if (need_mask) {
-          int valid = a.kv_len - j * FA_BN;
+        int valid = FA_BN;
+        if ((j * FA_BN + FA_BN > a.kv_len) || (a.causal && j * FA_BN + FA_BN - 1 > a.q_pos0 + m0)) {
+          valid = a.kv_len - j * FA_BN;
           if (a.causal) valid = min(valid, qpos - j * FA_BN + 1);
-#pragma unroll
-          for (int i = 0; i < FA_BN; ++i) sr[i] = (i < valid) ? sr[i] : 0xff800000u;   // -inf
+          valid = min(valid, FA_BN - 1 + (valid >= FA_BN));   // keeps "== FA_BN" meaning "no mask"
         }
-        float mx[4] = {SV(0), SV(1), SV(2), SV(3)};
-#pragma unroll
-        for (int i = 4; i < FA_BN - 4; i += 8) {
-          mx[0] = fa_max3(mx[0], SV(i), SV(i + 1)); mx[1] = fa_max3(mx[1], SV(i + 2), SV(i + 3));
-          mx[2] = fa_max3(mx[2], SV(i + 4), SV(i + 5)); mx[3] = fa_max3(mx[3], SV(i + 6), SV(i + 7));
-        }
-        mx[0] = fa_max3(mx[0], SV(FA_BN - 4), SV(FA_BN - 3));
-        mx[1] = fa_max3(mx[1], SV(FA_BN - 2), SV(FA_BN - 1));
-        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
-        if (j == 0) {
-          m_used = (mt == -INFINITY) ? 0.f : mt;
-        } else if (__any_sync(0xffffffffu, mt > m_used + kFaLazy)) {
-          // Some row of this warp outgrew its reference maximum: rescale the warp's rows of O
-          // (in tensor memory) once the tensor core has finished the previous tile's O.
-          if (!__all_sync(0xffffffffu, mbar_wait(bar(OF + x), (g - 1) & 1, abort_flag))) { ok = false; break; }
-          tc_fence_after();
-          const float m_new = fmaxf(m_used, mt);
-          const float f = ex2(m_used - m_new);
-#pragma unroll
-          for (int c = 0; c < HD / 16; ++c) {
-            uint32_t rr[16];
-            tc_ld16(my_o + c * 16, rr);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * f);
-            tc_st16(my_o + c * 16, rr);
-          }
-          l_run *= f;
-          m_used = m_new;
-        }
-        // p = exp2(s * scale - m) as packed bf16 pairs, row sum in fp32; 64 keys at a time so
-        // that the first half is on its way to tensor memory while the second is computed
-        if (SEP && j > 0) {
-          // P has columns of its own here: the previous tile's O MMA must be done reading them.
-          // It was issued a tile of exponentials ago, so this does not normally spin.  (A second
-          // wait on the phase the rescale above may have waited for is safe: the barrier cannot
-          // move on before this warp's next arrival.)
-          if (!__all_sync(0xffffffffu, mbar_wait(bar(OF + x), (g - 1) & 1, abort_flag))) { ok = false; break; }
-        }
-        const uint64_t sc2 = fa_pair(a.scale_log2, a.scale_log2), nm2 = fa_pair(-m_used, -m_used);
-        uint64_t ps2[2] = {0ull, 0ull};                 // two pairs of partial row sums
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 64; i += 4) {
-            float t0, t1, t2, t3;
-            fa_unpair(fa_fma2(fa_pair(SV(h * 64 + i), SV(h * 64 + i + 1)), sc2, nm2), t0, t1);
-            fa_unpair(fa_fma2(fa_pair(SV(h * 64 + i + 2), SV(h * 64 + i + 3)), sc2, nm2), t2, t3);
-            const float p0 = ex2(t0), p1 = ex2(t1), p2 = ex2(t2), p3 = ex2(t3);
-            ps2[0] = fa_add2(ps2[0], fa_pair(p0, p1));
-            ps2[1] = fa_add2(ps2[1], fa_pair(p2, p3));
-            pk[i / 2] = pack_bf16(p0, p1);
-            pk[i / 2 + 1] = pack_bf16(p2, p3);
-          }
-          tc_st32(my_p + h * 32, pk);
-        }
-#undef SV
-        {
-          float s0, s1, s2, s3;
-          fa_unpair(ps2[0], s0, s1);
-          fa_unpair(ps2[1], s2, s3);
-          l_run += (s0 + s1) + (s2 + s3);
-        }
-        tc_wait_st();
-        // hand P (and a possibly rescaled O) to the tensor core: one arrival per warp
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(PF + x));
+        const FaRowState st = fa_softmax_tile<HD, SEP>(my_s, my_p, my_o, a.scale_log2, m_used, l_run, j == 0,
+                                                        valid, bar(CF + x), bar(OF + x), (uint32_t)((g - 1) & 1),
+                                                        bar(PF + x), abort_flag);
+        if (!st.ok) { ok = false; break; }
+        m_used = st.m_used; l_run = st.l_run;
       }
       // item epilogue: O / row sum -> bf16 -> global
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(OF + x), (g - 1) & 1, abort_flag));
