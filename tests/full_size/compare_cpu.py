@@ -48,6 +48,7 @@ def compare_decoder(d, floor):
     got_h = torch.from_numpy(d["prefill_hidden"].astype(np.float32))   # [L, R, H]
     keep = torch.ones(len(sel), dtype=torch.bool)
     rerouted = 0
+    exhausted = None
     errs = []
     for l in range(cfg.layers - 1):
         if cfg.n_experts:
@@ -62,6 +63,9 @@ def compare_decoder(d, floor):
             rerouted = int((~keep).sum())
         ref = hidden[l + 1][:P]
         dd = (got_h[l] - ref[sel])[keep]
+        if dd.numel() == 0:         # every sampled row has met a router near-tie by this depth
+            exhausted = l if exhausted is None else exhausted
+            continue
         errs.append(float(dd.abs().max() / ref.abs().max()))
     step_h = torch.from_numpy(d["step_hidden"])
     step_errs = [float((step_h[l] - hidden[l + 1][P]).abs().max() / hidden[l + 1][P].abs().max())
@@ -85,7 +89,7 @@ def compare_decoder(d, floor):
     first_over = next((l for l, e in enumerate(errs) if e >= 2e-2), None)
     print(f"| {name} | {cfg.layers} L, P={P}, {N - 1} steps | {max(errs):.2e} (layer {int(np.argmax(errs))}; "
           f"first layer >= 2e-2: {first_over}) | {max(step_errs):.2e} | {cos:.5f} | {float(lerr.max()):.3f} | "
-          f"{len(flips)} {flips} | {rerouted} | transformers {transformers.__version__}, oracle {t_or:.0f} s, "
+          f"{len(flips)} {flips} | {rerouted}{'' if exhausted is None else f' (all sampled rows by layer {exhausted})'} | transformers {transformers.__version__}, oracle {t_or:.0f} s, "
           f"persistent kernel {bool(d['persistent_kernel'])}{fl} |", flush=True)
 
 
