@@ -1,4 +1,4 @@
-// (QK-RMSNorm +) rotate-half RoPE + KV-cache write, hd/8 lanes per (token, head).
+// (QK-RMSNorm +) rotate-half RoPE + KV-cache write, one CTA per token, hd/8 lanes per head.
 //
 // Heads of the packed projection row are laid out q[0..n_q), k[0..n_kv),
 // v[0..n_kv).  q heads go to q_out, k heads are normalised/rotated straight
@@ -33,78 +33,85 @@ __device__ __forceinline__ void st4(void* p, int dtype, size_t i, const float* f
   }
 }
 
-// A group of LPH = hd/8 lanes owns one (token, head): lane l of the group holds dims
-// [4l, 4l+4) of the first half and the matching four of the second half, so every access is
-// 8 or 16 bytes wide and a warp covers 32 / LPH heads.
-__global__ void __launch_bounds__(128) qk_rope_cache_kernel(RopeArgs a) {
+// One CTA per token.  A group of LPH = hd/8 lanes owns one head at a time and walks the token's
+// heads (q, then k, then v) with a stride of the CTA's group count: lane l of the group holds
+// dims [4l, 4l+4) of the first half and the matching four of the second half, so every access is
+// 8 or 16 bytes wide, the token's cos / sin values are loaded once per thread instead of once
+// per head, and a thread's loads of successive heads are independent (several in flight).
+constexpr int kRopeThreads = 128;
+
+__global__ void __launch_bounds__(kRopeThreads) qk_rope_cache_kernel(RopeArgs a) {
   const int hd = a.hd, half = hd >> 1;
   const int lph = half >> 2;                       // lanes per head: 16 (hd 128) or 8 (hd 64)
+  const int grp = threadIdx.x / lph, l = threadIdx.x - grp * lph;
+  const int ngrp = kRopeThreads / lph;
   const int lane = threadIdx.x & 31;
-  const int sub = lane / lph, l = lane - sub * lph;
-  const int hpw = 32 / lph;                        // heads per warp
+  const int sub = lane / lph;                      // group inside the warp
   const int slots = a.n_q + 2 * a.n_kv;
-  const long slot = ((long)blockIdx.x * 4 + (threadIdx.x >> 5)) * hpw + sub;
+  const int token = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
-  const bool active = slot < (long)a.s * slots;
-  const int token = active ? (int)(slot / slots) : 0;
-  const int h = active ? (int)(slot - (long)token * slots) : 0;
   const int pos = a.pos_dev[0] + token;
   const bool in_cache = pos >= 0 && pos < a.max_seq;   // never write outside the cache
-  const size_t src0 = ((size_t)token * slots + h) * hd;
-
-  if (h < a.n_q + a.n_kv) {
-    const bool is_q = h < a.n_q;
-    const uint16_t* nw = is_q ? a.qn_w : a.kn_w;
-    float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-    if (active) {
-      ld4(a.qkv, a.qkv_dtype, src0 + 4 * l, lo);
-      ld4(a.qkv, a.qkv_dtype, src0 + half + 4 * l, hi);
-    }
-    float inv = 1.f;
-    if (nw != nullptr) {                             // warp-uniform: all heads or none are normed
-      float ss = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
-      // only the lanes of this head take part: other groups of the warp may hold a V head
-      const unsigned gmask = (lph == 32 ? 0xffffffffu : ((1u << lph) - 1u)) << (sub * lph);
-      for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(gmask, ss, o);
-      inv = rsqrtf(ss / (float)hd + a.eps);
-    }
-    if (!active || (!is_q && !in_cache)) return;
-    if (nw != nullptr) {
-      float wl[4], wh[4];
-      ld4(nw, B200_BF16, 4 * l, wl);
-      ld4(nw, B200_BF16, half + 4 * l, wh);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) { lo[e] = lo[e] * inv * wl[e]; hi[e] = hi[e] * inv * wh[e]; }
-    }
-    float c[4], sn[4];
+  float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+  if (in_cache) {                                  // the tables have max_seq rows
     ld4(a.cos_t, B200_F32, (size_t)pos * half + 4 * l, c);
     ld4(a.sin_t, B200_F32, (size_t)pos * half + 4 * l, sn);
-    float r0[4], r1[4];
+  }
+  float wq[2][4], wk[2][4];
+  const bool normed = a.qn_w != nullptr;           // all q and k heads or none
+  if (normed) {
+    ld4(a.qn_w, B200_BF16, 4 * l, wq[0]); ld4(a.qn_w, B200_BF16, half + 4 * l, wq[1]);
+    ld4(a.kn_w, B200_BF16, 4 * l, wk[0]); ld4(a.kn_w, B200_BF16, half + 4 * l, wk[1]);
+  }
+  const unsigned gmask = (lph == 32 ? 0xffffffffu : ((1u << lph) - 1u)) << (sub * lph);
+  const int n_rot = a.n_q + a.n_kv;
+  // every group of a warp runs the same number of iterations (the shuffles below need the
+  // group's lanes, not the warp's, but a uniform trip count keeps the code simple)
+  for (int h0 = 0; h0 < slots; h0 += ngrp) {
+    const int h = h0 + grp;
+    if (h >= slots) break;                         // whole groups leave together
+    const size_t src0 = ((size_t)token * slots + h) * hd;
+    if (h < n_rot) {
+      const bool is_q = h < a.n_q;
+      float lo[4], hi[4];
+      ld4(a.qkv, a.qkv_dtype, src0 + 4 * l, lo);
+      ld4(a.qkv, a.qkv_dtype, src0 + half + 4 * l, hi);
+      if (normed) {
+        float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      r0[e] = lo[e] * c[e] - hi[e] * sn[e];
-      r1[e] = hi[e] * c[e] + lo[e] * sn[e];
-    }
-    if (is_q) {
-      const size_t d = ((size_t)token * a.n_q + h) * hd;
-      st4(a.q_out, a.q_dtype, d + 4 * l, r0);
-      st4(a.q_out, a.q_dtype, d + half + 4 * l, r1);
+        for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+        for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(gmask, ss, o);
+        const float inv = rsqrtf(ss / (float)hd + a.eps);
+        const float (*w)[4] = is_q ? wq : wk;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { lo[e] = lo[e] * inv * w[0][e]; hi[e] = hi[e] * inv * w[1][e]; }
+      }
+      if (!is_q && !in_cache) continue;
+      float r0[4], r1[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        r0[e] = lo[e] * c[e] - hi[e] * sn[e];
+        r1[e] = hi[e] * c[e] + lo[e] * sn[e];
+      }
+      if (is_q) {
+        const size_t d = ((size_t)token * a.n_q + h) * hd;
+        st4(a.q_out, a.q_dtype, d + 4 * l, r0);
+        st4(a.q_out, a.q_dtype, d + half + 4 * l, r1);
+      } else {
+        const size_t d = ((size_t)(h - a.n_q) * a.max_seq + pos) * hd;
+        st4(a.kcache, B200_BF16, d + 4 * l, r0);
+        st4(a.kcache, B200_BF16, d + half + 4 * l, r1);
+      }
     } else {
-      const size_t d = ((size_t)(h - a.n_q) * a.max_seq + pos) * hd;
-      st4(a.kcache, B200_BF16, d + 4 * l, r0);
-      st4(a.kcache, B200_BF16, d + half + 4 * l, r1);
+      if (!in_cache) continue;
+      const size_t d = ((size_t)(h - n_rot) * a.max_seq + pos) * hd;
+      float x[4], y[4];
+      ld4(a.qkv, a.qkv_dtype, src0 + 8 * l, x);
+      ld4(a.qkv, a.qkv_dtype, src0 + 8 * l + 4, y);
+      st4(a.vcache, B200_BF16, d + 8 * l, x);
+      st4(a.vcache, B200_BF16, d + 8 * l + 4, y);
     }
-  } else {
-    if (!active || !in_cache) return;
-    const size_t d = ((size_t)(h - a.n_q - a.n_kv) * a.max_seq + pos) * hd;
-    float x[4], y[4];
-    ld4(a.qkv, a.qkv_dtype, src0 + 8 * l, x);
-    ld4(a.qkv, a.qkv_dtype, src0 + 8 * l + 4, y);
-    st4(a.vcache, B200_BF16, d + 8 * l, x);
-    st4(a.vcache, B200_BF16, d + 8 * l + 4, y);
   }
 }
 
@@ -125,10 +132,7 @@ extern "C" int b200_qk_rope_cache(void* q_out, int q_dtype, void* kcache, void* 
   RopeArgs a{q_out, (uint16_t*)kcache, (uint16_t*)vcache, qkv, (const uint16_t*)qn_w,
              (const uint16_t*)kn_w, cos_t, sin_t, pos_dev, s, n_q, n_kv, hd, max_seq,
              q_dtype, qkv_dtype, eps};
-  const int hpw = 32 / (hd / 8);   // heads per warp
-  const long warps = ((long)s * (n_q + 2 * n_kv) + hpw - 1) / hpw;
-  const unsigned grid = (unsigned)((warps + 3) / 4);
-  cudaError_t e = launch(qk_rope_cache_kernel, dim3(grid), dim3(128), 0, (cudaStream_t)stream,
+  cudaError_t e = launch(qk_rope_cache_kernel, dim3((unsigned)s), dim3(kRopeThreads), 0, (cudaStream_t)stream,
                          (flags & B200_FLAG_PDL) != 0, a);
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
