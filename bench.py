@@ -390,7 +390,8 @@ def main():
     config = {"workload": f"{cfg.name} batch-1 greedy decode, {args.prompt}-token prompt + {K + W} steps "
                           f"(the reference's headline configuration)", "prompt_tokens": args.prompt,
               "parallelism": f"tp{world}",
-              "tp_allreduce": (args.tp_allreduce if world > 1 else None), "cache_policy": "inputs larger than L2 "
+              "tp_allreduce": (args.tp_allreduce if world > 1 else None), "settle_steps": (96 if world > 1 else 0),
+              "cache_policy": "inputs larger than L2 "
               "(every step streams all weights, 15 GB / TP)"}
 
     if args.impl == "reference":
@@ -429,9 +430,13 @@ def main():
         ops.set_tuning(*(int(t) for t in kv.split("=")))
 
     weights = make_decoder_weights(cfg, 1234, dev)
-    max_seq = args.prompt + W + K + 8
+    # Multi-GPU: some untimed replays before the W warm-up steps (config.settle_steps in the JSON
+    # line).  The first job on a fresh multi-GPU box measured up to 5 % slower at 2 GPUs than the
+    # same binary run again, and W = 8 warm-up steps last only ~20 ms.
+    settle = 96 if world > 1 else 0
+    max_seq = args.prompt + settle + W + K + 8
     eng = Llama31Optimized(cfg, weights, max_seq=max_seq, device=dev, tp_rank=rank, tp_size=world,
-                           group=group, max_new_tokens=W + K + 8, free_source_weights=True,
+                           group=group, max_new_tokens=settle + W + K + 8, free_source_weights=True,
                            fused_allreduce=args.tp_allreduce != "nccl",
                            fused_layers=args.persistent_layers)
     del weights
@@ -472,6 +477,10 @@ def main():
     # ---- decode: device-timed graph replays ----
     eng.capture()
     eng.set_step(first, args.prompt, 0)
+    if settle:
+        for _ in range(settle):
+            eng.graph.replay()
+        eng.set_step(first, args.prompt, 0)      # the timed steps run at the configured context
     for _ in range(W):
         eng.graph.replay()
     barrier()
