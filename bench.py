@@ -233,7 +233,9 @@ def run_secondary(args):
         cfg = C.QWEN3_4B if name == "qwen3-4b" else C.QWEN3_30B_A3B
         P = args.prompt or 1024                    # the reference quotes these two at 1k tokens
         w = Wt.make_decoder_weights(cfg, 1234, dev)
-        eng = DenseDecoder(cfg, w, max_seq=P + W + K + 8, device=dev, max_new_tokens=W + K + 8,
+        settle = 96 if world > 1 else 0            # untimed replays before the warm-up, see main()
+        eng = DenseDecoder(cfg, w, max_seq=P + settle + W + K + 8, device=dev,
+                           max_new_tokens=settle + W + K + 8,
                            free_source_weights=True, tp_rank=rank, tp_size=world, group=group,
                            fused_allreduce=args.tp_allreduce != "nccl",
                            fused_layers=args.persistent_layers,
@@ -251,6 +253,11 @@ def run_secondary(args):
         ops.check_status(dev)
         eng.capture()
         eng.set_step(first, P, 0)
+        if settle:
+            for _ in range(settle):
+                eng.graph.replay()
+            eng.set_step(first, P, 0)
+        line["settle_steps"] = settle
         sync()
         ms = over_ranks(_time_graph(eng.graph, K, W))
         sync()
