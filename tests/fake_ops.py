@@ -47,6 +47,9 @@ def _epilogue(y: Tensor, epilogue: int) -> Tensor:
         return F.silu(y[..., 0::2]) * y[..., 1::2]
     if epilogue == EPI_GELU:
         return F.gelu(y)
+    if epilogue == EPI_GEGLU:                   # stock projection: value half first, gate half second
+        half = y.shape[-1] // 2
+        return y[..., :half] * F.gelu(y[..., half:])
     return y
 
 
