@@ -8,7 +8,10 @@
 //              lane; warp w may only touch lanes 32 (w % 4) ..).  A thread pulls its whole row
 //              of 128 scores with tcgen05.ld, takes the row maximum and sum in registers (no
 //              exchange between threads), and writes P = exp2(...) as packed bf16 back into
-//              tensor memory over the first 64 columns of the scores it has just consumed.
+//              tensor memory: over the first 64 columns of the scores it has just consumed at
+//              head dim 128 (S_A, S_B, O_A, O_B fill the 512 columns), into 64 columns of its
+//              own at head dim 64, where the next tile's scores are then issued as soon as the
+//              current ones are in registers instead of after the O MMA that reads P.
 //   warp 8     TMA producer: Q tiles per item and stream, K and V tiles into one ring
 //   warp 9     MMA issuer (one lane): S_X = Q_X K^T (M128 N128, K = head dim) into the stream's
 //              score accumulator, and O_X += P_X V with P read straight from tensor memory and V
@@ -389,7 +392,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       fa_cursor_init(a, n_rounds, pv);
       ps = pv;
       int sq[2] = {0, 0};         // Q tiles consumed, per stream
-      int sg[2] = {0, 0};         // S tiles issued, per stream
       int pg[2] = {0, 0};         // O tiles issued, per stream
       int k_seen = -1;            // ring entry of the last K tile whose arrival was awaited
       bool ok = pv.valid;
@@ -413,7 +415,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           tc_mma(tS(x), umma_desc_k(sq_ + off), umma_desc_k(sk + off), idesc_s, k != 0 ? 1u : 0u);
         }
         tc_commit(bar(SF + x));
-        ++sg[x];
         if (ps.j == ps.it.n[x] - 1) { tc_commit(bar(QE + bi)); ++sq[x]; }   // Q free once these retire
         return 1;
       };
