@@ -131,3 +131,14 @@ def test_missing_library_fails_loudly(tmp_path):
     from hoid_optimized_models_b200 import _lib
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         _lib.load(str(tmp_path / "nope.so"))
+
+
+def test_header_and_binding_constants_agree():
+    """The enum values the Python side passes (epilogues, dtypes, error codes) are the header's."""
+    from hoid_optimized_models_b200 import _lib
+    text = re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+    enums = {k: int(v) for k, v in re.findall(r"\b(B200_[A-Z0-9_]+)\s*=\s*(-?\d+)", text)}
+    for name in ("EPI_NONE", "EPI_SWIGLU", "EPI_GELU", "EPI_GEGLU", "BF16", "F32", "FLAG_PDL"):
+        assert getattr(_lib, name) == enums["B200_" + name], name
+    for code, label in _lib.ERRORS.items():
+        assert enums[label.split()[0]] == code, label
