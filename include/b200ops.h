@@ -325,9 +325,12 @@ int b200_moe_grouped_gemm(const void* x, const void* w, void* y, const int* offs
  * Reference: models/llama31-8b/kernels/fmha_prefill_elastic.triton.py:1-58 (causal GQA),
  * models/bge-m3/kernels/bge_fa2_attention_nokb_postvb_late.ptx:1-2329 (bidirectional d64),
  * flash-attn-4 call at models/whisper-large-v3/whisper_optimized.py:356-360.
- * hd in {64, 128}; all strides multiples of 8 elements.
- * Runs on the tcgen05 tensor cores (TMA-fed, S and O accumulators in tensor memory, 128 x 128
- * tiles).  Each of q / k / v must be expressible as a 2D row-major view: the batch stride a
+ * hd in {64, 128}; all strides multiples of 8 elements; q_pos0 >= 0, kv_len >= 1, scale > 0
+ * (B200_ERR_SHAPE / B200_ERR_ARG otherwise).
+ * Runs on the tcgen05 tensor cores: persistent CTAs, TMA-fed, two 128-row query streams per
+ * CTA, scores, probabilities and output accumulators in tensor memory, 128 x 128 tiles.  The
+ * softmax raises a row's reference maximum only when it grows by more than 2^8, which is exact
+ * after the final division by the row sum.  Each of q / k / v must be expressible as a 2D row-major view: the batch stride a
  * multiple of the row stride, and the head stride either a multiple of the row stride (heads are
  * row blocks, as in the KV cache) or smaller than it (heads are column blocks, as in packed
  * projections).  status (nullable) receives B200_ERR_TIMEOUT if a bounded wait expired.
