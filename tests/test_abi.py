@@ -119,6 +119,29 @@ def test_validation_of_the_newer_entry_points(lib):
     assert lib.b200_add_rmsnorm(one, one, 0, one, 1, one, 0, one, 1, 12, 1e-5, 0, None) == -1
 
 
+def test_validation_of_attention_and_geglu(lib):
+    """The prefill attention and the GEGLU GEMM epilogue refuse bad arguments before any CUDA call."""
+    one = ctypes.c_void_p(16)
+    # out, q, k, v, batch, S, kv_len, q_pos0, n_q, n_kv, hd, 12 strides, causal, scale, status, flags, stream
+    strides = [512 * 8 * 128, 8 * 128, 128, 8 * 600 * 128, 128, 600 * 128, 8 * 600 * 128, 128, 600 * 128,
+               512 * 8 * 128, 8 * 128, 128]
+    args = [one, one, one, one, 1, 512, 512, 0, 8, 8, 128, *strides, 1, 0.088, None, 0, None]
+    bad = list(args); bad[7] = -1                             # negative position of the first query
+    assert lib.b200_flash_prefill_tc(*bad) == -1
+    bad = list(args); bad[24] = 0.0                           # scale must be positive
+    assert lib.b200_flash_prefill_tc(*bad) == -4
+    bad = list(args); bad[10] = 96                            # head dim 64 or 128
+    assert lib.b200_flash_prefill_tc(*bad) == -1
+    bad = list(args); bad[12] = 8 * 128 + 4                   # stride not a multiple of 8 elements
+    assert lib.b200_flash_prefill_tc(*bad) == -2
+    # GEGLU: N = 2 O must be a multiple of 16, no residual, bf16 output only, not grouped
+    geglu = 3
+    assert lib.b200_gemm_bf16(one, one, one, 0, 128, 200, 64, 64, 64, 104, None, None, 0, geglu, None, 0, None) == -1
+    assert lib.b200_gemm_bf16(one, one, one, 0, 128, 256, 64, 64, 64, 128, None, one, 128, geglu, None, 0, None) == -1
+    assert lib.b200_gemm_bf16(one, one, one, 1, 128, 256, 64, 64, 64, 128, None, None, 0, geglu, None, 0, None) == -4
+    assert lib.b200_gemm_bf16(one, one, one, 0, 128, 256, 64, 64, 64, 128, None, None, 0, 4, None, 0, None) == -4
+
+
 def test_ops_refuse_cpu_tensors():
     """There is no CPU fallback: CPU tensors are an error, not a slow path."""
     from hoid_optimized_models_b200 import ops
