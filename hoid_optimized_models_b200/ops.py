@@ -456,11 +456,12 @@ def moe_decode_down(y: Tensor, act: Tensor, w_down: Tensor, ids: Tensor,
 @torch.library.custom_op("b200::flash_prefill", mutates_args=("out",))
 def flash_prefill(out: Tensor, q: Tensor, k: Tensor, v: Tensor, kv_len: int, causal: bool,
                   scale: float, q_pos0: int = 0) -> None:
-    """Flash attention over strided views (tcgen05 / TMEM kernel).
+    """Flash attention over strided views (persistent tcgen05 / TMEM kernel).
 
     q / out: [B, S, n_q, hd] views; k / v: [B, n_kv, L, hd] views (any strides with a
     contiguous last dimension), attending to the first kv_len of L keys.  A decode cache
-    [n_kv, max_seq, hd] is passed as cache.unsqueeze(0)."""
+    [n_kv, max_seq, hd] is passed as cache.unsqueeze(0).  Causal: query row i sees keys up to
+    q_pos0 + i.  hd is 64 or 128, q_pos0 >= 0, kv_len >= 1, scale > 0."""
     for t, n in ((out, "out"), (q, "q"), (k, "k"), (v, "v")):
         _bf16(t, n)
         if t.stride(-1) != 1:

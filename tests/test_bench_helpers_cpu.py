@@ -64,3 +64,21 @@ def test_traffic_is_read_from_the_tracked_figures_file(tmp_path):
         json.dump({"k": {"dram_bytes_per_launch": 100.0, "layers": 2}, "flat": {"dram_bytes_per_launch": 7.0}}, f)
     assert b.ncu_traffic("k", 32) == 1600.0 and b.ncu_traffic("flat", 32) == 7.0
     assert b.ncu_traffic("missing", 32) is None
+
+
+def test_fake_gemm_epilogues_follow_the_abi_conventions():
+    """The CPU stand-in of ops.gemm used by the host-logic tests implements the same epilogue
+    conventions as the library: SwiGLU over interleaved gate / up rows, GEGLU over a stock
+    [value half; gate half] projection."""
+    import torch
+    from tests import fake_ops
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(5, 16, generator=g)
+    w = torch.randn(24, 16, generator=g)
+    b = torch.randn(24, generator=g)
+    full = x @ w.T + b
+    y = torch.empty(5, 12)
+    fake_ops.gemm(y, x, w, bias=b, epilogue=fake_ops.EPI_GEGLU)
+    assert torch.allclose(y, full[:, :12] * torch.nn.functional.gelu(full[:, 12:]), atol=1e-5)
+    fake_ops.gemm(y, x, w, bias=b, epilogue=fake_ops.EPI_SWIGLU)
+    assert torch.allclose(y, torch.nn.functional.silu(full[:, 0::2]) * full[:, 1::2], atol=1e-5)
