@@ -470,7 +470,11 @@ def test_flash_prefill_growing_row_maxima(dev, S, n_q, n_kv, hd, causal):
 
 
 @pytest.mark.parametrize("B,S,n_q,n_kv,hd,causal", [(12, 512, 16, 16, 64, False), (5, 700, 8, 2, 128, True),
-                                                     (3, 130, 6, 6, 64, False)])
+                                                     (3, 130, 6, 6, 64, False),
+                                                     # three query tiles per head: every second work item has
+                                                     # no rows for its second stream, and with more items than
+                                                     # SMs a CTA walks both kinds back to back
+                                                     (8, 300, 16, 4, 128, True), (10, 300, 16, 16, 64, False)])
 def test_flash_prefill_batched_many_rounds(dev, B, S, n_q, n_kv, hd, causal):
     """More work items than SMs: every CTA walks several (batch, head, query tile) items back
     to back, with the Q / K / V rings and the S accumulators carried across item boundaries."""
