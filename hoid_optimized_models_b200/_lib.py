@@ -94,12 +94,50 @@ def load(path: str = LIB_PATH) -> C.CDLL:
 
 
 _LIB = None
+_NVTX = os.environ.get("B200OPS_NVTX", "0") == "1"
+_NVTX_PROXY = None
 
 
-def lib() -> C.CDLL:
-    global _LIB
+class _NvtxProxy:
+    """The loaded library with every entry point wrapped in an NVTX range named after it, so that
+    a timeline (ncu --nvtx, or any NVTX consumer) attributes kernels to the C-ABI call that launched
+    them.  Ranges cost nothing on the device; the Python wrapper costs about a microsecond per call,
+    which is why it is opt-in (set_nvtx(True) or B200OPS_NVTX=1)."""
+
+    def __init__(self, raw: C.CDLL):
+        self._raw = raw
+        self._wrapped = {}
+
+    def __getattr__(self, name):
+        fn = self._wrapped.get(name)
+        if fn is None:
+            raw_fn = getattr(self._raw, name)
+            import torch
+
+            def fn(*args, _raw_fn=raw_fn, _name=name):
+                torch.cuda.nvtx.range_push(_name)
+                try:
+                    return _raw_fn(*args)
+                finally:
+                    torch.cuda.nvtx.range_pop()
+            self._wrapped[name] = fn
+        return fn
+
+
+def set_nvtx(enabled: bool) -> None:
+    """NVTX range per C-ABI call (off by default)."""
+    global _NVTX
+    _NVTX = bool(enabled)
+
+
+def lib():
+    global _LIB, _NVTX_PROXY
     if _LIB is None:
         _LIB = load()
+    if _NVTX:
+        if _NVTX_PROXY is None or _NVTX_PROXY._raw is not _LIB:
+            _NVTX_PROXY = _NvtxProxy(_LIB)
+        return _NVTX_PROXY
     return _LIB
 
 

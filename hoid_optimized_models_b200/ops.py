@@ -26,6 +26,12 @@ def set_pdl(enabled: bool) -> None:
     _PDL = bool(enabled)
 
 
+def set_nvtx(enabled: bool) -> None:
+    """Wrap every library call in an NVTX range named after its C entry point (off by default;
+    also B200OPS_NVTX=1).  For timelines: `ncu --nvtx` attributes each kernel to its call."""
+    _lib.set_nvtx(enabled)
+
+
 def set_tuning(key: int, value: int) -> None:
     """Process-wide kernel tuning knob (the B200_TUNE_* keys of include/b200ops.h)."""
     check(_lib.lib().b200_set_tuning(key, value), "b200_set_tuning")

@@ -165,3 +165,22 @@ def test_header_and_binding_constants_agree():
         assert getattr(_lib, name) == enums["B200_" + name], name
     for code, label in _lib.ERRORS.items():
         assert enums[label.split()[0]] == code, label
+
+
+def test_nvtx_ranges_wrap_every_call(lib, monkeypatch):
+    """Opt-in NVTX: each C-ABI call sits in a range named after its entry point, results pass
+    through unchanged, and switching it off returns the plain library."""
+    from hoid_optimized_models_b200 import _lib
+    events = []
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: events.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: events.append(("pop", None)))
+    monkeypatch.setattr(_lib, "_LIB", lib)
+    _lib.set_nvtx(True)
+    try:
+        assert _lib.lib().b200_sm_count() == 148
+        assert _lib.lib().b200_gemv_bf16(None, 0, None, None, 0, 256, 8, 256, None, None, 0.0, None, None,
+                                         0, 0, 0, None) == -4
+    finally:
+        _lib.set_nvtx(False)
+    assert events == [("push", "b200_sm_count"), ("pop", None), ("push", "b200_gemv_bf16"), ("pop", None)]
+    assert _lib.lib() is lib
