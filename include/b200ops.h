@@ -330,7 +330,10 @@ int b200_moe_grouped_gemm(const void* x, const void* w, void* y, const int* offs
  * Runs on the tcgen05 tensor cores: persistent CTAs, TMA-fed, two 128-row query streams per
  * CTA, scores, probabilities and output accumulators in tensor memory, 128 x 128 tiles.  The
  * softmax raises a row's reference maximum only when it grows by more than 2^8, which is exact
- * after the final division by the row sum.  Each of q / k / v must be expressible as a 2D row-major view: the batch stride a
+ * after the final division by the row sum.  Keys are consumed in tiles of 128: the rows of k and
+ * v between kv_len and the end of the last tile are masked to probability zero but still enter
+ * the second MMA as 0 * v, so v must hold finite values there (rows past the end of the whole
+ * view are zero-filled by the TMA unit; a zero-initialised cache, as the engines use, is enough).  Each of q / k / v must be expressible as a 2D row-major view: the batch stride a
  * multiple of the row stride, and the head stride either a multiple of the row stride (heads are
  * row blocks, as in the KV cache) or smaller than it (heads are column blocks, as in packed
  * projections).  status (nullable) receives B200_ERR_TIMEOUT if a bounded wait expired.
