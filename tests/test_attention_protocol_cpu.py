@@ -334,6 +334,21 @@ def test_protocol_under_random_schedules(hd, S, n_q, batch, causal, G):
             assert sim.outputs == want
 
 
+def test_protocol_on_random_problems():
+    """Random shapes (ragged sequence lengths, longer key ranges than queries, one to five CTAs),
+    one random CTA and one random schedule each."""
+    rng = random.Random(7)
+    for _ in range(60):
+        hd = rng.choice([64, 128])
+        S = rng.choice([1, 64, 128, 129, 200, 256, 257, 300, 511, 512, 700, 900, 1100, 1300])
+        n_q, batch, causal = rng.randint(1, 5), rng.randint(1, 3), rng.random() < 0.5
+        kv_len = S if causal else rng.choice([S, S + 77, 3 * S + 5])
+        n_items = ((S + 255) // 256) * n_q * batch
+        G = min(rng.randint(1, 5), n_items)
+        items = cta_items(rng.randrange(G), G, S, kv_len, n_q, batch, causal)
+        Sim(hd, items, rng.randrange(1 << 30)).run()
+
+
 @pytest.mark.parametrize("hd,fault", [(64, "no_wait_for_loaded_scores"), (64, "p_stored_without_waiting_for_o_mma"),
                                       (128, "q_released_a_tile_early"), (128, "epilogue_without_waiting_for_o_mma"),
                                       (64, "epilogue_without_waiting_for_o_mma")])
